@@ -1,0 +1,226 @@
+/*
+ * b200ops.h -- C ABI of the sm_100a kernel library (libb200ops.so).
+ *
+ * This library takes the place that the closed vendor kernel library
+ * (`topsaten::topsaten<Op>(out, in..., scalars..., stream)`) has in the
+ * reference backend: the host code of the PrivateUse1 backend marshals every
+ * at::Tensor into a non-owning {dims, strides, dtype, data} view and calls one
+ * entry point per operator with the stream as the last argument
+ * (reference: torch_gcu/csrc/aten/aot_ops/topsaten_bridge_define.h:323-427,
+ * view construction torch_gcu/csrc/gcu/gcu_utils.cpp:79-108).
+ *
+ * Conventions
+ *  - every entry point is `extern "C"`, re-entrant, and takes plain pointers
+ *    and sizes only; no C++ or torch type crosses this boundary;
+ *  - tensors are borrowed for the duration of the call; kernels are enqueued on
+ *    `stream` (a cudaStream_t passed as void*) and the call returns without
+ *    synchronising;
+ *  - outputs are allocated by the caller (the host code runs ATen's meta
+ *    functions, exactly as the reference's shape-inference layer does);
+ *  - nothing in here allocates device memory: kernels that need scratch take a
+ *    caller-supplied workspace whose size the matching *_workspace_size
+ *    function reports;
+ *  - every function returns a b200Status; b200_last_error() gives the
+ *    thread-local message of the last non-OK status. The host maps non-OK to
+ *    an exception (reference: CHECK_TOPSATEN_CALL, gcu_utils.cpp:64-77).
+ *    Kernels never trap.
+ *  - strides are in ELEMENTS, sizes/strides are int64, ndim <= 8; a rank-0
+ *    tensor is passed with ndim == 0 (numel 1).
+ */
+#ifndef B200OPS_H_
+#define B200OPS_H_
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility */
+#endif
+
+#define B200_MAX_DIMS 8
+
+typedef enum b200Status {
+  B200_OK = 0,
+  B200_BAD_PARAM = 1,           /* null pointer, shape/stride/dtype mismatch   */
+  B200_NOT_SUPPORTED = 2,       /* valid request this library has no kernel for */
+  B200_LAUNCH_FAILED = 3,       /* CUDA reported an error at enqueue            */
+  B200_WORKSPACE_TOO_SMALL = 4,
+  B200_TIMEOUT = 5
+} b200Status;
+
+typedef enum b200DType {
+  B200_F32 = 0,
+  B200_BF16 = 1,
+  B200_F16 = 2,
+  B200_F64 = 3,
+  B200_I64 = 4,
+  B200_I32 = 5,
+  B200_I16 = 6,
+  B200_I8 = 7,
+  B200_U8 = 8,
+  B200_BOOL = 9
+} b200DType;
+
+/* Non-owning strided view of device memory. */
+typedef struct b200Tensor {
+  void* data;
+  int32_t dtype; /* b200DType */
+  int32_t ndim;
+  int64_t sizes[B200_MAX_DIMS];
+  int64_t strides[B200_MAX_DIMS];
+} b200Tensor;
+
+typedef void* b200Stream; /* cudaStream_t */
+
+/* ---- library / device queries ------------------------------------------- */
+const char* b200_last_error(void);
+const char* b200_version(void);
+int b200_device_count(void);            /* 0 when no usable GPU / driver     */
+int b200_sm_count(int device);          /* multiprocessors of `device`, or -1 */
+size_t b200_dtype_size(int32_t dtype);  /* bytes per element, 0 if unknown    */
+/* Index kernels never trap on an out-of-range index: they substitute index 0
+ * (or drop the element) and set bit 0 of a device-side error word. This call
+ * synchronises the device, returns the word and clears it; the host uses it in
+ * its per-op sync/debug mode (reference: op_sync_mode,
+ * torch_gcu/csrc/gcu/gcu_stream.cpp:382-386).                                */
+b200Status b200_device_error_fetch(uint32_t* flags);
+
+/* ---- elementwise (reference: generated aotops::add_out / mul_out / silu_out
+ *      -> topsatenAdd / topsatenMul / topsatenSilu; scalar-operand variants
+ *      codegen/gen_backend_stubs.py:1061-1078) -------------------------------
+ * Operands are broadcast against `out` by the caller (stride 0 on expanded
+ * dims) and must already have out's dtype (type promotion is the host's job,
+ * as TensorIterator does it in ATen's meta).                                 */
+b200Status b200_add(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                    double alpha, b200Stream stream); /* out = a + alpha*b     */
+b200Status b200_mul(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                    b200Stream stream);
+b200Status b200_add_scalar(const b200Tensor* out, const b200Tensor* a, double b,
+                           double alpha, b200Stream stream); /* a + alpha*b    */
+b200Status b200_mul_scalar(const b200Tensor* out, const b200Tensor* a, double b,
+                           b200Stream stream);
+b200Status b200_silu(const b200Tensor* out, const b200Tensor* a, b200Stream stream);
+/* Unary / binary helpers the unfused decoder layer reaches through the same
+ * generated path (yaml rows neg.out, rsqrt.out, pow.Tensor_Scalar_out, ...). */
+typedef enum b200UnaryOp {
+  B200_UNARY_NEG = 0, B200_UNARY_RSQRT = 1, B200_UNARY_SQRT = 2, B200_UNARY_EXP = 3,
+  B200_UNARY_SIGMOID = 4, B200_UNARY_TANH = 5, B200_UNARY_RELU = 6, B200_UNARY_ABS = 7,
+  B200_UNARY_RECIPROCAL = 8, B200_UNARY_COS = 9, B200_UNARY_SIN = 10, B200_UNARY_LOG = 11,
+  B200_UNARY_GELU = 12 /* erf form, as CPU ATen's default */
+} b200UnaryOp;
+b200Status b200_unary(const b200Tensor* out, const b200Tensor* a, int32_t op,
+                      b200Stream stream);
+b200Status b200_pow_scalar(const b200Tensor* out, const b200Tensor* a, double exponent,
+                           b200Stream stream);
+b200Status b200_sub(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                    double alpha, b200Stream stream); /* out = a - alpha*b */
+b200Status b200_div(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                    b200Stream stream);
+b200Status b200_fill(const b200Tensor* out, double value, b200Stream stream);
+
+/* ---- copy / cast (reference: aotops::_copy_from -> copy_device_to_device ->
+ *      topsatenCopy, torch_gcu/csrc/aten/aot_ops/gcu_copy.cpp:34-198,402-442)
+ * dst[i] = (dst dtype) src[i] for same-shaped (caller-expanded) views; any
+ * strides, any pair of dtypes. fp32->bf16 is round-to-nearest-even with NaN
+ * mapped to 0x7FC0, the rule of c10::BFloat16.                               */
+b200Status b200_copy(const b200Tensor* dst, const b200Tensor* src, b200Stream stream);
+
+/* ---- reductions ---------------------------------------------------------- */
+/* reference: generated aotops::sum_out -> topsatenSum. `dims` lists the reduced
+ * dimensions of `in` (non-negative, unique); out has the reduced shape with or
+ * without kept 1-dims (its numel decides nothing: only its data/dtype are used).
+ * Accumulation is fp32 for f32/bf16/f16 inputs, fp64 for f64, int64 for ints. */
+size_t b200_sum_workspace_size(const b200Tensor* in, const int64_t* dims, int32_t ndims);
+b200Status b200_sum(const b200Tensor* out, const b200Tensor* in, const int64_t* dims,
+                    int32_t ndims, int32_t mean /* 1: divide by count */,
+                    void* workspace, size_t workspace_bytes, b200Stream stream);
+/* reference: generated aotops::_softmax_out -> topsatenSoftmaxForward
+ * (codegen/gcu_native_functions.yaml:182-183). out dtype may be f32 for a
+ * bf16/f16 input (half_to_float).                                            */
+b200Status b200_softmax(const b200Tensor* out, const b200Tensor* in, int64_t dim,
+                        b200Stream stream);
+/* reference: aotops::native_layer_norm -> topsatenNativeLayerNorm
+ * (torch_gcu/csrc/aten/aot_ops/gcu_layer_norm.cpp:17-86). `in` is viewed as
+ * (M, N) contiguous, N = product of normalized_shape; weight/bias may be NULL;
+ * mean/rstd are (M) tensors in the accumulate type (f32) or in's dtype.       */
+b200Status b200_native_layer_norm(const b200Tensor* out, const b200Tensor* mean,
+                                  const b200Tensor* rstd, const b200Tensor* in,
+                                  int64_t M, int64_t N, const b200Tensor* weight,
+                                  const b200Tensor* bias, double eps, b200Stream stream);
+
+/* ---- index ops ----------------------------------------------------------- */
+/* reference: generated aotops::index_select -> topsatenIndexSelect (this is
+ * also where aten::embedding lands). index: 1-D int32/int64.                 */
+b200Status b200_index_select(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                             const b200Tensor* index, b200Stream stream);
+/* reference: generated aotops::gather_out -> topsatenGather.                  */
+b200Status b200_gather(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                       const b200Tensor* index, b200Stream stream);
+/* reference: generated aotops::scatter_add_out -> topsatenScatterAdd.
+ * out = self; out[index[i][j]][j] += src[i][j] (for dim 0; any dim accepted).
+ * Every destination element receives its addends in ascending source order
+ * along `dim`, starting from self's value -- the order CPU ATen uses -- so the
+ * result is bit-identical to the CPU's and run-to-run reproducible. out may
+ * alias self.                                                                */
+size_t b200_scatter_add_workspace_size(const b200Tensor* self, int64_t dim,
+                                       const b200Tensor* index, const b200Tensor* src);
+b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                            const b200Tensor* index, const b200Tensor* src,
+                            void* workspace, size_t workspace_bytes, b200Stream stream);
+/* reference: aotops::_index_put_impl_ -> topsatenIndexPutImpl
+ * (torch_gcu/csrc/aten/aot_ops/gcu_tensor_advanced_indexing.cpp:60-90).
+ * self[index[i], ...] (+)= values[i, ...] for ONE index tensor over the
+ * leading dimension of a contiguous self (the host reduces the general case to
+ * this by linearising the indexed dims). accumulate != 0 adds in ascending i
+ * order (bit-identical to CPU ATen under deterministic algorithms);
+ * accumulate == 0 writes and, on duplicates, the highest i wins.             */
+size_t b200_index_put_workspace_size(const b200Tensor* self, const b200Tensor* index,
+                                     const b200Tensor* values);
+b200Status b200_index_put(const b200Tensor* self, const b200Tensor* index,
+                          const b200Tensor* values, int32_t accumulate,
+                          void* workspace, size_t workspace_bytes, b200Stream stream);
+/* reference: efficient::device_int32_indices_index -> topsatenIndex
+ * (torch_gcu/csrc/efficient_ops/ops.cpp:335-342) and aotops index
+ * (gcu_tensor_advanced_indexing.cpp:40-58). Arguments are ATen's AdvancedIndex
+ * (ops.cpp:48-90): `src` is self restrided to out's shape with stride 0 on the
+ * indexed dims, `indices[k]` are int32 or int64 tensors broadcast to out's
+ * shape, and indexed_sizes/strides (elements) describe the replaced dims.
+ * Negative indices wrap once, as in ATen.                                    */
+b200Status b200_index(const b200Tensor* out, const b200Tensor* src,
+                      const b200Tensor* const* indices, int32_t n_indices,
+                      const int64_t* indexed_sizes, const int64_t* indexed_strides,
+                      b200Stream stream);
+
+/* ---- fused inference ops (no counterpart kernel in the reference, which runs
+ *      them as chains of the ops above; they sit beside the reference's one
+ *      efficient op, torch_gcu/csrc/efficient_ops/ops.cpp:335-342) ---------- */
+/* h = x + residual (rounded to the I/O dtype, written to residual_out);
+ * y = h * rsqrt(mean(h^2) + eps) * weight, fp32 internally. x/residual: (M,N)
+ * contiguous bf16/f16/f32. residual may be NULL (plain RMSNorm). Outputs may
+ * alias the inputs.                                                          */
+b200Status b200_rms_norm_residual(const b200Tensor* y, const b200Tensor* residual_out,
+                                  const b200Tensor* x, const b200Tensor* residual,
+                                  const b200Tensor* weight, double eps, b200Stream stream);
+/* Rotate-half rotary embedding (the Llama / HF convention):
+ * out[..., i]       = x[..., i]*cos[p,i] - x[..., i+D/2]*sin[p,i]
+ * out[..., i+D/2]   = x[..., i+D/2]*cos[p,i] + x[..., i]*sin[p,i],  i < D/2,
+ * x: (B,S,H,D) with D contiguous; cos/sin: f32 (P, D/2) tables; positions:
+ * int64 (B,S) or NULL for p = s. fp32 math, one rounding. In place allowed.   */
+b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tensor* cos_table,
+                     const b200Tensor* sin_table, const b200Tensor* positions,
+                     b200Stream stream);
+/* out = silu(gate) * up, fp32 math, one rounding. 2-D views with contiguous
+ * last dim (gate and up may be the two halves of one projection output).      */
+b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200Tensor* up,
+                       b200Stream stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200OPS_H_ */

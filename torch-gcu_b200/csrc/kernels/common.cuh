@@ -1,0 +1,256 @@
+// Shared helpers of the sm_100a kernel library: status/error plumbing, tensor
+// view inspection, dtype dispatch, 128-bit vector access and the bf16/f16
+// conversions whose rounding matches c10::BFloat16 / c10::Half bit for bit.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "b200ops.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- errors ----
+char* error_buffer();  // thread-local, 512 bytes (runtime.cu)
+
+inline b200Status fail(b200Status st, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return st;
+}
+
+#define B200_REQUIRE(cond, status, ...)                \
+  do {                                                 \
+    if (!(cond)) return ::b200::fail((status), __VA_ARGS__); \
+  } while (0)
+
+inline b200Status check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return fail(B200_LAUNCH_FAILED, "%s: %s", what, cudaGetErrorString(e));
+  return B200_OK;
+}
+
+int sm_count_current_device();  // cached per device (runtime.cu)
+
+// ------------------------------------------------------------ tensor view ----
+inline int64_t numel(const b200Tensor* t) {
+  int64_t n = 1;
+  for (int i = 0; i < t->ndim; ++i) n *= t->sizes[i];
+  return n;
+}
+
+inline bool valid(const b200Tensor* t) {
+  if (!t || t->ndim < 0 || t->ndim > B200_MAX_DIMS) return false;
+  for (int i = 0; i < t->ndim; ++i)
+    if (t->sizes[i] < 0) return false;
+  if (t->dtype < 0 || t->dtype > B200_BOOL) return false;
+  return numel(t) == 0 || t->data != nullptr;
+}
+
+inline bool is_contiguous(const b200Tensor* t) {
+  int64_t expect = 1;
+  for (int i = t->ndim - 1; i >= 0; --i) {
+    if (t->sizes[i] == 1) continue;
+    if (t->strides[i] != expect) return false;
+    expect *= t->sizes[i];
+  }
+  return true;
+}
+
+inline bool same_shape(const b200Tensor* a, const b200Tensor* b) {
+  if (a->ndim != b->ndim) return false;
+  for (int i = 0; i < a->ndim; ++i)
+    if (a->sizes[i] != b->sizes[i]) return false;
+  return true;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline size_t dtype_size(int32_t dt) {
+  switch (dt) {
+    case B200_F32: case B200_I32: return 4;
+    case B200_BF16: case B200_F16: case B200_I16: return 2;
+    case B200_F64: case B200_I64: return 8;
+    case B200_I8: case B200_U8: case B200_BOOL: return 1;
+    default: return 0;
+  }
+}
+
+// Strided addressing of up to three operands over a common (collapsed) shape.
+// Dimension 0 is the fastest-varying one.
+template <int NARGS>
+struct StridedIndexer {
+  int ndim;
+  int64_t sizes[B200_MAX_DIMS];
+  int64_t strides[NARGS][B200_MAX_DIMS];
+
+  __host__ __device__ void offsets(int64_t linear, int64_t (&off)[NARGS]) const {
+#pragma unroll
+    for (int a = 0; a < NARGS; ++a) off[a] = 0;
+#pragma unroll 1
+    for (int d = 0; d < ndim; ++d) {
+      int64_t q = linear / sizes[d];
+      int64_t r = linear - q * sizes[d];
+      linear = q;
+#pragma unroll
+      for (int a = 0; a < NARGS; ++a) off[a] += r * strides[a][d];
+    }
+  }
+};
+
+// Builds an indexer over `ts[0..NARGS)` (all of the same shape) and merges
+// neighbouring dimensions that every operand walks contiguously.
+template <int NARGS>
+inline StridedIndexer<NARGS> make_indexer(const b200Tensor* const (&ts)[NARGS]) {
+  StridedIndexer<NARGS> ix;
+  int nd = 0;
+  const b200Tensor* t0 = ts[0];
+  for (int i = t0->ndim - 1; i >= 0; --i) {  // innermost first
+    int64_t sz = t0->sizes[i];
+    if (sz == 1) continue;
+    bool merged = false;
+    if (nd > 0) {
+      bool can = true;
+      for (int a = 0; a < NARGS; ++a)
+        if (ts[a]->strides[i] != ix.strides[a][nd - 1] * ix.sizes[nd - 1]) can = false;
+      if (can) {
+        ix.sizes[nd - 1] *= sz;
+        merged = true;
+      }
+    }
+    if (!merged) {
+      ix.sizes[nd] = sz;
+      for (int a = 0; a < NARGS; ++a) ix.strides[a][nd] = ts[a]->strides[i];
+      ++nd;
+    }
+  }
+  if (nd == 0) {
+    ix.sizes[0] = 1;
+    for (int a = 0; a < NARGS; ++a) ix.strides[a][0] = 0;
+    nd = 1;
+  }
+  ix.ndim = nd;
+  return ix;
+}
+
+// ------------------------------------------------------------- conversions ----
+// fp32 -> bf16, round to nearest even; every NaN becomes 0x7FC0 (c10::BFloat16).
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7FC0;
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
+  return __uint_as_float(static_cast<uint32_t>(b) << 16);
+}
+// fp32 -> fp16, round to nearest even; NaN becomes sign|0x7E00 (c10::Half).
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float f) {
+  uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>(((u >> 16) & 0x8000u) | 0x7E00u);
+  return __half_as_ushort(__float2half_rn(f));
+}
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
+  return __half2float(__ushort_as_half(h));
+}
+
+// Storage types: bf16 and f16 are carried as tagged 16-bit integers so that all
+// arithmetic goes through the conversions above.
+struct bf16_t { uint16_t bits; };
+struct f16_t { uint16_t bits; };
+
+template <typename T> struct OpMath { using type = T; };
+template <> struct OpMath<bf16_t> { using type = float; };
+template <> struct OpMath<f16_t> { using type = float; };
+
+template <typename T> __device__ __forceinline__ typename OpMath<T>::type load_as_math(T v) { return v; }
+template <> __device__ __forceinline__ float load_as_math<bf16_t>(bf16_t v) { return bf16_bits_to_f32(v.bits); }
+template <> __device__ __forceinline__ float load_as_math<f16_t>(f16_t v) { return f16_bits_to_f32(v.bits); }
+
+template <typename T> __device__ __forceinline__ T store_from_math(typename OpMath<T>::type v) { return v; }
+template <> __device__ __forceinline__ bf16_t store_from_math<bf16_t>(float v) { return bf16_t{f32_to_bf16_bits(v)}; }
+template <> __device__ __forceinline__ f16_t store_from_math<f16_t>(float v) { return f16_t{f32_to_f16_bits(v)}; }
+
+// ------------------------------------------------------- 128-bit accessors ----
+template <typename T> struct alignas(16) Vec16 { T v[16 / sizeof(T)]; };
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> load_stream16(const T* p) {
+  int4 r = __ldcs(reinterpret_cast<const int4*>(p));
+  return *reinterpret_cast<Vec16<T>*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ Vec16<T> load16(const T* p) {
+  int4 r = *reinterpret_cast<const int4*>(p);
+  return *reinterpret_cast<Vec16<T>*>(&r);
+}
+template <typename T>
+__device__ __forceinline__ void store_stream16(T* p, const Vec16<T>& v) {
+  __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const Vec16<T>& v) {
+  *reinterpret_cast<int4*>(p) = *reinterpret_cast<const int4*>(&v);
+}
+
+// --------------------------------------------------------------- dispatch ----
+#define B200_DISPATCH_FLOAT(DT, T, ...)                                          \
+  switch (DT) {                                                                  \
+    case B200_F32: { using T = float; __VA_ARGS__; break; }                      \
+    case B200_BF16: { using T = ::b200::bf16_t; __VA_ARGS__; break; }            \
+    case B200_F16: { using T = ::b200::f16_t; __VA_ARGS__; break; }              \
+    case B200_F64: { using T = double; __VA_ARGS__; break; }                     \
+    default: return ::b200::fail(B200_NOT_SUPPORTED, "%s: dtype %d not supported", __func__, (int)(DT)); \
+  }
+
+#define B200_DISPATCH_ARITH(DT, T, ...)                                          \
+  switch (DT) {                                                                  \
+    case B200_F32: { using T = float; __VA_ARGS__; break; }                      \
+    case B200_BF16: { using T = ::b200::bf16_t; __VA_ARGS__; break; }            \
+    case B200_F16: { using T = ::b200::f16_t; __VA_ARGS__; break; }              \
+    case B200_F64: { using T = double; __VA_ARGS__; break; }                     \
+    case B200_I64: { using T = int64_t; __VA_ARGS__; break; }                    \
+    case B200_I32: { using T = int32_t; __VA_ARGS__; break; }                    \
+    case B200_I16: { using T = int16_t; __VA_ARGS__; break; }                    \
+    case B200_I8: { using T = int8_t; __VA_ARGS__; break; }                      \
+    case B200_U8: { using T = uint8_t; __VA_ARGS__; break; }                     \
+    default: return ::b200::fail(B200_NOT_SUPPORTED, "%s: dtype %d not supported", __func__, (int)(DT)); \
+  }
+
+// Byte-width dispatch for pure data movement (bit-exact by construction).
+#define B200_DISPATCH_BYTES(NBYTES, T, ...)                                      \
+  switch (NBYTES) {                                                              \
+    case 1: { using T = uint8_t; __VA_ARGS__; break; }                           \
+    case 2: { using T = uint16_t; __VA_ARGS__; break; }                          \
+    case 4: { using T = uint32_t; __VA_ARGS__; break; }                          \
+    case 8: { using T = uint64_t; __VA_ARGS__; break; }                          \
+    default: return ::b200::fail(B200_NOT_SUPPORTED, "%s: element size %d", __func__, (int)(NBYTES)); \
+  }
+
+// Grid size for grid-stride kernels: a whole number of waves of the device.
+inline int grid_for(int64_t work_items, int threads, int blocks_per_sm) {
+  int64_t need = (work_items + threads - 1) / threads;
+  int64_t cap = static_cast<int64_t>(sm_count_current_device()) * blocks_per_sm;
+  if (need < 1) need = 1;
+  return static_cast<int>(need < cap ? need : cap);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace b200

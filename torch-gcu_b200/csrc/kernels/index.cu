@@ -1,0 +1,952 @@
+// Index kernels: index_select (and embedding), gather, advanced index with
+// int32/int64 indices, and the deterministic scatter_add / index_put.
+//
+// Pure moves (index_select, gather, index) copy the widest unit the layout
+// allows -- 128-bit for the row-shaped cases -- with the index read once.
+//
+// scatter_add / index_put(accumulate) must equal CPU ATen bit for bit, and the
+// CPU adds the sources of one destination in ascending source order starting
+// from self's value. The kernels therefore invert the index first: a stable
+// least-significant-digit radix sort of (destination, source) pairs (8-bit
+// digits, hand-written: per-tile digit histograms, one scan, stable per-tile
+// ranking with warp match), then one warp per destination row walks its
+// segment in order, several source rows in flight, adding sequentially. No
+// floating-point atomics anywhere, so results are run-to-run identical.
+#include "common.cuh"
+
+namespace b200 {
+
+// Device-side error word: kernels OR a bit in instead of trapping.
+__device__ unsigned int g_device_error_word = 0;
+enum : unsigned int { kErrIndexOutOfRange = 1u };
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <typename I> __device__ __forceinline__ int64_t load_index(const void* p, int64_t i);
+template <> __device__ __forceinline__ int64_t load_index<int64_t>(const void* p, int64_t i) {
+  return static_cast<const int64_t*>(p)[i];
+}
+template <> __device__ __forceinline__ int64_t load_index<int32_t>(const void* p, int64_t i) {
+  return static_cast<const int32_t*>(p)[i];
+}
+
+// ------------------------------------------------------------ row gather ----
+// dst row r = (o, k) takes src row (o, index[k]). Rows are `upr` copy units
+// long. A group of 2^g_log lanes moves one chunk of a row (4 units per lane).
+struct RowGatherArgs {
+  const void* src;
+  void* dst;
+  const void* index;
+  int64_t index_stride;   // elements between consecutive indices
+  int64_t n_rows;         // outer * K destination rows
+  int64_t K;              // indices per outer slice
+  int64_t S;              // size of the indexed source dim (bounds check / wrap)
+  int64_t upr;            // units per row
+  int64_t src_outer_stride, src_row_stride;  // in units
+  int64_t chunks_per_row;
+  int g_log;
+  int wrap_negative;
+};
+
+template <typename U, typename I, typename W /* item arithmetic */>
+__global__ void __launch_bounds__(kThreads)
+row_gather_kernel(RowGatherArgs a) {
+  const int G = 1 << a.g_log;
+  const W lane = threadIdx.x & (G - 1);
+  const W groups_per_block = kThreads >> a.g_log;
+  const W n_items = static_cast<W>(a.n_rows) * static_cast<W>(a.chunks_per_row);
+  const W step = static_cast<W>(gridDim.x) * groups_per_block;
+  const U* src = static_cast<const U*>(a.src);
+  U* dst = static_cast<U*>(a.dst);
+  for (W item = static_cast<W>(blockIdx.x) * groups_per_block + (threadIdx.x >> a.g_log); item < n_items;
+       item += step) {
+    const W row = item / static_cast<W>(a.chunks_per_row);
+    const W chunk = item - row * static_cast<W>(a.chunks_per_row);
+    W o = 0, k = row;
+    if (a.n_rows != a.K) {
+      o = row / static_cast<W>(a.K);
+      k = row - o * static_cast<W>(a.K);
+    }
+    int64_t idx = load_index<I>(a.index, static_cast<int64_t>(k) * a.index_stride);
+    if (a.wrap_negative && idx < 0) idx += a.S;
+    const bool ok = idx >= 0 && idx < a.S;
+    if (!ok) {
+      if (lane == 0) atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+      idx = 0;
+    }
+    const U* s = src + static_cast<int64_t>(o) * a.src_outer_stride + idx * a.src_row_stride;
+    U* d = dst + static_cast<int64_t>(row) * a.upr;
+    const int64_t c0 = static_cast<int64_t>(chunk) * (G * 4) + lane;
+    U v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t c = c0 + u * G;
+      if (c < a.upr) v[u] = s[c];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t c = c0 + u * G;
+      if (c < a.upr) d[c] = v[u];
+    }
+  }
+}
+
+// Widest copy unit (bytes) for rows of `row_bytes` at the given addresses/strides.
+inline int pick_unit(int64_t row_bytes, const void* p0, const void* p1, int64_t stride_bytes0,
+                     int64_t stride_bytes1, int64_t min_unit) {
+  for (int64_t w = 16; w > min_unit; w >>= 1) {
+    if (row_bytes % w == 0 && reinterpret_cast<uintptr_t>(p0) % w == 0 &&
+        reinterpret_cast<uintptr_t>(p1) % w == 0 && stride_bytes0 % w == 0 && stride_bytes1 % w == 0)
+      return static_cast<int>(w);
+  }
+  return static_cast<int>(min_unit);
+}
+
+template <typename I>
+b200Status launch_row_gather_i(RowGatherArgs a, int unit, cudaStream_t s) {
+  int g_log = 0;
+  while ((1 << g_log) < 32 && (int64_t(1) << g_log) * 4 < a.upr) ++g_log;
+  a.g_log = g_log;
+  a.chunks_per_row = (a.upr + (int64_t(4) << g_log) - 1) / (int64_t(4) << g_log);
+  const int64_t items = a.n_rows * a.chunks_per_row;
+  if (items == 0) return B200_OK;
+  const int64_t groups_per_block = kThreads >> g_log;
+  int64_t need = (items + groups_per_block - 1) / groups_per_block;
+  const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 16;
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  const bool small = items < (int64_t(1) << 31) && a.n_rows < (int64_t(1) << 31);
+#define B200_RG(U)                                                                     \
+  do {                                                                                 \
+    if (small) row_gather_kernel<U, I, uint32_t><<<grid, kThreads, 0, s>>>(a);         \
+    else row_gather_kernel<U, I, int64_t><<<grid, kThreads, 0, s>>>(a);                \
+  } while (0)
+  switch (unit) {
+    case 16: B200_RG(int4); break;
+    case 8: B200_RG(uint64_t); break;
+    case 4: B200_RG(uint32_t); break;
+    case 2: B200_RG(uint16_t); break;
+    default: B200_RG(uint8_t); break;
+  }
+#undef B200_RG
+  return check_launch("row gather");
+}
+
+b200Status launch_row_gather(const RowGatherArgs& a, int unit, int32_t index_dtype, cudaStream_t s) {
+  if (index_dtype == B200_I64) return launch_row_gather_i<int64_t>(a, unit, s);
+  if (index_dtype == B200_I32) return launch_row_gather_i<int32_t>(a, unit, s);
+  return fail(B200_BAD_PARAM, "index dtype must be int32 or int64");
+}
+
+// ---------------------------------------------------------------- gather ----
+// Fast form: index/out (rows, cols) contiguous, dim = last, self rows aligned
+// with index rows. Four outputs per thread.
+template <typename U, typename I>
+__global__ void __launch_bounds__(kThreads)
+gather_lastdim_kernel(U* __restrict__ out, const U* __restrict__ self, const I* __restrict__ index,
+                      int64_t n4, int64_t cols, int64_t self_cols) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; v < n4; v += stride) {
+    const int64_t e = v * 4;
+    const int64_t row = e / cols;
+    alignas(16) I idx[4];
+    if constexpr (sizeof(I) == 8) {
+      int4 a = __ldcs(reinterpret_cast<const int4*>(index + e));
+      int4 b = __ldcs(reinterpret_cast<const int4*>(index + e) + 1);
+      *reinterpret_cast<int4*>(&idx[0]) = a;
+      *reinterpret_cast<int4*>(&idx[2]) = b;
+    } else {
+      int4 a = __ldcs(reinterpret_cast<const int4*>(index + e));
+      *reinterpret_cast<int4*>(&idx[0]) = a;
+    }
+    const U* srow = self + row * self_cols;
+    struct alignas(sizeof(U) * 4 > 16 ? 16 : sizeof(U) * 4) Pack { U v[4]; } r;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int64_t j = idx[k];
+      if (j < 0 || j >= self_cols) {
+        atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+        j = 0;
+      }
+      r.v[k] = srow[j];
+    }
+    *reinterpret_cast<Pack*>(out + e) = r;
+  }
+}
+
+template <typename U, typename I>
+__global__ void __launch_bounds__(kThreads)
+gather_generic_kernel(U* out, const U* self, const I* index, int64_t n, StridedIndexer<3> ix,
+                      int64_t self_dim_stride, int64_t self_dim_size) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    int64_t off[3];
+    ix.offsets(i, off);
+    int64_t j = index[off[1]];
+    if (j < 0 || j >= self_dim_size) {
+      atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+      j = 0;
+    }
+    out[off[0]] = self[off[2] + j * self_dim_stride];
+  }
+}
+
+// ------------------------------------------------------- advanced index ----
+constexpr int kMaxIndexTensors = 4;
+struct IndexArgs {
+  const void* idx[kMaxIndexTensors];
+  int64_t sizes[kMaxIndexTensors];
+  int64_t strides[kMaxIndexTensors];
+  int n;
+};
+
+template <typename U, typename I>
+__global__ void __launch_bounds__(kThreads)
+index_generic_kernel(U* out, const U* src, int64_t n, StridedIndexer<2 + kMaxIndexTensors> ix, IndexArgs a) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    int64_t off[2 + kMaxIndexTensors];
+    ix.offsets(i, off);
+    int64_t so = off[1];
+#pragma unroll
+    for (int k = 0; k < kMaxIndexTensors; ++k) {
+      if (k < a.n) {
+        int64_t j = static_cast<const I*>(a.idx[k])[off[2 + k]];
+        if (j < 0) j += a.sizes[k];
+        if (j < 0 || j >= a.sizes[k]) {
+          atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+          j = 0;
+        }
+        so += j * a.strides[k];
+      }
+    }
+    out[off[0]] = src[so];
+  }
+}
+
+// ------------------------------------------------ stable LSD radix sort ----
+// Sorts n (key, value) uint32 pairs by key, 8 bits per pass, stable.
+// Tile = 256 threads x 16 items; warp w owns items [w*512, (w+1)*512) of the
+// tile, read 32 consecutive items per round.
+constexpr int kSortThreads = 256;
+constexpr int kItemsPerThread = 16;
+constexpr int kTile = kSortThreads * kItemsPerThread;  // 4096
+constexpr int kWarps = kSortThreads / 32;
+constexpr int kMaxPasses = 4;
+
+// hist[pass][digit * nblocks + block]
+__global__ void __launch_bounds__(kSortThreads)
+radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int passes, int nblocks,
+                  uint32_t* __restrict__ hist) {
+  __shared__ uint32_t sh[kMaxPasses][256];
+  for (int i = threadIdx.x; i < kMaxPasses * 256; i += kSortThreads) (&sh[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+#pragma unroll 4
+  for (int r = 0; r < kItemsPerThread; ++r) {
+    const int64_t i = base + r * kSortThreads + threadIdx.x;
+    if (i < n) {
+      const uint32_t k = keys[i];
+      for (int p = 0; p < passes; ++p) atomicAdd(&sh[p][(k >> (8 * p)) & 255u], 1u);
+    }
+  }
+  __syncthreads();
+  for (int p = 0; p < passes; ++p)
+    hist[(static_cast<int64_t>(p) * 256 + threadIdx.x) * nblocks + blockIdx.x] = sh[p][threadIdx.x];
+}
+
+// One block per pass: exclusive scan of 256*nblocks counters, in place.
+__global__ void __launch_bounds__(1024)
+radix_scan_kernel(uint32_t* hist, int64_t per_pass) {
+  __shared__ uint32_t warp_tot[32];
+  __shared__ uint32_t carry_s;
+  uint32_t* h = hist + static_cast<int64_t>(blockIdx.x) * per_pass;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t base = 0; base < per_pass; base += 1024) {
+    const int64_t i = base + threadIdx.x;
+    const uint32_t v = i < per_pass ? h[i] : 0u;
+    uint32_t inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      uint32_t w = warp_tot[lane];
+      uint32_t winc = w;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        uint32_t t = __shfl_up_sync(0xffffffffu, winc, o);
+        if (lane >= o) winc += t;
+      }
+      warp_tot[lane] = winc - w;  // exclusive
+    }
+    __syncthreads();
+    const uint32_t carry = carry_s;
+    if (i < per_pass) h[i] = carry + warp_tot[warp] + inc - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = carry + warp_tot[31] + inc;
+    __syncthreads();
+  }
+}
+
+// vals_in == nullptr: the value of item i is i (first pass).
+__global__ void __launch_bounds__(kSortThreads)
+radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
+                     int pass, int nblocks, const uint32_t* __restrict__ hist_scanned) {
+  __shared__ uint32_t warp_count[kWarps][256];  // sweep 1: counts; then exclusive base per warp
+  __shared__ uint32_t digit_base[256];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kWarps * 256; i += kSortThreads) (&warp_count[0][0])[i] = 0;
+  digit_base[threadIdx.x] =
+      hist_scanned[(static_cast<int64_t>(pass) * 256 + threadIdx.x) * nblocks + blockIdx.x];
+  __syncthreads();
+
+  const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItemsPerThread * 32);
+  uint32_t key[kItemsPerThread];
+  const int shift = 8 * pass;
+#pragma unroll
+  for (int r = 0; r < kItemsPerThread; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    key[r] = i < n ? keys_in[i] : 0xffffffffu;
+  }
+  // sweep 1: per-warp digit counts
+#pragma unroll
+  for (int r = 0; r < kItemsPerThread; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    const bool live = i < n;
+    const uint32_t d = live ? ((key[r] >> shift) & 255u) : (256u + lane);
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    if (live && lane == (__ffs(peers) - 1)) warp_count[warp][d] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  // exclusive prefix over warps, per digit (thread = digit)
+  {
+    uint32_t run = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      uint32_t c = warp_count[w][threadIdx.x];
+      warp_count[w][threadIdx.x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  // sweep 2: stable ranks and scatter
+#pragma unroll
+  for (int r = 0; r < kItemsPerThread; ++r) {
+    const int64_t i = wbase + r * 32 + lane;
+    const bool live = i < n;
+    const uint32_t d = live ? ((key[r] >> shift) & 255u) : (256u + lane);
+    const uint32_t peers = __match_any_sync(0xffffffffu, d);
+    uint32_t pos = 0;
+    if (live) {
+      const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+      pos = digit_base[d] + warp_count[warp][d] + before;
+    }
+    __syncwarp();
+    if (live && lane == (__ffs(peers) - 1)) warp_count[warp][d] += __popc(peers);
+    __syncwarp();
+    if (live) {
+      keys_out[pos] = key[r];
+      vals_out[pos] = vals_in ? vals_in[i] : static_cast<uint32_t>(i);
+    }
+  }
+}
+
+// seg_start[d] = first sorted position whose key is >= d, for d in [0, n_dst].
+__global__ void __launch_bounds__(kThreads)
+segment_bounds_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n, int64_t n_dst,
+                      uint32_t* __restrict__ seg_start) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p <= n; p += stride) {
+    const int64_t lo = p == 0 ? 0 : static_cast<int64_t>(sorted_keys[p - 1]) + 1;
+    int64_t hi = p == n ? n_dst : static_cast<int64_t>(sorted_keys[p]);
+    if (hi > n_dst) hi = n_dst;
+    for (int64_t d = lo; d <= hi; ++d) seg_start[d] = static_cast<uint32_t>(p);
+  }
+}
+
+// keys for the row form: the destination row of every source row.
+template <typename I>
+__global__ void __launch_bounds__(kThreads)
+row_keys_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, int64_t n_dst,
+                int wrap_negative, uint32_t* __restrict__ keys) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    int64_t d = index[i * index_stride];
+    if (wrap_negative && d < 0) d += n_dst;
+    if (d < 0 || d >= n_dst) {
+      atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+      d = n_dst;  // parked after every real destination, never consumed
+    }
+    keys[i] = static_cast<uint32_t>(d);
+  }
+}
+
+// keys for the element form: linear offset of the destination element.
+template <typename I>
+__global__ void __launch_bounds__(kThreads)
+element_keys_kernel(const I* __restrict__ index, int64_t n, StridedIndexer<2> ix, int64_t dim_stride,
+                    int64_t dim_size, int64_t out_numel, uint32_t* __restrict__ keys) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    int64_t off[2];  // [0]: index element, [1]: destination offset without the dim term
+    ix.offsets(i, off);
+    int64_t j = index[off[0]];
+    int64_t dst = off[1] + j * dim_stride;
+    if (j < 0 || j >= dim_size) {
+      atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+      dst = out_numel;
+    }
+    keys[i] = static_cast<uint32_t>(dst);
+  }
+}
+
+// Sequential add in the element type: 16-bit floats round after every add, as
+// the CPU's `self[idx] += src` does.
+template <typename T> __device__ __forceinline__ T seq_add(T a, T b) { return a + b; }
+template <> __device__ __forceinline__ float seq_add<float>(float a, float b) { return __fadd_rn(a, b); }
+template <> __device__ __forceinline__ bf16_t seq_add<bf16_t>(bf16_t a, bf16_t b) {
+  return bf16_t{f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a.bits), bf16_bits_to_f32(b.bits)))};
+}
+template <> __device__ __forceinline__ f16_t seq_add<f16_t>(f16_t a, f16_t b) {
+  return f16_t{f32_to_f16_bits(__fadd_rn(f16_bits_to_f32(a.bits), f16_bits_to_f32(b.bits)))};
+}
+
+// One warp per (destination row, 64-vector column chunk).
+// MODE 0: out = self + sum(sources in order); MODE 1: out = last source (or self).
+template <typename T, int V, int MODE>
+__global__ void __launch_bounds__(kThreads)
+segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __restrict__ src,
+                    const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
+                    int64_t n_dst, int64_t inner /* elements per row */, int64_t chunks_per_row) {
+  struct alignas(sizeof(T) * V) VecT { T v[V]; };
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+  const int64_t vpr = inner / V;
+  const int64_t n_items = n_dst * chunks_per_row;
+  for (int64_t item = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+       item < n_items; item += warps) {
+    const int64_t r = item / chunks_per_row;
+    const int64_t chunk = item - r * chunks_per_row;
+    const int64_t c0 = chunk * 64 + lane, c1 = c0 + 32;
+    const bool h0 = c0 < vpr, h1 = c1 < vpr;
+    const uint32_t beg = seg_start[r], end = seg_start[r + 1];
+    const VecT* self_row = reinterpret_cast<const VecT*>(self + r * inner);
+    VecT* out_row = reinterpret_cast<VecT*>(out + r * inner);
+    if (MODE == 1) {
+      const VecT* from = beg < end ? reinterpret_cast<const VecT*>(src + static_cast<int64_t>(sorted_src[end - 1]) * inner)
+                                   : self_row;
+      if (from != out_row) {
+        if (h0) out_row[c0] = from[c0];
+        if (h1) out_row[c1] = from[c1];
+      }
+      continue;
+    }
+    VecT a0, a1;
+    if (h0) a0 = self_row[c0];
+    if (h1) a1 = self_row[c1];
+    for (uint32_t p = beg; p < end; p += 32) {
+      const uint32_t cnt = min(32u, end - p);
+      const uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0u;
+      uint32_t k = 0;
+      for (; k + 4 <= cnt; k += 4) {  // four source rows in flight, added in order
+        VecT b0[4], b1[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(__shfl_sync(0xffffffffu, mine, k + u)) * inner);
+          if (h0) b0[u] = srow[c0];
+          if (h1) b1[u] = srow[c1];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            if (h0) a0.v[e] = seq_add(a0.v[e], b0[u].v[e]);
+            if (h1) a1.v[e] = seq_add(a1.v[e], b1[u].v[e]);
+          }
+        }
+      }
+      for (; k < cnt; ++k) {
+        const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(__shfl_sync(0xffffffffu, mine, k)) * inner);
+        VecT b0, b1;
+        if (h0) b0 = srow[c0];
+        if (h1) b1 = srow[c1];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          if (h0) a0.v[e] = seq_add(a0.v[e], b0.v[e]);
+          if (h1) a1.v[e] = seq_add(a1.v[e], b1.v[e]);
+        }
+      }
+    }
+    if (h0) out_row[c0] = a0;
+    if (h1) out_row[c1] = a1;
+  }
+}
+
+// Element form: the thread that holds the head of a segment walks it.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+segment_elements_kernel(T* out, const T* self, const T* __restrict__ src,
+                        const uint32_t* __restrict__ sorted_keys, const uint32_t* __restrict__ sorted_src,
+                        int64_t n, int64_t out_numel) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n; p += stride) {
+    const uint32_t key = sorted_keys[p];
+    if (key >= out_numel) continue;
+    if (p > 0 && sorted_keys[p - 1] == key) continue;
+    T acc = self[key];
+    for (int64_t q = p; q < n && sorted_keys[q] == key; ++q) acc = seq_add(acc, src[sorted_src[q]]);
+    out[key] = acc;
+  }
+}
+
+struct SortPlan {
+  int64_t n;
+  int passes;
+  int nblocks;
+  size_t keys_bytes, hist_bytes, seg_bytes, total;
+};
+
+inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range] */, int64_t n_dst_rows) {
+  SortPlan p{};
+  p.n = n;
+  int bits = 1;
+  while ((int64_t(1) << bits) <= key_range && bits < 32) ++bits;
+  p.passes = (bits + 7) / 8;
+  p.nblocks = static_cast<int>((n + kTile - 1) / kTile);
+  if (p.nblocks < 1) p.nblocks = 1;
+  p.keys_bytes = align256(static_cast<size_t>(n) * 4);
+  p.hist_bytes = align256(static_cast<size_t>(p.passes) * 256 * p.nblocks * 4);
+  p.seg_bytes = n_dst_rows >= 0 ? align256(static_cast<size_t>(n_dst_rows + 2) * 4) : 0;
+  p.total = 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
+  return p;
+}
+
+// Runs the sort. On return *sorted_keys / *sorted_vals point into the workspace.
+b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a,
+                    uint32_t* vals_b, uint32_t* hist, cudaStream_t s, uint32_t** sorted_keys,
+                    uint32_t** sorted_vals) {
+  radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(keys_a, p.n, p.passes, p.nblocks, hist);
+  radix_scan_kernel<<<p.passes, 1024, 0, s>>>(hist, static_cast<int64_t>(256) * p.nblocks);
+  uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
+  for (int pass = 0; pass < p.passes; ++pass) {
+    radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist);
+    uint32_t* t = kin; kin = kout; kout = t;
+    vin = vout;
+    vout = vother;
+    vother = vin;
+  }
+  *sorted_keys = kin;
+  *sorted_vals = vin;
+  return check_launch("radix sort");
+}
+
+// Decides whether scatter_add(dim) can use the row form, and its geometry.
+struct ScatterGeom {
+  bool row_form;
+  int64_t n_src, n_dst, inner;
+  int64_t index_stride;
+};
+
+bool row_form_geometry(const b200Tensor* self, int64_t dim, const b200Tensor* index,
+                       const b200Tensor* src, ScatterGeom* g) {
+  if (dim != 0 || self->ndim < 1 || index->ndim != self->ndim || src->ndim != self->ndim) return false;
+  if (!is_contiguous(self) || !is_contiguous(src)) return false;
+  int64_t inner = 1;
+  for (int d = 1; d < self->ndim; ++d) {
+    if (index->sizes[d] != src->sizes[d] || index->sizes[d] != self->sizes[d]) return false;
+    if (index->sizes[d] != 1 && index->strides[d] != 0) return false;  // must be broadcast along the row
+    inner *= self->sizes[d];
+  }
+  if (index->sizes[0] != src->sizes[0]) return false;
+  g->row_form = true;
+  g->n_src = index->sizes[0];
+  g->n_dst = self->sizes[0];
+  g->inner = inner;
+  g->index_stride = index->sizes[0] > 1 ? index->strides[0] : 1;
+  return true;
+}
+
+template <typename T, int MODE>
+b200Status launch_segment_rows(void* out, const void* self, const void* src, const uint32_t* sorted_src,
+                               const uint32_t* seg_start, int64_t n_dst, int64_t inner, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = inner % V == 0 && aligned16(out) && aligned16(self) && aligned16(src);
+  const int64_t vpr = vec ? inner / V : inner;
+  const int64_t cpr = (vpr + 63) / 64;
+  const int64_t items = n_dst * cpr;
+  if (items == 0) return B200_OK;
+  int64_t need = (items + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 8;
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  if (vec)
+    segment_rows_kernel<T, V, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
+                                                             sorted_src, seg_start, n_dst, inner, cpr);
+  else
+    segment_rows_kernel<T, 1, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
+                                                             sorted_src, seg_start, n_dst, inner, cpr);
+  return check_launch("segment rows");
+}
+
+// Row-form pipeline shared by scatter_add and index_put.
+template <typename T>
+b200Status scatter_rows(void* out, const void* self, const void* src, const b200Tensor* index,
+                        int64_t index_stride, int64_t n_src, int64_t n_dst, int64_t inner, int mode,
+                        int wrap_negative, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+  B200_REQUIRE(n_src < (int64_t(1) << 31) && n_dst < (int64_t(1) << 31) - 2, B200_NOT_SUPPORTED,
+               "scatter: more than 2^31 rows");
+  if (n_src == 0) {
+    if (out != self) {
+      cudaError_t e = cudaMemcpyAsync(out, self, static_cast<size_t>(n_dst) * inner * sizeof(T),
+                                      cudaMemcpyDeviceToDevice, s);
+      if (e != cudaSuccess) return fail(B200_LAUNCH_FAILED, "scatter: %s", cudaGetErrorString(e));
+    }
+    return B200_OK;
+  }
+  SortPlan p = make_plan(n_src, n_dst, n_dst);
+  B200_REQUIRE(workspace && workspace_bytes >= p.total, B200_WORKSPACE_TOO_SMALL,
+               "scatter: workspace of %zu bytes needed, %zu given", p.total, workspace_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, B200_BAD_PARAM,
+               "scatter: workspace must be 256-byte aligned");
+  char* w = static_cast<char*>(workspace);
+  uint32_t* keys_a = reinterpret_cast<uint32_t*>(w);
+  uint32_t* keys_b = reinterpret_cast<uint32_t*>(w + p.keys_bytes);
+  uint32_t* vals_a = reinterpret_cast<uint32_t*>(w + 2 * p.keys_bytes);
+  uint32_t* vals_b = reinterpret_cast<uint32_t*>(w + 3 * p.keys_bytes);
+  uint32_t* hist = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes);
+  uint32_t* seg = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes + p.hist_bytes);
+  const int kgrid = grid_for(n_src, kThreads, 8);
+  if (index->dtype == B200_I64)
+    row_keys_kernel<int64_t><<<kgrid, kThreads, 0, s>>>((const int64_t*)index->data, index_stride, n_src, n_dst, wrap_negative, keys_a);
+  else
+    row_keys_kernel<int32_t><<<kgrid, kThreads, 0, s>>>((const int32_t*)index->data, index_stride, n_src, n_dst, wrap_negative, keys_a);
+  uint32_t *sk, *sv;
+  b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
+  if (st != B200_OK) return st;
+  segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
+  if (mode == 0) return launch_segment_rows<T, 0>(out, self, src, sv, seg, n_dst, inner, s);
+  return launch_segment_rows<T, 1>(out, self, src, sv, seg, n_dst, inner, s);
+}
+
+#define B200_DISPATCH_SCATTER(DT, T, ...)                                        \
+  switch (DT) {                                                                  \
+    case B200_F32: { using T = float; __VA_ARGS__; break; }                      \
+    case B200_BF16: { using T = ::b200::bf16_t; __VA_ARGS__; break; }            \
+    case B200_F16: { using T = ::b200::f16_t; __VA_ARGS__; break; }              \
+    case B200_F64: { using T = double; __VA_ARGS__; break; }                     \
+    case B200_I64: { using T = int64_t; __VA_ARGS__; break; }                    \
+    case B200_I32: { using T = int32_t; __VA_ARGS__; break; }                    \
+    default: return ::b200::fail(B200_NOT_SUPPORTED, "%s: dtype %d not supported", __func__, (int)(DT)); \
+  }
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+// Reads and clears the device error word (bit 0: an index was out of range and
+// was replaced by 0 / skipped). Synchronises the device; meant for debug modes.
+b200Status b200_device_error_fetch(uint32_t* flags) {
+  B200_REQUIRE(flags, B200_BAD_PARAM, "b200_device_error_fetch: null");
+  unsigned int v = 0, zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_error_word, sizeof(v));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_device_error_word, &zero, sizeof(zero));
+  if (e != cudaSuccess) return fail(B200_LAUNCH_FAILED, "b200_device_error_fetch: %s", cudaGetErrorString(e));
+  *flags = v;
+  return B200_OK;
+}
+
+b200Status b200_index_select(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                             const b200Tensor* index, b200Stream stream) {
+  B200_REQUIRE(valid(out) && valid(self) && valid(index), B200_BAD_PARAM, "b200_index_select: invalid tensor view");
+  B200_REQUIRE(index->ndim <= 1, B200_BAD_PARAM, "b200_index_select: index must be 1-D");
+  B200_REQUIRE(out->dtype == self->dtype, B200_BAD_PARAM, "b200_index_select: dtype mismatch");
+  B200_REQUIRE(is_contiguous(self) && is_contiguous(out), B200_NOT_SUPPORTED,
+               "b200_index_select: self/out must be contiguous");
+  const int64_t K = numel(index);
+  int64_t outer = 1, S = 1, inner = 1;
+  if (self->ndim == 0) {
+    B200_REQUIRE(dim == 0, B200_BAD_PARAM, "b200_index_select: dim");
+  } else {
+    B200_REQUIRE(dim >= 0 && dim < self->ndim, B200_BAD_PARAM, "b200_index_select: dim %lld", (long long)dim);
+    for (int d = 0; d < dim; ++d) outer *= self->sizes[d];
+    S = self->sizes[dim];
+    for (int d = (int)dim + 1; d < self->ndim; ++d) inner *= self->sizes[d];
+  }
+  B200_REQUIRE(numel(out) == outer * K * inner, B200_BAD_PARAM, "b200_index_select: out shape");
+  if (numel(out) == 0) return B200_OK;
+  const int64_t es = static_cast<int64_t>(dtype_size(self->dtype));
+  const int unit = pick_unit(inner * es, self->data, out->data, 0, 0, es);
+  RowGatherArgs a{};
+  a.src = self->data; a.dst = out->data; a.index = index->data;
+  a.index_stride = index->ndim == 1 && K > 1 ? index->strides[0] : 1;
+  a.n_rows = outer * K; a.K = K; a.S = S;
+  a.upr = inner * es / unit;
+  a.src_outer_stride = S * a.upr; a.src_row_stride = a.upr;
+  a.wrap_negative = 0;
+  return launch_row_gather(a, unit, index->dtype, static_cast<cudaStream_t>(stream));
+}
+
+b200Status b200_gather(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                       const b200Tensor* index, b200Stream stream) {
+  B200_REQUIRE(valid(out) && valid(self) && valid(index), B200_BAD_PARAM, "b200_gather: invalid tensor view");
+  B200_REQUIRE(same_shape(out, index), B200_BAD_PARAM, "b200_gather: out and index shapes differ");
+  B200_REQUIRE(out->dtype == self->dtype, B200_BAD_PARAM, "b200_gather: dtype mismatch");
+  B200_REQUIRE(index->dtype == B200_I64 || index->dtype == B200_I32, B200_BAD_PARAM, "b200_gather: index dtype");
+  const int64_t n = numel(out);
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(self->ndim == index->ndim || (self->ndim == 0 && index->ndim <= 1) ||
+               (index->ndim == 0 && self->ndim <= 1), B200_BAD_PARAM, "b200_gather: rank mismatch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t es = static_cast<int64_t>(dtype_size(self->dtype));
+  const int nd = index->ndim;
+  int64_t dim_size = self->ndim ? self->sizes[dim] : 1, dim_stride = self->ndim ? self->strides[dim] : 0;
+  if (nd > 0) B200_REQUIRE(dim >= 0 && dim < nd, B200_BAD_PARAM, "b200_gather: dim");
+
+  bool fast = nd >= 1 && self->ndim == nd && dim == nd - 1 && is_contiguous(out) && is_contiguous(index) &&
+              is_contiguous(self) && index->sizes[nd - 1] % 4 == 0 && (es == 4 || es == 2 || es == 8) &&
+              aligned16(index->data) && aligned16(out->data);
+  for (int d = 0; fast && d < nd - 1; ++d) fast = self->sizes[d] == index->sizes[d];
+  if (fast) {
+    const int64_t cols = index->sizes[nd - 1], n4 = n / 4;
+    const int grid = grid_for(n4, kThreads, 8);
+#define B200_GL(U)                                                                                     \
+  do {                                                                                                 \
+    if (index->dtype == B200_I64)                                                                      \
+      gather_lastdim_kernel<U, int64_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data, \
+                                                                  (const int64_t*)index->data, n4, cols, dim_size); \
+    else                                                                                               \
+      gather_lastdim_kernel<U, int32_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data, \
+                                                                  (const int32_t*)index->data, n4, cols, dim_size); \
+  } while (0)
+    if (es == 4) B200_GL(uint32_t); else if (es == 2) B200_GL(uint16_t); else B200_GL(uint64_t);
+#undef B200_GL
+    return check_launch("b200_gather");
+  }
+  // generic: walk index's shape; self contributes every stride except dim's
+  b200Tensor self_view = *index;
+  self_view.data = self->data;
+  self_view.dtype = self->dtype;
+  for (int d = 0; d < nd; ++d) self_view.strides[d] = (d == dim || self->ndim == 0) ? 0 : self->strides[d];
+  const b200Tensor* ts[3] = {out, index, &self_view};
+  auto ix = make_indexer<3>(ts);
+  const int grid = grid_for(n, kThreads, 8);
+#define B200_GG(U)                                                                                      \
+  do {                                                                                                  \
+    if (index->dtype == B200_I64)                                                                       \
+      gather_generic_kernel<U, int64_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data,  \
+                                                                  (const int64_t*)index->data, n, ix, dim_stride, dim_size); \
+    else                                                                                                \
+      gather_generic_kernel<U, int32_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data,  \
+                                                                  (const int32_t*)index->data, n, ix, dim_stride, dim_size); \
+  } while (0)
+  B200_DISPATCH_BYTES(es, U, B200_GG(U));
+#undef B200_GG
+  return check_launch("b200_gather");
+}
+
+b200Status b200_index(const b200Tensor* out, const b200Tensor* src, const b200Tensor* const* indices,
+                      int32_t n_indices, const int64_t* indexed_sizes, const int64_t* indexed_strides,
+                      b200Stream stream) {
+  B200_REQUIRE(valid(out) && valid(src), B200_BAD_PARAM, "b200_index: invalid tensor view");
+  B200_REQUIRE(n_indices >= 1 && n_indices <= kMaxIndexTensors && indices && indexed_sizes && indexed_strides,
+               B200_NOT_SUPPORTED, "b200_index: between 1 and %d index tensors supported", kMaxIndexTensors);
+  B200_REQUIRE(same_shape(out, src) && out->dtype == src->dtype, B200_BAD_PARAM,
+               "b200_index: src must be restrided to out's shape");
+  for (int k = 0; k < n_indices; ++k) {
+    B200_REQUIRE(indices[k] && valid(indices[k]) && same_shape(out, indices[k]), B200_BAD_PARAM,
+                 "b200_index: index %d must be broadcast to out's shape", k);
+    B200_REQUIRE(indices[k]->dtype == indices[0]->dtype &&
+                 (indices[k]->dtype == B200_I32 || indices[k]->dtype == B200_I64), B200_BAD_PARAM,
+                 "b200_index: indices must all be int32 or all int64");
+  }
+  const int64_t n = numel(out);
+  if (n == 0) return B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t es = static_cast<int64_t>(dtype_size(out->dtype));
+
+  // Row form: one index tensor, constant along a contiguous trailing block that
+  // src and out both walk contiguously.
+  if (n_indices == 1 && is_contiguous(out)) {
+    const b200Tensor* idx = indices[0];
+    int split = out->ndim;  // trailing dims [split, ndim) form the row
+    int64_t row = 1;
+    while (split > 0) {
+      const int d = split - 1;
+      if (out->sizes[d] != 1 && (idx->strides[d] != 0 || src->strides[d] != row)) break;
+      row *= out->sizes[d];
+      --split;
+    }
+    bool lead_ok = row > 1;
+    int64_t K = 1, expect = 1;
+    for (int d = split - 1; d >= 0 && lead_ok; --d) {  // leading dims: index contiguous, src stride 0
+      if (out->sizes[d] == 1) continue;
+      if (src->strides[d] != 0 || idx->strides[d] != expect) lead_ok = false;
+      expect *= out->sizes[d];
+      K *= out->sizes[d];
+    }
+    if (lead_ok) {
+      const int unit = pick_unit(row * es, src->data, out->data, indexed_strides[0] * es, 0, es);
+      RowGatherArgs a{};
+      a.src = src->data; a.dst = out->data; a.index = idx->data;
+      a.index_stride = 1;
+      a.n_rows = K; a.K = K; a.S = indexed_sizes[0];
+      a.upr = row * es / unit;
+      a.src_outer_stride = 0; a.src_row_stride = indexed_strides[0] * es / unit;
+      a.wrap_negative = 1;
+      return launch_row_gather(a, unit, idx->dtype, s);
+    }
+  }
+
+  b200Tensor dummy = *out;
+  dummy.data = nullptr;
+  for (int d = 0; d < dummy.ndim; ++d) dummy.strides[d] = 0;
+  const b200Tensor* ts[2 + kMaxIndexTensors];
+  ts[0] = out; ts[1] = src;
+  IndexArgs ia{};
+  ia.n = n_indices;
+  for (int k = 0; k < kMaxIndexTensors; ++k) {
+    ts[2 + k] = k < n_indices ? indices[k] : &dummy;
+    ia.idx[k] = k < n_indices ? indices[k]->data : nullptr;
+    ia.sizes[k] = k < n_indices ? indexed_sizes[k] : 1;
+    ia.strides[k] = k < n_indices ? indexed_strides[k] : 0;
+  }
+  auto ix = make_indexer<2 + kMaxIndexTensors>(ts);
+  const int grid = grid_for(n, kThreads, 8);
+#define B200_IG(U)                                                                                   \
+  do {                                                                                               \
+    if (indices[0]->dtype == B200_I64)                                                               \
+      index_generic_kernel<U, int64_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)src->data, n, ix, ia); \
+    else                                                                                             \
+      index_generic_kernel<U, int32_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)src->data, n, ix, ia); \
+  } while (0)
+  B200_DISPATCH_BYTES(es, U, B200_IG(U));
+#undef B200_IG
+  return check_launch("b200_index");
+}
+
+size_t b200_scatter_add_workspace_size(const b200Tensor* self, int64_t dim, const b200Tensor* index,
+                                       const b200Tensor* src) {
+  if (!self || !index || !src || !valid(self) || !valid(index) || !valid(src)) return 0;
+  ScatterGeom g{};
+  if (row_form_geometry(self, dim, index, src, &g)) return make_plan(g.n_src, g.n_dst, g.n_dst).total;
+  return make_plan(numel(index), numel(self), -1).total;
+}
+
+b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                            const b200Tensor* index, const b200Tensor* src, void* workspace,
+                            size_t workspace_bytes, b200Stream stream) {
+  B200_REQUIRE(valid(out) && valid(self) && valid(index) && valid(src), B200_BAD_PARAM,
+               "b200_scatter_add: invalid tensor view");
+  B200_REQUIRE(same_shape(out, self) && out->dtype == self->dtype && src->dtype == self->dtype, B200_BAD_PARAM,
+               "b200_scatter_add: out/self/src must agree in dtype, out and self in shape");
+  B200_REQUIRE(index->dtype == B200_I64 || index->dtype == B200_I32, B200_BAD_PARAM, "b200_scatter_add: index dtype");
+  B200_REQUIRE(is_contiguous(out) && is_contiguous(self), B200_NOT_SUPPORTED,
+               "b200_scatter_add: out/self must be contiguous");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (numel(self) == 0) return B200_OK;
+  B200_REQUIRE(self->ndim == 0 || (dim >= 0 && dim < self->ndim), B200_BAD_PARAM, "b200_scatter_add: dim");
+
+  ScatterGeom g{};
+  if (row_form_geometry(self, dim, index, src, &g)) {
+    B200_DISPATCH_SCATTER(self->dtype, T, {
+      return scatter_rows<T>(out->data, self->data, src->data, index, g.index_stride, g.n_src, g.n_dst,
+                             g.inner, 0, 0, workspace, workspace_bytes, s);
+    });
+  }
+
+  // element form
+  if (out->data != self->data) {
+    b200Status st = b200_copy(out, self, stream);
+    if (st != B200_OK) return st;
+  }
+  const int64_t n = numel(index);
+  if (n == 0) return B200_OK;
+  B200_REQUIRE(index->ndim == self->ndim && src->ndim == self->ndim, B200_BAD_PARAM,
+               "b200_scatter_add: index/src rank must equal self's");
+  B200_REQUIRE(same_shape(index, src) && is_contiguous(src), B200_NOT_SUPPORTED,
+               "b200_scatter_add: element form needs src contiguous and shaped like index");
+  const int64_t out_numel = numel(self);
+  B200_REQUIRE(n < (int64_t(1) << 31) && out_numel < (int64_t(1) << 32) - 1, B200_NOT_SUPPORTED,
+               "b200_scatter_add: element form limited to 2^31 sources / 2^32 destinations");
+  SortPlan p = make_plan(n, out_numel, -1);
+  B200_REQUIRE(workspace && workspace_bytes >= p.total, B200_WORKSPACE_TOO_SMALL,
+               "b200_scatter_add: workspace of %zu bytes needed, %zu given", p.total, workspace_bytes);
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, B200_BAD_PARAM,
+               "b200_scatter_add: workspace must be 256-byte aligned");
+  char* w = static_cast<char*>(workspace);
+  uint32_t* keys_a = reinterpret_cast<uint32_t*>(w);
+  uint32_t* keys_b = reinterpret_cast<uint32_t*>(w + p.keys_bytes);
+  uint32_t* vals_a = reinterpret_cast<uint32_t*>(w + 2 * p.keys_bytes);
+  uint32_t* vals_b = reinterpret_cast<uint32_t*>(w + 3 * p.keys_bytes);
+  uint32_t* hist = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes);
+
+  b200Tensor dst_view = *index;  // destination offsets without the dim term
+  dst_view.data = out->data;
+  for (int d = 0; d < index->ndim; ++d) dst_view.strides[d] = d == dim ? 0 : self->strides[d];
+  b200Tensor idx_c = *index;
+  // The sort's tie order is the row-major order of index's shape, so walk it
+  // uncollapsed-by-value: make_indexer only merges dims, it keeps the order.
+  const b200Tensor* ts[2] = {&idx_c, &dst_view};
+  auto ix = make_indexer<2>(ts);
+  const int64_t dim_stride = self->ndim ? self->strides[dim] : 0;
+  const int64_t dim_size = self->ndim ? self->sizes[dim] : 1;
+  const int kgrid = grid_for(n, kThreads, 8);
+  if (index->dtype == B200_I64)
+    element_keys_kernel<int64_t><<<kgrid, kThreads, 0, s>>>((const int64_t*)index->data, n, ix, dim_stride, dim_size, out_numel, keys_a);
+  else
+    element_keys_kernel<int32_t><<<kgrid, kThreads, 0, s>>>((const int32_t*)index->data, n, ix, dim_stride, dim_size, out_numel, keys_a);
+  uint32_t *sk, *sv;
+  b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
+  if (st != B200_OK) return st;
+  B200_DISPATCH_SCATTER(self->dtype, T, {
+    segment_elements_kernel<T><<<kgrid, kThreads, 0, s>>>((T*)out->data, (const T*)self->data,
+                                                         (const T*)src->data, sk, sv, n, out_numel);
+  });
+  return check_launch("b200_scatter_add");
+}
+
+size_t b200_index_put_workspace_size(const b200Tensor* self, const b200Tensor* index,
+                                     const b200Tensor* values) {
+  if (!self || !index || !values || !valid(self) || !valid(index) || self->ndim < 1) return 0;
+  return make_plan(numel(index), self->sizes[0], self->sizes[0]).total;
+}
+
+b200Status b200_index_put(const b200Tensor* self, const b200Tensor* index, const b200Tensor* values,
+                          int32_t accumulate, void* workspace, size_t workspace_bytes, b200Stream stream) {
+  B200_REQUIRE(valid(self) && valid(index) && valid(values), B200_BAD_PARAM, "b200_index_put: invalid tensor view");
+  B200_REQUIRE(self->ndim >= 1 && index->ndim <= 1, B200_BAD_PARAM,
+               "b200_index_put: self must have rank >= 1 and index rank 1");
+  B200_REQUIRE(index->dtype == B200_I64 || index->dtype == B200_I32, B200_BAD_PARAM, "b200_index_put: index dtype");
+  B200_REQUIRE(values->dtype == self->dtype, B200_BAD_PARAM, "b200_index_put: dtype mismatch");
+  B200_REQUIRE(is_contiguous(self) && is_contiguous(values), B200_NOT_SUPPORTED,
+               "b200_index_put: self/values must be contiguous");
+  const int64_t n_src = numel(index), n_dst = self->sizes[0];
+  int64_t inner = 1;
+  for (int d = 1; d < self->ndim; ++d) inner *= self->sizes[d];
+  B200_REQUIRE(numel(values) == n_src * inner, B200_BAD_PARAM,
+               "b200_index_put: values must hold index.numel() rows of self's row shape");
+  if (n_src == 0 || numel(self) == 0) return B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t istride = index->ndim == 1 && n_src > 1 ? index->strides[0] : 1;
+  // Negative indices wrap once, as ATen's index_put does.
+  B200_DISPATCH_SCATTER(self->dtype, T, {
+    return scatter_rows<T>(self->data, self->data, values->data, index, istride, n_src, n_dst, inner,
+                           accumulate ? 0 : 1, 1, workspace, workspace_bytes, s);
+  });
+  return B200_OK;
+}
+
+}  // extern "C"

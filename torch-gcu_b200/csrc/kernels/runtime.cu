@@ -1,0 +1,56 @@
+// Library-level queries and the small amount of process state the kernel
+// library keeps: a thread-local error message and the per-device SM count.
+#include "common.cuh"
+
+#include <atomic>
+
+namespace b200 {
+
+char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+int sm_count_current_device() {
+  // Immutable once written; racing writers store the same value.
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+    n = 148;
+  cache[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+const char* b200_last_error(void) { return b200::error_buffer(); }
+
+const char* b200_version(void) { return "b200ops 0.1 (sm_100a)"; }
+
+int b200_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int b200_sm_count(int device) {
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return n;
+}
+
+size_t b200_dtype_size(int32_t dtype) { return b200::dtype_size(dtype); }
+
+}  // extern "C"
