@@ -80,9 +80,24 @@ def build_ops(dev, scale=1.0, want_gpu=True):
         import b200ops as ops_mod
     R = lambda n: max(8, int(n * scale))  # noqa: E731
     out = []
+    import ctypes
+    cd, ci64, ci32, csz = ctypes.c_double, ctypes.c_int64, ctypes.c_int32, ctypes.c_size_t
+
+    def i64s(v):
+        return (ctypes.c_int64 * len(v))(*v)
+
+    def B(name, *a):
+        # pre-marshalled C-ABI call (GPU arm only; the CPU arm never invokes it)
+        return ops_mod.bind(name, *a) if want_gpu else None
+
+    def wsa(w_):
+        return ops_mod.ws_args(w_) if want_gpu else (None, None)
 
     def to_dev(d):
-        return {k: v.to(dev) for k, v in d.items() if torch.is_tensor(v)} if want_gpu else {}
+        if not want_gpu:
+            import collections
+            return collections.defaultdict(lambda: None)
+        return {k: v.to(dev) for k, v in d.items() if torch.is_tensor(v)}
 
     # ---- config 1: fp32 op sweep ------------------------------------------
     sw = workloads.op_sweep(rows=R(4096))
@@ -99,23 +114,23 @@ def build_ops(dev, scale=1.0, want_gpu=True):
     else:
         o32 = o16 = a16 = osum = mean = rstd = None
     a16_cpu = a.to(torch.bfloat16)
-    out.append(Op("add", 3 * nbytes(a), 1, g, lambda: ops_mod.add(o32, g["a"], g["b"], 1.0),
+    out.append(Op("add", 3 * nbytes(a), 1, g, B("add", o32, g["a"], g["b"], cd(1.0)),
                   lambda: cpu.add(a, b), dict(a=a, b=b), lambda: o32))
-    out.append(Op("mul", 3 * nbytes(a), 1, g, lambda: ops_mod.mul(o32, g["a"], g["b"]),
+    out.append(Op("mul", 3 * nbytes(a), 1, g, B("mul", o32, g["a"], g["b"]),
                   lambda: cpu.mul(a, b), dict(a=a, b=b), lambda: o32))
-    out.append(Op("silu", 2 * nbytes(a), 1, g, lambda: ops_mod.silu(o32, g["a"]),
+    out.append(Op("silu", 2 * nbytes(a), 1, g, B("silu", o32, g["a"]),
                   lambda: cpu.silu(a), dict(a=a), lambda: o32))
-    out.append(Op("cast_f32_bf16", nbytes(a) + nbytes(a) // 2, 1, g, lambda: ops_mod.copy(o16, g["a"]),
+    out.append(Op("cast_f32_bf16", nbytes(a) + nbytes(a) // 2, 1, g, B("copy", o16, g["a"]),
                   lambda: cpu.cast(a, torch.bfloat16), dict(a=a), lambda: o16))
-    g16 = dict(a=a16)
-    out.append(Op("cast_bf16_f32", nbytes(a) + nbytes(a) // 2, 1, g16, lambda: ops_mod.copy(o32, g16["a"]),
+    g16 = dict(a=a16)  # a16 is None on the CPU arm
+    out.append(Op("cast_bf16_f32", nbytes(a) + nbytes(a) // 2, 1, g16, B("copy", o32, g16["a"]),
                   lambda: cpu.cast(a16_cpu, torch.float32), dict(a=a16_cpu), lambda: o32))
-    out.append(Op("sum_lastdim", nbytes(a) + rows * 4, 1, g, lambda: ops_mod.sum(osum, g["a"], [1]),
+    out.append(Op("sum_lastdim", nbytes(a) + rows * 4, 1, g, B("sum", osum, g["a"], i64s([1]), ci32(1), ci32(0), None, csz(0)),
                   lambda: cpu.sum_dim(a, [-1]), dict(a=a), lambda: osum))
-    out.append(Op("softmax_lastdim", 2 * nbytes(a), 1, g, lambda: ops_mod.softmax(o32, g["a"], 1),
+    out.append(Op("softmax_lastdim", 2 * nbytes(a), 1, g, B("softmax", o32, g["a"], ci64(1)),
                   lambda: cpu.softmax(a, -1), dict(a=a), lambda: o32))
     out.append(Op("layer_norm", 2 * nbytes(a) + 2 * cols * 4 + 2 * rows * 4, 1, g,
-                  lambda: ops_mod.native_layer_norm(o32, mean, rstd, g["a"], rows, cols, g["w"], g["bias"], 1e-5),
+                  B("native_layer_norm", o32, mean, rstd, g["a"], ci64(rows), ci64(cols), g["w"], g["bias"], cd(1e-5)),
                   lambda: cpu.native_layer_norm(a, (cols,), w, bias, 1e-5)[0], dict(a=a, w=w, bias=bias),
                   lambda: o32))
 
@@ -139,23 +154,25 @@ def build_ops(dev, scale=1.0, want_gpu=True):
                          device=dev)
         ip_self = torch.zeros(n_dst, scols, device=dev)
 
+        _ip = B("index_put", ip_self, gi["srows"], gi["svals"], ci32(1), *wsa(ws))
+
         def run_index_put():
             ip_self.zero_()  # restore the accumulator (a memset node, counted as a launch)
-            ops_mod.index_put(ip_self, gi["srows"], gi["svals"], True, ws)
+            _ip()
     else:
         emb_out = sel_out = gat_out = sc_out = sidx = ws = ip_self = run_index_put = None
     out.append(Op("embedding", 2 * ids.numel() * hidden * 2 + nbytes(ids), 1, gi,
-                  lambda: ops_mod.index_select(emb_out, gi["table"], 0, gi["ids"]),
+                  B("index_select", emb_out, gi["table"], ci64(0), gi["ids"]),
                   lambda: cpu.embedding(table, ids), dict(table=table, ids=ids.reshape(-1)), lambda: emb_out))
     out.append(Op("index_select", 2 * sel.numel() * hidden * 2 + nbytes(sel), 1, gi,
-                  lambda: ops_mod.index_select(sel_out, gi["table"], 0, gi["sel"]),
+                  B("index_select", sel_out, gi["table"], ci64(0), gi["sel"]),
                   lambda: cpu.index_select(table, 0, sel), dict(table=table, sel=sel), lambda: sel_out))
     out.append(Op("gather", nbytes(gidx) + 2 * nbytes(gsrc), 1, gi,
-                  lambda: ops_mod.gather(gat_out, gi["gsrc"], 1, gi["gidx"]),
+                  B("gather", gat_out, gi["gsrc"], ci64(1), gi["gidx"]),
                   lambda: cpu.gather(gsrc, 1, gidx), dict(gsrc=gsrc, gidx=gidx), lambda: gat_out))
     sc_bytes = nbytes(svals) + nbytes(srows) + 2 * n_dst * scols * 4
     out.append(Op("scatter_add", sc_bytes, 7, gi,
-                  lambda: ops_mod.scatter_add(sc_out, gi["zeros"], 0, sidx, gi["svals"], ws),
+                  B("scatter_add", sc_out, gi["zeros"], ci64(0), sidx, gi["svals"], *wsa(ws)),
                   lambda: cpu.scatter_add(zeros_cpu, 0, srows[:, None].expand(-1, scols), svals),
                   dict(svals=svals, srows=srows, zeros=zeros_cpu), lambda: sc_out))
     out.append(Op("index_put_accumulate", sc_bytes, 8, gi, run_index_put,
@@ -172,18 +189,21 @@ def build_ops(dev, scale=1.0, want_gpu=True):
         qo, ko = torch.empty_like(gf["q"]), torch.empty_like(gf["k"])
         so = torch.empty_like(gf["gate"])
 
+        _rq = B("rope", qo, gf["q"], gf["cos"], gf["sin"], None)
+        _rk = B("rope", ko, gf["k"], gf["cos"], gf["sin"], None)
+
         def run_rope():
-            ops_mod.rope(qo, gf["q"], gf["cos"], gf["sin"])
-            ops_mod.rope(ko, gf["k"], gf["cos"], gf["sin"])
+            _rq()
+            _rk()
     else:
         y = hres = qo = ko = so = run_rope = None
     out.append(Op("rms_norm_residual", 4 * nbytes(x) + nbytes(wn), 1, gf,
-                  lambda: ops_mod.rms_norm_residual(y, hres, gf["x"], gf["res"], gf["wn"], 1e-6),
+                  B("rms_norm_residual", y, hres, gf["x"], gf["res"], gf["wn"], cd(1e-6)),
                   lambda: cpu.rms_norm_residual(x, res, wn, 1e-6)[0], dict(x=x, res=res, wn=wn), lambda: y))
     out.append(Op("rope_q_k", 2 * (nbytes(q) + nbytes(k)), 2, gf, run_rope,
                   lambda: (cpu.rope(q, cos, sin), cpu.rope(k, cos, sin))[0], dict(q=q, k=k, cos=cos, sin=sin),
                   lambda: qo))
-    out.append(Op("swiglu", 3 * nbytes(gate), 1, gf, lambda: ops_mod.swiglu(so, gf["gate"], gf["up"]),
+    out.append(Op("swiglu", 3 * nbytes(gate), 1, gf, B("swiglu", so, gf["gate"], gf["up"]),
                   lambda: cpu.swiglu(gate, up), dict(gate=gate, up=up), lambda: so))
     return out
 

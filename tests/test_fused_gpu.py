@@ -11,8 +11,10 @@ BF = torch.bfloat16
 
 
 def bf16_close(a, b):
-    # reference tolerance for bf16 is 1e-3; one bf16 ulp (2^-8 relative) is allowed
-    close(a, b, 2 ** -8, 1e-3)
+    # reference tolerance for bf16 is 1e-3 absolute/relative; one bf16 ulp is up to
+    # 2^-7 relative at the bottom of a binade, which a different summation order
+    # of the row statistics can flip, so allow exactly one ulp
+    close(a, b, 2 ** -7, 1e-3)
 
 
 @pytest.mark.parametrize("rows,n", [(9, 64), (33, 4096), (4, 8192), (3, 1000), (2, 24576), (5, 40), (0, 64)])

@@ -121,6 +121,41 @@ def _i64_array(values):
     return arr
 
 
+def bind(name, *args):
+    """Pre-marshals one call: tensors become b200Tensor views once, ctypes scalars
+    pass through, None is NULL. Returns a callable that enqueues the call on the
+    given (or current) stream; the stream is appended as the last argument. The
+    caller keeps the tensors alive. Used where per-call Python overhead matters."""
+    import torch
+    fn = getattr(lib(), "b200_" + name)
+    keep, conv = [], []
+    for a in args:
+        if torch.is_tensor(a):
+            v = view(a)
+            keep.append(v)
+            conv.append(ctypes.byref(v))
+        elif isinstance(a, (list, tuple)) and a and torch.is_tensor(a[0]):
+            views = [view(t) for t in a]
+            arr = (ctypes.POINTER(Tensor) * len(views))(*[ctypes.pointer(v) for v in views])
+            keep.extend([views, arr])
+            conv.append(arr)
+        else:
+            conv.append(a)
+
+    def call(stream=None, _fn=fn, _conv=tuple(conv), _keep=keep):
+        st = _fn(*_conv, _stream(stream))
+        if st != OK:
+            check(st)
+    return call
+
+
+def ws_args(workspace):
+    """(pointer, size) ctypes pair for a workspace tensor (or NULL, 0)."""
+    if workspace is None:
+        return None, ctypes.c_size_t(0)
+    return ctypes.c_void_p(workspace.data_ptr()), ctypes.c_size_t(workspace.numel() * workspace.element_size())
+
+
 # ---- thin wrappers: one per entry point; tensors are torch tensors ----------
 
 def add(out, a, b, alpha=1.0, stream=None):

@@ -8,8 +8,8 @@
 // CPU adds the sources of one destination in ascending source order starting
 // from self's value. The kernels therefore invert the index first: a stable
 // least-significant-digit radix sort of (destination, source) pairs (8-bit
-// digits, hand-written: per-tile digit histograms, one scan, stable per-tile
-// ranking with warp match), then one warp per destination row walks its
+// digits, hand-written: per pass a per-tile digit histogram, one scan and a
+// stable per-tile ranking with warp match), then one warp per destination row walks its
 // segment in order, several source rows in flight, adding sequentially. No
 // floating-point atomics anywhere, so results are run-to-run identical.
 #include "common.cuh"
@@ -235,33 +235,32 @@ constexpr int kTile = kSortThreads * kItemsPerThread;  // 4096
 constexpr int kWarps = kSortThreads / 32;
 constexpr int kMaxPasses = 4;
 
-// hist[pass][digit * nblocks + block]
+// hist[digit * nblocks + block]: digit counts of every tile, for one pass. The
+// histogram is taken again before each pass because the previous pass has
+// permuted which keys sit in which tile.
 __global__ void __launch_bounds__(kSortThreads)
-radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int passes, int nblocks,
+radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int pass, int nblocks,
                   uint32_t* __restrict__ hist) {
-  __shared__ uint32_t sh[kMaxPasses][256];
-  for (int i = threadIdx.x; i < kMaxPasses * 256; i += kSortThreads) (&sh[0][0])[i] = 0;
+  __shared__ uint32_t sh[256];
+  sh[threadIdx.x] = 0;
   __syncthreads();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+  const int shift = 8 * pass;
 #pragma unroll 4
   for (int r = 0; r < kItemsPerThread; ++r) {
     const int64_t i = base + r * kSortThreads + threadIdx.x;
-    if (i < n) {
-      const uint32_t k = keys[i];
-      for (int p = 0; p < passes; ++p) atomicAdd(&sh[p][(k >> (8 * p)) & 255u], 1u);
-    }
+    if (i < n) atomicAdd(&sh[(keys[i] >> shift) & 255u], 1u);
   }
   __syncthreads();
-  for (int p = 0; p < passes; ++p)
-    hist[(static_cast<int64_t>(p) * 256 + threadIdx.x) * nblocks + blockIdx.x] = sh[p][threadIdx.x];
+  hist[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x] = sh[threadIdx.x];
 }
 
-// One block per pass: exclusive scan of 256*nblocks counters, in place.
+// One block: exclusive scan of 256*nblocks counters, in place.
 __global__ void __launch_bounds__(1024)
 radix_scan_kernel(uint32_t* hist, int64_t per_pass) {
   __shared__ uint32_t warp_tot[32];
   __shared__ uint32_t carry_s;
-  uint32_t* h = hist + static_cast<int64_t>(blockIdx.x) * per_pass;
+  uint32_t* h = hist;
   if (threadIdx.x == 0) carry_s = 0;
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -304,8 +303,7 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
   __shared__ uint32_t digit_base[256];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kWarps * 256; i += kSortThreads) (&warp_count[0][0])[i] = 0;
-  digit_base[threadIdx.x] =
-      hist_scanned[(static_cast<int64_t>(pass) * 256 + threadIdx.x) * nblocks + blockIdx.x];
+  digit_base[threadIdx.x] = hist_scanned[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x];
   __syncthreads();
 
   const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItemsPerThread * 32);
@@ -426,7 +424,8 @@ template <typename T, int V, int MODE>
 __global__ void __launch_bounds__(kThreads)
 segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __restrict__ src,
                     const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
-                    int64_t n_dst, int64_t inner /* elements per row */, int64_t chunks_per_row) {
+                    int64_t n_dst, int64_t n_src, int64_t inner /* elements per row */,
+                    int64_t chunks_per_row) {
   struct alignas(sizeof(T) * V) VecT { T v[V]; };
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
@@ -438,12 +437,14 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
     const int64_t chunk = item - r * chunks_per_row;
     const int64_t c0 = chunk * 64 + lane, c1 = c0 + 32;
     const bool h0 = c0 < vpr, h1 = c1 < vpr;
-    const uint32_t beg = seg_start[r], end = seg_start[r + 1];
+    uint32_t beg = seg_start[r], end = seg_start[r + 1];
+    if (end > n_src || beg > end) beg = end = 0;  // never walk outside the sorted list
     const VecT* self_row = reinterpret_cast<const VecT*>(self + r * inner);
     VecT* out_row = reinterpret_cast<VecT*>(out + r * inner);
     if (MODE == 1) {
-      const VecT* from = beg < end ? reinterpret_cast<const VecT*>(src + static_cast<int64_t>(sorted_src[end - 1]) * inner)
-                                   : self_row;
+      uint32_t last = beg < end ? sorted_src[end - 1] : 0u;
+      if (last >= n_src) last = 0;
+      const VecT* from = beg < end ? reinterpret_cast<const VecT*>(src + static_cast<int64_t>(last) * inner) : self_row;
       if (from != out_row) {
         if (h0) out_row[c0] = from[c0];
         if (h1) out_row[c1] = from[c1];
@@ -455,7 +456,8 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
     if (h1) a1 = self_row[c1];
     for (uint32_t p = beg; p < end; p += 32) {
       const uint32_t cnt = min(32u, end - p);
-      const uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0u;
+      uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0u;
+      if (mine >= n_src) mine = 0;  // keeps every read inside src
       uint32_t k = 0;
       for (; k + 4 <= cnt; k += 4) {  // four source rows in flight, added in order
         VecT b0[4], b1[4];
@@ -503,7 +505,10 @@ segment_elements_kernel(T* out, const T* self, const T* __restrict__ src,
     if (key >= out_numel) continue;
     if (p > 0 && sorted_keys[p - 1] == key) continue;
     T acc = self[key];
-    for (int64_t q = p; q < n && sorted_keys[q] == key; ++q) acc = seq_add(acc, src[sorted_src[q]]);
+    for (int64_t q = p; q < n && sorted_keys[q] == key; ++q) {
+      const uint32_t sidx = sorted_src[q];
+      if (sidx < n) acc = seq_add(acc, src[sidx]);
+    }
     out[key] = acc;
   }
 }
@@ -526,7 +531,7 @@ SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range] */, in
   p.nblocks = static_cast<int>((n + kTile - 1) / kTile);
   if (p.nblocks < 1) p.nblocks = 1;
   p.keys_bytes = align256(static_cast<size_t>(n) * 4);
-  p.hist_bytes = align256(static_cast<size_t>(p.passes) * 256 * p.nblocks * 4);
+  p.hist_bytes = align256(static_cast<size_t>(256) * p.nblocks * 4);
   p.seg_bytes = n_dst_rows >= 0 ? align256(static_cast<size_t>(n_dst_rows + 2) * 4) : 0;
   p.total = 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
   return p;
@@ -536,10 +541,10 @@ SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range] */, in
 b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a,
                     uint32_t* vals_b, uint32_t* hist, cudaStream_t s, uint32_t** sorted_keys,
                     uint32_t** sorted_vals) {
-  radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(keys_a, p.n, p.passes, p.nblocks, hist);
-  radix_scan_kernel<<<p.passes, 1024, 0, s>>>(hist, static_cast<int64_t>(256) * p.nblocks);
   uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
   for (int pass = 0; pass < p.passes; ++pass) {
+    radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, p.n, pass, p.nblocks, hist);
+    radix_scan_kernel<<<1, 1024, 0, s>>>(hist, static_cast<int64_t>(256) * p.nblocks);
     radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist);
     uint32_t* t = kin; kin = kout; kout = t;
     vin = vout;
@@ -579,7 +584,8 @@ bool row_form_geometry(const b200Tensor* self, int64_t dim, const b200Tensor* in
 
 template <typename T, int MODE>
 b200Status launch_segment_rows(void* out, const void* self, const void* src, const uint32_t* sorted_src,
-                               const uint32_t* seg_start, int64_t n_dst, int64_t inner, cudaStream_t s) {
+                               const uint32_t* seg_start, int64_t n_dst, int64_t n_src, int64_t inner,
+                               cudaStream_t s) {
   constexpr int V = 16 / sizeof(T);
   const bool vec = inner % V == 0 && aligned16(out) && aligned16(self) && aligned16(src);
   const int64_t vpr = vec ? inner / V : inner;
@@ -591,10 +597,10 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
   const int grid = static_cast<int>(need < cap ? need : cap);
   if (vec)
     segment_rows_kernel<T, V, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
-                                                             sorted_src, seg_start, n_dst, inner, cpr);
+                                                             sorted_src, seg_start, n_dst, n_src, inner, cpr);
   else
     segment_rows_kernel<T, 1, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
-                                                             sorted_src, seg_start, n_dst, inner, cpr);
+                                                             sorted_src, seg_start, n_dst, n_src, inner, cpr);
   return check_launch("segment rows");
 }
 
@@ -634,8 +640,8 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
   if (st != B200_OK) return st;
   segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
-  if (mode == 0) return launch_segment_rows<T, 0>(out, self, src, sv, seg, n_dst, inner, s);
-  return launch_segment_rows<T, 1>(out, self, src, sv, seg, n_dst, inner, s);
+  if (mode == 0) return launch_segment_rows<T, 0>(out, self, src, sv, seg, n_dst, n_src, inner, s);
+  return launch_segment_rows<T, 1>(out, self, src, sv, seg, n_dst, n_src, inner, s);
 }
 
 #define B200_DISPATCH_SCATTER(DT, T, ...)                                        \
