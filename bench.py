@@ -42,6 +42,7 @@ METRIC = "op_hbm_gbs"
 UNIT = "GB/s"
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
+NSETS = 4
 
 
 def measured_peaks():
@@ -70,15 +71,23 @@ def nbytes(*ts):
     return sum(t.numel() * t.element_size() for t in ts)
 
 
-def build_ops(dev, scale=1.0, want_gpu=True):
-    """The operator list of one pass. scale < 1 shrinks the row counts (used by
-    the bounded CPU sample only; the GPU arm always runs scale 1)."""
+def make_data(scale=1.0):
+    """Seeded CPU tensors of configs 1-3. scale < 1 shrinks the row counts (used
+    by the bounded CPU sample only; the GPU arm always runs scale 1)."""
     import workloads
+    R = lambda n: max(8, int(n * scale))  # noqa: E731
+    return dict(sw=workloads.op_sweep(rows=R(4096)),
+                ix=workloads.index_ops(vocab=R(128256), seq=R(2048), n_select=R(65536), gather_rows=R(8192),
+                                       scatter_src=R(262144), scatter_dst=R(65536)),
+                fu=workloads.fused_ops(tokens=R(16384), seq=R(2048)))
+
+
+def build_ops(dev, data, want_gpu=True):
+    """The operator list of one pass over `data`, with its own device buffers."""
     from oracle import aten_cpu as cpu  # used ONLY inside the cpu_run closures (CPU baseline leg)
     ops_mod = None
     if want_gpu:
         import b200ops as ops_mod
-    R = lambda n: max(8, int(n * scale))  # noqa: E731
     out = []
     import ctypes
     cd, ci64, ci32, csz = ctypes.c_double, ctypes.c_int64, ctypes.c_int32, ctypes.c_size_t
@@ -86,9 +95,9 @@ def build_ops(dev, scale=1.0, want_gpu=True):
     def i64s(v):
         return (ctypes.c_int64 * len(v))(*v)
 
-    def B(name, *a):
+    def B(name, *a, keep=()):
         # pre-marshalled C-ABI call (GPU arm only; the CPU arm never invokes it)
-        return ops_mod.bind(name, *a) if want_gpu else None
+        return ops_mod.bind(name, *a, keep=keep) if want_gpu else None
 
     def wsa(w_):
         return ops_mod.ws_args(w_) if want_gpu else (None, None)
@@ -100,7 +109,7 @@ def build_ops(dev, scale=1.0, want_gpu=True):
         return {k: v.to(dev) for k, v in d.items() if torch.is_tensor(v)}
 
     # ---- config 1: fp32 op sweep ------------------------------------------
-    sw = workloads.op_sweep(rows=R(4096))
+    sw = data["sw"]
     a, b, w, bias = sw["a"], sw["b"], sw["weight"], sw["bias"]
     rows, cols = a.shape
     g = to_dev(dict(a=a, b=b, w=w, bias=bias))
@@ -135,8 +144,7 @@ def build_ops(dev, scale=1.0, want_gpu=True):
                   lambda: o32))
 
     # ---- config 2: index ops ------------------------------------------------
-    ix = workloads.index_ops(vocab=R(128256), seq=R(2048), n_select=R(65536), gather_rows=R(8192),
-                             scatter_src=R(262144), scatter_dst=R(65536))
+    ix = data["ix"]
     table, ids, sel = ix["table"], ix["ids"], ix["select_idx"]
     gsrc, gidx, svals, srows = ix["gather_src"], ix["gather_idx"], ix["scatter_vals"], ix["scatter_rows"]
     n_dst, scols = ix["scatter_dst"], ix["scatter_cols"]
@@ -154,7 +162,7 @@ def build_ops(dev, scale=1.0, want_gpu=True):
                          device=dev)
         ip_self = torch.zeros(n_dst, scols, device=dev)
 
-        _ip = B("index_put", ip_self, gi["srows"], gi["svals"], ci32(1), *wsa(ws))
+        _ip = B("index_put", ip_self, gi["srows"], gi["svals"], ci32(1), *wsa(ws), keep=(ws,))
 
         def run_index_put():
             ip_self.zero_()  # restore the accumulator (a memset node, counted as a launch)
@@ -172,7 +180,7 @@ def build_ops(dev, scale=1.0, want_gpu=True):
                   lambda: cpu.gather(gsrc, 1, gidx), dict(gsrc=gsrc, gidx=gidx), lambda: gat_out))
     sc_bytes = nbytes(svals) + nbytes(srows) + 2 * n_dst * scols * 4
     out.append(Op("scatter_add", sc_bytes, 7, gi,
-                  B("scatter_add", sc_out, gi["zeros"], ci64(0), sidx, gi["svals"], *wsa(ws)),
+                  B("scatter_add", sc_out, gi["zeros"], ci64(0), sidx, gi["svals"], *wsa(ws), keep=(ws,)),
                   lambda: cpu.scatter_add(zeros_cpu, 0, srows[:, None].expand(-1, scols), svals),
                   dict(svals=svals, srows=srows, zeros=zeros_cpu), lambda: sc_out))
     out.append(Op("index_put_accumulate", sc_bytes, 8, gi, run_index_put,
@@ -180,7 +188,7 @@ def build_ops(dev, scale=1.0, want_gpu=True):
                   dict(svals=svals, srows=srows), lambda: ip_self))
 
     # ---- config 3: fused bf16 inference ops ---------------------------------
-    fu = workloads.fused_ops(tokens=R(16384), seq=R(2048))
+    fu = data["fu"]
     x, res, wn, q, k, gate, up, cos, sin = (fu[n] for n in ("x", "res", "weight", "q", "k", "gate", "up", "cos", "sin"))
     gf = to_dev(dict(x=x, res=res, wn=wn, q=q, k=k, gate=gate, up=up, cos=cos, sin=sin))
     if want_gpu:
@@ -273,8 +281,16 @@ def run_gpu(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    ops = build_ops(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+    data = make_data()
+    # NSETS independent copies of every operator's buffers, used round-robin, so
+    # that a launch never finds its operands in the 126 MB L2: between two uses
+    # of one buffer set the other sets stream >= 3x its footprint (>= 200 MB
+    # even for the smallest operator).
+    sets = [build_ops(dev, data) for _ in range(NSETS)]
+    if args.only:
+        keep = set(args.only.split(","))
+        sets = [[op for op in st if op.name in keep] for st in sets]
+    ops = sets[0]
     stream = torch.cuda.current_stream()
 
     def barrier():
@@ -283,11 +299,12 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     def timed_pass(per_op_ms):
-        for i, op in enumerate(ops):
-            flush.zero_()  # evict L2 (outside the events)
+        # one event pair around NSETS back-to-back launches of the same operator
+        for i in range(len(ops)):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record(stream)
-            op.gpu_run()
+            for st in sets:
+                st[i].gpu_run()
             e.record(stream)
             per_op_ms[i].append((s, e))
 
@@ -299,7 +316,7 @@ def run_gpu(args):
         for _ in range(args.steps):
             timed_pass(events)
         barrier()
-    op_ms = [sum(s.elapsed_time(e) for s, e in ev) / args.steps for ev in events]
+    op_ms = [sum(s.elapsed_time(e) for s, e in ev) / args.steps / NSETS for ev in events]
     pass_ms = sum(op_ms)
     pass_bytes = sum(op.bytes for op in ops)
 
@@ -347,12 +364,12 @@ def run_gpu(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32+bf16", "data": "synthetic",
             "config": {"workload": "configs[0..2]: fp32 (4096,4096) op sweep + index ops on bf16 (128256,4096) "
                                    "table + fused bf16 RMSNorm/RoPE/SwiGLU, one pass of all 16 operators",
-                       "l2": "256 MiB flush before every operator launch", "parallelism": "replicas" if world > 1 else "1gpu",
+                       "l2": "%d rotating buffer sets per operator (no launch re-reads data resident in L2)" % NSETS, "parallelism": "replicas" if world > 1 else "1gpu",
                        "peak": "%s copy bandwidth %.1f GB/s" % (peak_kind, peak)},
             "clocks": clocks.summary(),
             "e2e": {"value": round(world * pass_bytes / e2e_ms_max / 1e6, 2), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps * sum(op.launches for op in ops),
+            "gpu_launches": args.steps * NSETS * sum(op.launches for op in ops),
             "roofline": {"bound": "hbm", "kernel": ops[top].name, "achieved": round(top_gbs, 1), "peak": peak,
                          "unit": "GB/s", "frac": round(top_gbs / peak, 3), "traffic": None,
                          "peak_kind": peak_kind},
@@ -377,7 +394,7 @@ def cpu_pass(ops):
 def cpu_baseline(pass_bytes_full, sample_steps=1, scale=0.25):
     """CPU ATen over a bounded sample: the same 16 operators on `scale` of the rows."""
     torch.set_num_threads(os.cpu_count() or 1)
-    ops = build_ops(None, scale=scale, want_gpu=False)
+    ops = build_ops(None, make_data(scale), want_gpu=False)
     sample_bytes = sum(op.bytes for op in ops)
     cpu_pass(ops)  # warm-up
     dt = min(cpu_pass(ops) for _ in range(max(1, sample_steps)))
@@ -393,7 +410,7 @@ def run_reference(args):
         return
     torch.set_num_threads(os.cpu_count() or 1)
     scale = 0.25
-    ops = build_ops(None, scale=scale, want_gpu=False)
+    ops = build_ops(None, make_data(scale), want_gpu=False)
     sample_bytes = sum(op.bytes for op in ops)
     for _ in range(max(1, min(args.warmup, 2))):
         cpu_pass(ops)
@@ -421,6 +438,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default="", help="comma-separated operator names (profiling aid)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

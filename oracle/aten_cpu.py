@@ -49,7 +49,9 @@ def mean_dim(a, dims, keepdim=False):
 
 
 def softmax(a, dim, half_to_float=False):
-    return torch.ops.aten._softmax(a, dim, half_to_float)
+    if half_to_float:  # the CPU kernel has no half_to_float form: widen first, same result
+        return torch.ops.aten._softmax(a.float(), dim, False)
+    return torch.ops.aten._softmax(a, dim, False)
 
 
 def native_layer_norm(a, normalized_shape, weight, bias, eps):

@@ -103,17 +103,27 @@ def test_scatter_add_all_sources_one_row(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float64, torch.int64])
-def test_scatter_add_other_dtypes(ops, dtype):
+@pytest.mark.parametrize("inner", [24, 8])
+def test_scatter_add_other_dtypes(ops, dtype, inner):
+    """bf16: CPU scatter_add sums in fp32 and rounds once (index_put, checked
+    below, rounds after every add); both must match bit for bit."""
     g = torch.Generator().manual_seed(26)
-    src = (torch.randn(3000, 24, generator=g) * 4).to(dtype)
+    src = (torch.randn(3000, inner, generator=g) * 4).to(dtype)
     rows = torch.randint(0, 100, (3000,), generator=g)
-    base = (torch.randn(100, 24, generator=g) * 4).to(dtype)
-    ref = aten_cpu.scatter_add(base, 0, rows[:, None].expand(-1, 24), src)
-    idx = dev(rows)[:, None].expand(-1, 24)
+    base = (torch.randn(100, inner, generator=g) * 4).to(dtype)
+    ref = aten_cpu.scatter_add(base, 0, rows[:, None].expand(-1, inner), src)
+    idx = dev(rows)[:, None].expand(-1, inner)
     ws = _ws(ops.scatter_add_workspace_size(dev(base), 0, idx, dev(src)))
     out = torch.empty_like(dev(base))
     ops.scatter_add(out, dev(base), 0, idx, dev(src), ws)
     exact(out, ref)
+    full = torch.randint(0, 100, (3000, inner), generator=g)
+    ws = _ws(ops.scatter_add_workspace_size(dev(base), 0, dev(full), dev(src)))
+    ops.scatter_add(out, dev(base), 0, dev(full), dev(src), ws)
+    exact(out, aten_cpu.scatter_add(base, 0, full, src))
+    tgt = dev(base).clone()
+    ops.index_put(tgt, dev(rows), dev(src), True, _ws(ops.index_put_workspace_size(tgt, dev(rows), dev(src))))
+    exact(tgt, aten_cpu.index_put(base, [rows], src, True))
 
 
 @pytest.mark.parametrize("dim", [0, 1])

@@ -121,23 +121,25 @@ def _i64_array(values):
     return arr
 
 
-def bind(name, *args):
+def bind(name, *args, keep=()):
     """Pre-marshals one call: tensors become b200Tensor views once, ctypes scalars
     pass through, None is NULL. Returns a callable that enqueues the call on the
     given (or current) stream; the stream is appended as the last argument. The
-    caller keeps the tensors alive. Used where per-call Python overhead matters."""
+    returned callable holds a reference to every tensor argument; memory passed
+    as a raw pointer (a workspace) must be kept alive by the caller, e.g. through
+    `keep=`. Used where per-call Python overhead matters."""
     import torch
     fn = getattr(lib(), "b200_" + name)
-    keep, conv = [], []
+    keep, conv = list(keep), []
     for a in args:
         if torch.is_tensor(a):
             v = view(a)
-            keep.append(v)
+            keep.extend([v, a])
             conv.append(ctypes.byref(v))
         elif isinstance(a, (list, tuple)) and a and torch.is_tensor(a[0]):
             views = [view(t) for t in a]
             arr = (ctypes.POINTER(Tensor) * len(views))(*[ctypes.pointer(v) for v in views])
-            keep.extend([views, arr])
+            keep.extend([views, arr, list(a)])
             conv.append(arr)
         else:
             conv.append(a)

@@ -9,6 +9,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <string.h>
 
 #include "b200ops.h"
 
@@ -159,6 +160,24 @@ __device__ __forceinline__ uint16_t f32_to_f16_bits(float f) {
 }
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {
   return __half2float(__ushort_as_half(h));
+}
+
+// Host-side rounding of a scalar operand to the tensor's element type: ATen
+// converts `alpha` and wrapped-number operands to the op's dtype before use.
+inline double round_scalar_to_dtype(double v, int32_t dtype) {
+  if (dtype == B200_F32) return static_cast<double>(static_cast<float>(v));
+  if (dtype == B200_BF16) {
+    float f = static_cast<float>(v);
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return v;
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    u &= 0xFFFF0000u;
+    memcpy(&f, &u, 4);
+    return f;
+  }
+  if (dtype == B200_F16) return static_cast<double>(__half2float(__float2half_rn(static_cast<float>(v))));
+  return v;
 }
 
 // Storage types: bf16 and f16 are carried as tagged 16-bit integers so that all

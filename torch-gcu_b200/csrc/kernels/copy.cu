@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kThreads)
 cast_stream_kernel(D* __restrict__ dst, const S* __restrict__ src, int64_t n) {
   const int64_t n8 = n / 8;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
-  constexpr int U = 2;
+  constexpr int U = 4;
   int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   auto load8 = [&](int64_t idx) {
     Pack8<S> p;
@@ -137,7 +137,7 @@ b200Status dispatch_dst(const b200Tensor* dst, const b200Tensor* src, cudaStream
 template <typename S, typename D>
 b200Status launch_stream_cast(const b200Tensor* dst, const b200Tensor* src, cudaStream_t s) {
   const int64_t n = numel(dst);
-  int grid = grid_for(n / 8 / 2 + 1, kThreads, 8);
+  int grid = grid_for(n / 8 / 4 + 1, kThreads, 8);
   cast_stream_kernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<D*>(dst->data),
                                                     static_cast<const S*>(src->data), n);
   return check_launch("b200_copy(cast)");

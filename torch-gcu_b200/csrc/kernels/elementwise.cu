@@ -238,6 +238,7 @@ b200Status b200_add(const b200Tensor* out, const b200Tensor* a, const b200Tensor
   b200Status st = check_binary(out, a, b, "b200_add");
   if (st != B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  alpha = round_scalar_to_dtype(alpha, out->dtype);  // ATen: alpha.to<scalar_t>()
   B200_DISPATCH_ARITH(out->dtype, T, {
     using M = typename OpMath<T>::type;
     if (alpha == 1.0) return launch_binary<T>(out, a, b, AddPlain<M>{}, s, "b200_add");
@@ -251,6 +252,7 @@ b200Status b200_sub(const b200Tensor* out, const b200Tensor* a, const b200Tensor
   b200Status st = check_binary(out, a, b, "b200_sub");
   if (st != B200_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  alpha = round_scalar_to_dtype(alpha, out->dtype);
   B200_DISPATCH_ARITH(out->dtype, T, {
     using M = typename OpMath<T>::type;
     if (alpha == 1.0) return launch_binary<T>(out, a, b, SubPlain<M>{}, s, "b200_sub");
@@ -290,9 +292,9 @@ b200Status b200_add_scalar(const b200Tensor* out, const b200Tensor* a, double b,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_ARITH(out->dtype, T, {
     using M = typename OpMath<T>::type;
-    // ATen wraps the scalar into the op's compute type and evaluates
-    // a + alpha*b with both in that type.
-    M c = static_cast<M>(alpha) * static_cast<M>(b);
+    // ATen casts the wrapped scalar and alpha to the tensor's dtype, then
+    // evaluates a + alpha*b in the compute type.
+    M c = static_cast<M>(round_scalar_to_dtype(alpha, out->dtype)) * static_cast<M>(round_scalar_to_dtype(b, out->dtype));
     return launch_unary<T>(out, a, AddConst<M>{c}, s, "b200_add_scalar");
   });
   return B200_OK;
@@ -304,7 +306,7 @@ b200Status b200_mul_scalar(const b200Tensor* out, const b200Tensor* a, double b,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   B200_DISPATCH_ARITH(out->dtype, T, {
     using M = typename OpMath<T>::type;
-    return launch_unary<T>(out, a, MulConst<M>{static_cast<M>(b)}, s, "b200_mul_scalar");
+    return launch_unary<T>(out, a, MulConst<M>{static_cast<M>(round_scalar_to_dtype(b, out->dtype))}, s, "b200_mul_scalar");
   });
   return B200_OK;
 }

@@ -353,7 +353,9 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
     __syncwarp();
     if (live) {
       keys_out[pos] = key[r];
-      vals_out[pos] = vals_in ? vals_in[i] : static_cast<uint32_t>(i);
+      // bit 31 of a key marks an out-of-range index: it rides along unsorted
+      // (the digits never reach it) and turns the value into an invalid id
+      vals_out[pos] = (key[r] >> 31) ? 0xffffffffu : (vals_in ? vals_in[i] : static_cast<uint32_t>(i));
     }
   }
 }
@@ -364,8 +366,8 @@ segment_bounds_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n, int64
                       uint32_t* __restrict__ seg_start) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p <= n; p += stride) {
-    const int64_t lo = p == 0 ? 0 : static_cast<int64_t>(sorted_keys[p - 1]) + 1;
-    int64_t hi = p == n ? n_dst : static_cast<int64_t>(sorted_keys[p]);
+    const int64_t lo = p == 0 ? 0 : static_cast<int64_t>(sorted_keys[p - 1] & 0x7fffffffu) + 1;
+    int64_t hi = p == n ? n_dst : static_cast<int64_t>(sorted_keys[p] & 0x7fffffffu);
     if (hi > n_dst) hi = n_dst;
     for (int64_t d = lo; d <= hi; ++d) seg_start[d] = static_cast<uint32_t>(p);
   }
@@ -382,7 +384,7 @@ row_keys_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, in
     if (wrap_negative && d < 0) d += n_dst;
     if (d < 0 || d >= n_dst) {
       atomicOr(&g_device_error_word, kErrIndexOutOfRange);
-      d = n_dst;  // parked after every real destination, never consumed
+      d = 0x80000000ll;  // flagged: sorts as key 0, consumed as an invalid source
     }
     keys[i] = static_cast<uint32_t>(d);
   }
@@ -401,7 +403,7 @@ element_keys_kernel(const I* __restrict__ index, int64_t n, StridedIndexer<2> ix
     int64_t dst = off[1] + j * dim_stride;
     if (j < 0 || j >= dim_size) {
       atomicOr(&g_device_error_word, kErrIndexOutOfRange);
-      dst = out_numel;
+      dst = 0x80000000ll;
     }
     keys[i] = static_cast<uint32_t>(dst);
   }
@@ -418,9 +420,22 @@ template <> __device__ __forceinline__ f16_t seq_add<f16_t>(f16_t a, f16_t b) {
   return f16_t{f32_to_f16_bits(__fadd_rn(f16_bits_to_f32(a.bits), f16_bits_to_f32(b.bits)))};
 }
 
+// Accumulator type of the segment kernels. 16-bit floats either round after
+// every add (ACC32 = false, what CPU index_put does) or accumulate in fp32 and
+// round once (ACC32 = true, what CPU scatter_add does).
+template <typename T, bool ACC32> struct AccT { using type = T; };
+template <> struct AccT<bf16_t, true> { using type = float; };
+template <> struct AccT<f16_t, true> { using type = float; };
+template <typename A, typename T> __device__ __forceinline__ A to_accum(T v) { return v; }
+template <> __device__ __forceinline__ float to_accum<float, bf16_t>(bf16_t v) { return bf16_bits_to_f32(v.bits); }
+template <> __device__ __forceinline__ float to_accum<float, f16_t>(f16_t v) { return f16_bits_to_f32(v.bits); }
+template <typename T, typename A> __device__ __forceinline__ T from_accum(A v) { return v; }
+template <> __device__ __forceinline__ bf16_t from_accum<bf16_t, float>(float v) { return bf16_t{f32_to_bf16_bits(v)}; }
+template <> __device__ __forceinline__ f16_t from_accum<f16_t, float>(float v) { return f16_t{f32_to_f16_bits(v)}; }
+
 // One warp per (destination row, 64-vector column chunk).
 // MODE 0: out = self + sum(sources in order); MODE 1: out = last source (or self).
-template <typename T, int V, int MODE>
+template <typename T, int V, int MODE, bool ACC32>
 __global__ void __launch_bounds__(kThreads)
 segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __restrict__ src,
                     const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
@@ -451,45 +466,69 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
       }
       continue;
     }
-    VecT a0, a1;
-    if (h0) a0 = self_row[c0];
-    if (h1) a1 = self_row[c1];
+    using A = typename AccT<T, ACC32>::type;
+    A a0[V], a1[V];
+    if (h0) {
+      const VecT t = self_row[c0];
+#pragma unroll
+      for (int e = 0; e < V; ++e) a0[e] = to_accum<A>(t.v[e]);
+    }
+    if (h1) {
+      const VecT t = self_row[c1];
+#pragma unroll
+      for (int e = 0; e < V; ++e) a1[e] = to_accum<A>(t.v[e]);
+    }
     for (uint32_t p = beg; p < end; p += 32) {
       const uint32_t cnt = min(32u, end - p);
-      uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0u;
-      if (mine >= n_src) mine = 0;  // keeps every read inside src
+      const uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0xffffffffu;
       uint32_t k = 0;
       for (; k + 4 <= cnt; k += 4) {  // four source rows in flight, added in order
         VecT b0[4], b1[4];
+        bool okr[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(__shfl_sync(0xffffffffu, mine, k + u)) * inner);
+          const uint32_t sid = __shfl_sync(0xffffffffu, mine, k + u);
+          okr[u] = sid < n_src;  // out-of-range sources were parked with an invalid id
+          const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(okr[u] ? sid : 0u) * inner);
           if (h0) b0[u] = srow[c0];
           if (h1) b1[u] = srow[c1];
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
+          if (!okr[u]) continue;
 #pragma unroll
           for (int e = 0; e < V; ++e) {
-            if (h0) a0.v[e] = seq_add(a0.v[e], b0[u].v[e]);
-            if (h1) a1.v[e] = seq_add(a1.v[e], b1[u].v[e]);
+            if (h0) a0[e] = seq_add(a0[e], to_accum<A>(b0[u].v[e]));
+            if (h1) a1[e] = seq_add(a1[e], to_accum<A>(b1[u].v[e]));
           }
         }
       }
       for (; k < cnt; ++k) {
-        const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(__shfl_sync(0xffffffffu, mine, k)) * inner);
+        const uint32_t sid = __shfl_sync(0xffffffffu, mine, k);
+        if (sid >= n_src) continue;
+        const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(sid) * inner);
         VecT b0, b1;
         if (h0) b0 = srow[c0];
         if (h1) b1 = srow[c1];
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          if (h0) a0.v[e] = seq_add(a0.v[e], b0.v[e]);
-          if (h1) a1.v[e] = seq_add(a1.v[e], b1.v[e]);
+          if (h0) a0[e] = seq_add(a0[e], to_accum<A>(b0.v[e]));
+          if (h1) a1[e] = seq_add(a1[e], to_accum<A>(b1.v[e]));
         }
       }
     }
-    if (h0) out_row[c0] = a0;
-    if (h1) out_row[c1] = a1;
+    if (h0) {
+      VecT t;
+#pragma unroll
+      for (int e = 0; e < V; ++e) t.v[e] = from_accum<T>(a0[e]);
+      out_row[c0] = t;
+    }
+    if (h1) {
+      VecT t;
+#pragma unroll
+      for (int e = 0; e < V; ++e) t.v[e] = from_accum<T>(a1[e]);
+      out_row[c1] = t;
+    }
   }
 }
 
@@ -501,15 +540,16 @@ segment_elements_kernel(T* out, const T* self, const T* __restrict__ src,
                         int64_t n, int64_t out_numel) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p < n; p += stride) {
-    const uint32_t key = sorted_keys[p];
+    const uint32_t key = sorted_keys[p] & 0x7fffffffu;
     if (key >= out_numel) continue;
-    if (p > 0 && sorted_keys[p - 1] == key) continue;
-    T acc = self[key];
-    for (int64_t q = p; q < n && sorted_keys[q] == key; ++q) {
+    if (p > 0 && (sorted_keys[p - 1] & 0x7fffffffu) == key) continue;
+    using A = typename AccT<T, true>::type;
+    A acc = to_accum<A>(self[key]);
+    for (int64_t q = p; q < n && (sorted_keys[q] & 0x7fffffffu) == key; ++q) {
       const uint32_t sidx = sorted_src[q];
-      if (sidx < n) acc = seq_add(acc, src[sidx]);
+      if (sidx < n) acc = seq_add(acc, to_accum<A>(src[sidx]));
     }
-    out[key] = acc;
+    out[key] = from_accum<T>(acc);
   }
 }
 
@@ -522,11 +562,11 @@ struct SortPlan {
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
 
-SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range] */, int64_t n_dst_rows) {
+SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range) */, int64_t n_dst_rows) {
   SortPlan p{};
   p.n = n;
   int bits = 1;
-  while ((int64_t(1) << bits) <= key_range && bits < 32) ++bits;
+  while ((int64_t(1) << bits) < key_range && bits < 31) ++bits;
   p.passes = (bits + 7) / 8;
   p.nblocks = static_cast<int>((n + kTile - 1) / kTile);
   if (p.nblocks < 1) p.nblocks = 1;
@@ -582,7 +622,7 @@ bool row_form_geometry(const b200Tensor* self, int64_t dim, const b200Tensor* in
   return true;
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, bool ACC32>
 b200Status launch_segment_rows(void* out, const void* self, const void* src, const uint32_t* sorted_src,
                                const uint32_t* seg_start, int64_t n_dst, int64_t n_src, int64_t inner,
                                cudaStream_t s) {
@@ -596,15 +636,17 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
   const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 8;
   const int grid = static_cast<int>(need < cap ? need : cap);
   if (vec)
-    segment_rows_kernel<T, V, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
+    segment_rows_kernel<T, V, MODE, ACC32><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
                                                              sorted_src, seg_start, n_dst, n_src, inner, cpr);
   else
-    segment_rows_kernel<T, 1, MODE><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
+    segment_rows_kernel<T, 1, MODE, ACC32><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
                                                              sorted_src, seg_start, n_dst, n_src, inner, cpr);
   return check_launch("segment rows");
 }
 
 // Row-form pipeline shared by scatter_add and index_put.
+// mode 0: accumulate in the element type; 1: assign (last source wins);
+// 2: accumulate, 16-bit floats in fp32 with one final rounding.
 template <typename T>
 b200Status scatter_rows(void* out, const void* self, const void* src, const b200Tensor* index,
                         int64_t index_stride, int64_t n_src, int64_t n_dst, int64_t inner, int mode,
@@ -640,8 +682,9 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
   if (st != B200_OK) return st;
   segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
-  if (mode == 0) return launch_segment_rows<T, 0>(out, self, src, sv, seg, n_dst, n_src, inner, s);
-  return launch_segment_rows<T, 1>(out, self, src, sv, seg, n_dst, n_src, inner, s);
+  if (mode == 1) return launch_segment_rows<T, 1, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
+  if (mode == 2 && sizeof(T) == 2) return launch_segment_rows<T, 0, true>(out, self, src, sv, seg, n_dst, n_src, inner, s);
+  return launch_segment_rows<T, 0, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
 }
 
 #define B200_DISPATCH_SCATTER(DT, T, ...)                                        \
@@ -868,8 +911,11 @@ b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64
   ScatterGeom g{};
   if (row_form_geometry(self, dim, index, src, &g)) {
     B200_DISPATCH_SCATTER(self->dtype, T, {
+      // CPU ATen runs scatter_add on bf16/f16 through an fp32 buffer: the sums
+      // are accumulated in fp32 and rounded once (mode 2). index_put(accumulate)
+      // instead adds in the element type, rounding after every add (mode 0).
       return scatter_rows<T>(out->data, self->data, src->data, index, g.index_stride, g.n_src, g.n_dst,
-                             g.inner, 0, 0, workspace, workspace_bytes, s);
+                             g.inner, 2, 0, workspace, workspace_bytes, s);
     });
   }
 
@@ -885,8 +931,8 @@ b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64
   B200_REQUIRE(same_shape(index, src) && is_contiguous(src), B200_NOT_SUPPORTED,
                "b200_scatter_add: element form needs src contiguous and shaped like index");
   const int64_t out_numel = numel(self);
-  B200_REQUIRE(n < (int64_t(1) << 31) && out_numel < (int64_t(1) << 32) - 1, B200_NOT_SUPPORTED,
-               "b200_scatter_add: element form limited to 2^31 sources / 2^32 destinations");
+  B200_REQUIRE(n < (int64_t(1) << 31) && out_numel < (int64_t(1) << 31), B200_NOT_SUPPORTED,
+               "b200_scatter_add: element form limited to 2^31 sources and destinations");
   SortPlan p = make_plan(n, out_numel, -1);
   B200_REQUIRE(workspace && workspace_bytes >= p.total, B200_WORKSPACE_TOO_SMALL,
                "b200_scatter_add: workspace of %zu bytes needed, %zu given", p.total, workspace_bytes);
