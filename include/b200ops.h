@@ -194,6 +194,23 @@ b200Status b200_index(const b200Tensor* out, const b200Tensor* src,
                       const int64_t* indexed_sizes, const int64_t* indexed_strides,
                       b200Stream stream);
 
+/* ---- contractions (reference: generated aotops::mm_out / addmm_out / bmm_out
+ *      -> topsatenMm / topsatenAddmm / topsatenBmm / topsatenBaddbmm) ----------
+ * out = beta*self + alpha*(a @ b). bf16 / f16 operands run on the tcgen05 tensor
+ * cores with fp32 accumulation and one rounding of the result; each operand may
+ * be row- or column-major (e.g. `weight.t()`) as long as its leading dimension
+ * is a multiple of 8 elements and its base 16-byte aligned, and out's last
+ * dimension is contiguous. fp32 / fp64 and every other layout take an exact-order
+ * SIMT kernel. `self` must be expanded to out's shape by the caller.          */
+b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                   b200Stream stream);
+b200Status b200_addmm(const b200Tensor* out, const b200Tensor* self, const b200Tensor* a,
+                      const b200Tensor* b, double beta, double alpha, b200Stream stream);
+b200Status b200_bmm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
+                    b200Stream stream);
+b200Status b200_baddbmm(const b200Tensor* out, const b200Tensor* self, const b200Tensor* a,
+                        const b200Tensor* b, double beta, double alpha, b200Stream stream);
+
 /* ---- fused inference ops (no counterpart kernel in the reference, which runs
  *      them as chains of the ops above; they sit beside the reference's one
  *      efficient op, torch_gcu/csrc/efficient_ops/ops.cpp:335-342) ---------- */

@@ -1,0 +1,141 @@
+"""mm / addmm / bmm / baddbmm through the C ABI: the reference's own fp32 cases
+(test/op_test/test_linear.py) and bf16 / f16 tensor-core shapes and layouts,
+checked against CPU arithmetic."""
+import pytest
+import torch
+
+from oracle import aten_cpu
+from test_ops_gpu import DEV, close, dev
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def tc_close(out, a, b, extra=None, alpha=1.0, beta=1.0):
+    """bf16/f16 contraction tolerance: fp32-accumulated CPU result rounded once;
+    rtol 1.6e-2 (reference class tolerance for 16-bit contractions), atol scaled
+    with sqrt(K) because |out| grows like sqrt(K) for N(0,1) operands."""
+    ref = alpha * (a.float() @ b.float())
+    if extra is not None:
+        ref = ref + beta * extra.float()
+    K = a.shape[-1]
+    close(out, ref.to(out.dtype), 1.6e-2, 1e-2 * max(1.0, (K / 64) ** 0.5))
+
+
+def test_reference_linear_cases_fp32(ops, golden):
+    g = golden("ref_linear")
+    m = g["mm"]
+    out = torch.empty(2, 3, device=DEV)
+    ops.mm(out, dev(m["m1"]), dev(m["m2"]))
+    close(out, m["out"], 1e-5, 1e-8)  # torch.allclose defaults, as the reference test uses
+    am = g["addmm"]
+    ops.addmm(out, dev(am["c"]).expand(2, 3), dev(am["m1"]), dev(am["m2"]))
+    close(out, am["out"], 1e-5, 1e-8)
+    bm = g["bmm"]
+    ob = torch.empty(4, 2, 3, device=DEV)
+    ops.bmm(ob, dev(bm["b1"]), dev(bm["b2"]))
+    close(ob, bm["out"], 1e-5, 1e-8)
+    bb = g["baddbmm"]
+    o2 = torch.empty(4, 2, 5, device=DEV)
+    ops.baddbmm(o2, dev(bb["i"]), dev(bb["b1"]), dev(bb["b2"]), bb["beta"], bb["alpha"])
+    close(o2, bb["out"], 1e-5, 1e-7)
+    lin = g["linear"]  # linear = addmm(bias, x, w.t())
+    ol = torch.empty(2, 3, device=DEV)
+    ops.addmm(ol, dev(lin["b"]).expand(2, 3), dev(lin["x"]), dev(lin["w"]).t())
+    close(ol, lin["out"], 1e-5, 1e-7)
+    ops.mm(ol, dev(lin["x"]), dev(lin["w"]).t())
+    close(ol, lin["out_nobias"], 1e-5, 1e-7)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 64, 128), (256, 512, 256), (130, 200, 72), (64, 6144, 512),
+                                   (1, 8, 8), (300, 136, 40), (1024, 1024, 1024), (257, 1032, 192)])
+@pytest.mark.parametrize("dtype", [BF, torch.float16])
+def test_mm_weight_transposed(ops, M, N, K, dtype):
+    """x @ w.t(): both operands K-contiguous (the nn.Linear layout)."""
+    g = torch.Generator().manual_seed(41)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g).to(dtype)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    ops.mm(out, dev(a), dev(w).t())
+    tc_close(out, a, w.t())
+    assert ops.device_error_fetch() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (200, 136, 96), (512, 384, 320)])
+def test_mm_other_layouts(ops, M, N, K):
+    g = torch.Generator().manual_seed(42)
+    a = torch.randn(M, K, generator=g).to(BF)
+    b = torch.randn(K, N, generator=g).to(BF)
+    out = torch.empty(M, N, dtype=BF, device=DEV)
+    ops.mm(out, dev(a), dev(b))                  # B row-major (N contiguous)
+    tc_close(out, a, b)
+    at = dev(a.t().contiguous()).t()             # A column-major (M contiguous)
+    ops.mm(out, at, dev(b))
+    tc_close(out, a, b)
+    ops.mm(out, at, dev(b.t().contiguous()).t())
+    tc_close(out, a, b)
+    wide = torch.zeros(M, N + 24, dtype=BF, device=DEV)   # strided output rows
+    ops.mm(wide[:, 8:8 + N], dev(a), dev(b))
+    tc_close(wide[:, 8:8 + N], a, b)
+    assert wide[:, :8].abs().sum().item() == 0 and wide[:, 8 + N:].abs().sum().item() == 0
+
+
+def test_addmm_bias_and_scaling(ops, golden):
+    g = torch.Generator().manual_seed(43)
+    a, w = torch.randn(160, 192, generator=g).to(BF), torch.randn(264, 192, generator=g).to(BF)
+    bias = torch.randn(264, generator=g).to(BF)
+    out = torch.empty(160, 264, dtype=BF, device=DEV)
+    ops.addmm(out, dev(bias).expand(160, 264), dev(a), dev(w).t())
+    tc_close(out, a, w.t(), bias.expand(160, 264))
+    full = torch.randn(160, 264, generator=g).to(BF)
+    ops.addmm(out, dev(full), dev(a), dev(w).t(), beta=-0.5, alpha=0.25)
+    tc_close(out, a, w.t(), full, alpha=0.25, beta=-0.5)
+    m = golden("op_small")["mm_bf16"]
+    o = torch.empty(64, 80, dtype=BF, device=DEV)
+    ops.mm(o, dev(m["a"]), dev(m["b"]))
+    close(o, m["out"], 1.6e-2, 1e-2)
+
+
+def test_bmm_batched(ops):
+    g = torch.Generator().manual_seed(44)
+    a = torch.randn(5, 130, 72, generator=g).to(BF)
+    b = torch.randn(5, 72, 96, generator=g).to(BF)
+    out = torch.empty(5, 130, 96, dtype=BF, device=DEV)
+    ops.bmm(out, dev(a), dev(b))
+    tc_close(out, a, b)
+    ops.bmm(out, dev(a), dev(b.transpose(1, 2).contiguous()).transpose(1, 2))
+    tc_close(out, a, b)
+    add = torch.randn(5, 130, 96, generator=g).to(BF)
+    ops.baddbmm(out, dev(add), dev(a), dev(b), beta=2.0, alpha=0.5)
+    tc_close(out, a, b, add, alpha=0.5, beta=2.0)
+    f = torch.randn(3, 7, 5, generator=g)
+    h = torch.randn(3, 5, 9, generator=g)
+    of = torch.empty(3, 7, 9, device=DEV)
+    ops.bmm(of, dev(f), dev(h))
+    close(of, aten_cpu.bmm(f, h), 1e-5, 1e-6)
+
+
+def test_mm_unaligned_falls_back_and_empty(ops):
+    g = torch.Generator().manual_seed(45)
+    a, b = torch.randn(33, 21, generator=g).to(BF), torch.randn(21, 19, generator=g).to(BF)
+    out = torch.empty(33, 19, dtype=BF, device=DEV)
+    ops.mm(out, dev(a), dev(b))  # leading dimensions not multiples of 8: SIMT path
+    tc_close(out, a, b)
+    e = torch.empty(0, 19, dtype=BF, device=DEV)
+    ops.mm(e, torch.empty(0, 21, dtype=BF, device=DEV), dev(b))
+    z = torch.ones(4, 6, dtype=BF, device=DEV)
+    ops.mm(z, torch.empty(4, 0, dtype=BF, device=DEV), torch.empty(0, 6, dtype=BF, device=DEV))
+    assert z.abs().sum().item() == 0
+
+
+def test_layer_projection_shapes(ops):
+    """Decoder-layer GEMM shapes at a reduced token count, checked on sampled rows."""
+    g = torch.Generator().manual_seed(46)
+    x = torch.randn(512, 4096, generator=g).to(BF)
+    for n in (6144, 4096):
+        w = (torch.randn(n, 4096, generator=g) * 0.02).to(BF)
+        out = torch.empty(512, n, dtype=BF, device=DEV)
+        ops.mm(out, dev(x), dev(w).t())
+        rows = torch.tensor([0, 1, 127, 128, 255, 300, 511])
+        ref = (x[rows].float() @ w.float().t())
+        close(out[rows], ref.to(BF), 1.6e-2, 1e-2)

@@ -281,6 +281,24 @@ def swiglu(out, gate, up, stream=None):
     check(lib().b200_swiglu(_ref(view(out)), _ref(view(gate)), _ref(view(up)), _stream(stream)))
 
 
+def mm(out, a, b, stream=None):
+    check(lib().b200_mm(_ref(view(out)), _ref(view(a)), _ref(view(b)), _stream(stream)))
+
+
+def addmm(out, self, a, b, beta=1.0, alpha=1.0, stream=None):
+    check(lib().b200_addmm(_ref(view(out)), _ref(view(self)), _ref(view(a)), _ref(view(b)), ctypes.c_double(beta),
+                           ctypes.c_double(alpha), _stream(stream)))
+
+
+def bmm(out, a, b, stream=None):
+    check(lib().b200_bmm(_ref(view(out)), _ref(view(a)), _ref(view(b)), _stream(stream)))
+
+
+def baddbmm(out, self, a, b, beta=1.0, alpha=1.0, stream=None):
+    check(lib().b200_baddbmm(_ref(view(out)), _ref(view(self)), _ref(view(a)), _ref(view(b)), ctypes.c_double(beta),
+                             ctypes.c_double(alpha), _stream(stream)))
+
+
 def device_error_fetch():
     flags = ctypes.c_uint32(0)
     check(lib().b200_device_error_fetch(ctypes.byref(flags)))

@@ -62,45 +62,54 @@ copy_indexed_kernel(U* dst, const U* src, int64_t n, StridedIndexer<2> ix) {
   }
 }
 
-// Streaming cast between f32 / bf16 / f16: 8 elements per step.
-template <typename T> struct Pack8 { T v[8]; };
+// Streaming cast between f32 / bf16 / f16. E elements per thread step, chosen so
+// that the wider side moves 128 bits and every warp access is contiguous on
+// both sides (f32<->16-bit: 4 elements = 16 B + 8 B; 16-bit<->16-bit: 8 elements).
+template <typename T, int E> struct alignas(sizeof(T) * E) PackE { T v[E]; };
+
+template <typename P> __device__ __forceinline__ P load_stream_pack(const P* p) {
+  static_assert(sizeof(P) == 16 || sizeof(P) == 8, "pack size");
+  P r;
+  if constexpr (sizeof(P) == 16) {
+    int4 t = __ldcs(reinterpret_cast<const int4*>(p));
+    r = *reinterpret_cast<P*>(&t);
+  } else {
+    int2 t = __ldcs(reinterpret_cast<const int2*>(p));
+    r = *reinterpret_cast<P*>(&t);
+  }
+  return r;
+}
+template <typename P> __device__ __forceinline__ void store_stream_pack(P* p, const P& v) {
+  if constexpr (sizeof(P) == 16) __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
+  else __stcs(reinterpret_cast<int2*>(p), *reinterpret_cast<const int2*>(&v));
+}
 
 template <typename S, typename D>
 __global__ void __launch_bounds__(kThreads)
 cast_stream_kernel(D* __restrict__ dst, const S* __restrict__ src, int64_t n) {
-  const int64_t n8 = n / 8;
+  constexpr int E = 16 / (sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D));
+  constexpr int U = 8;
+  const int64_t nv = n / E;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
-  constexpr int U = 4;
+  const PackE<S, E>* in = reinterpret_cast<const PackE<S, E>*>(src);
+  PackE<D, E>* out = reinterpret_cast<PackE<D, E>*>(dst);
+  auto convert = [](const PackE<S, E>& p) {
+    PackE<D, E> o;
+#pragma unroll
+    for (int k = 0; k < E; ++k) o.v[k] = store_from_math<D>(load_as_math(p.v[k]));
+    return o;
+  };
   int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  auto load8 = [&](int64_t idx) {
-    Pack8<S> p;
-    constexpr int nvec = sizeof(S) * 8 / 16;
-    const int4* q = reinterpret_cast<const int4*>(src + idx * 8);
-    int4* r = reinterpret_cast<int4*>(&p);
+  for (; i + (U - 1) * stride < nv; i += U * stride) {
+    PackE<S, E> p[U];
 #pragma unroll
-    for (int k = 0; k < nvec; ++k) r[k] = __ldcs(q + k);
-    return p;
-  };
-  auto store8 = [&](int64_t idx, const Pack8<S>& p) {
-    Pack8<D> o;
+    for (int u = 0; u < U; ++u) p[u] = load_stream_pack(in + i + u * stride);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) o.v[k] = store_from_math<D>(load_as_math(p.v[k]));
-    constexpr int nvec = sizeof(D) * 8 / 16;
-    int4* q = reinterpret_cast<int4*>(dst + idx * 8);
-    const int4* r = reinterpret_cast<const int4*>(&o);
-#pragma unroll
-    for (int k = 0; k < nvec; ++k) __stcs(q + k, r[k]);
-  };
-  for (; i + (U - 1) * stride < n8; i += U * stride) {
-    Pack8<S> p[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) p[u] = load8(i + u * stride);
-#pragma unroll
-    for (int u = 0; u < U; ++u) store8(i + u * stride, p[u]);
+    for (int u = 0; u < U; ++u) store_stream_pack(out + i + u * stride, convert(p[u]));
   }
-  for (; i < n8; i += stride) store8(i, load8(i));
+  for (; i < nv; i += stride) out[i] = convert(in[i]);
   if (blockIdx.x == 0) {
-    int64_t t = n8 * 8 + threadIdx.x;
+    int64_t t = nv * E + threadIdx.x;
     if (t < n) dst[t] = store_from_math<D>(load_as_math(src[t]));
   }
 }
@@ -137,7 +146,7 @@ b200Status dispatch_dst(const b200Tensor* dst, const b200Tensor* src, cudaStream
 template <typename S, typename D>
 b200Status launch_stream_cast(const b200Tensor* dst, const b200Tensor* src, cudaStream_t s) {
   const int64_t n = numel(dst);
-  int grid = grid_for(n / 8 / 4 + 1, kThreads, 8);
+  int grid = grid_for(n / 4 / 8 + 1, kThreads, 8);
   cast_stream_kernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<D*>(dst->data),
                                                     static_cast<const S*>(src->data), n);
   return check_launch("b200_copy(cast)");

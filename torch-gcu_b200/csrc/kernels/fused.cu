@@ -127,21 +127,24 @@ struct RopeArgs {
   int64_t P;             // rows of the tables
 };
 
-template <typename T>
+// W: index arithmetic type (uint32_t when the element count allows).
+template <typename T, typename W>
 __global__ void __launch_bounds__(256)
 rope_kernel(RopeArgs a) {
   constexpr int V = 16 / sizeof(T);
   const int64_t half = a.D / 2;
-  const int vph = static_cast<int>(half / V);  // vectors per half row
-  const int64_t total = a.B * a.S * a.H * vph;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
-    const int v = static_cast<int>(i % vph);
-    int64_t t = i / vph;
-    const int64_t h = t % a.H;
-    t /= a.H;
-    const int64_t s = t % a.S;
-    const int64_t b = t / a.S;
+  const W vph = static_cast<W>(half / V);  // vectors per half row
+  const W total = static_cast<W>(a.B * a.S * a.H) * vph;
+  const W stride = static_cast<W>(gridDim.x) * 256;
+  const W H = static_cast<W>(a.H), S = static_cast<W>(a.S);
+  for (W i = static_cast<W>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
+    W t = i / vph;
+    const int v = static_cast<int>(i - t * vph);
+    const W th = t / H;
+    const int64_t h = t - th * H;
+    const W tb = th / S;
+    const int64_t s = th - tb * S;
+    const int64_t b = tb;
     int64_t p = a.positions ? a.positions[b * a.pos_stride_b + s * a.pos_stride_s] : s;
     if (p < 0 || p >= a.P) p = 0;  // caller guarantees range; keep reads in bounds
     const T* xr = static_cast<const T*>(a.x) + b * a.xs[0] + s * a.xs[1] + h * a.xs[2];
@@ -179,7 +182,13 @@ __device__ __forceinline__ Vec16<T> swiglu_vec(const Vec16<T>& g, const Vec16<T>
 #pragma unroll
   for (int e = 0; e < V; ++e) {
     const float x = load_as_math(g.v[e]);
-    o.v[e] = store_from_math<T>(x / (1.0f + expf(-x)) * load_as_math(u.v[e]));
+    if constexpr (sizeof(T) == 2) {
+      // 16-bit output: the fast exp / reciprocal (a few fp32 ulp) are far below
+      // half an output ulp, and keep the kernel off the instruction-issue limit
+      o.v[e] = store_from_math<T>(x * __frcp_rn(1.0f + __expf(-x)) * load_as_math(u.v[e]));
+    } else {
+      o.v[e] = store_from_math<T>(x / (1.0f + expf(-x)) * load_as_math(u.v[e]));
+    }
   }
   return o;
 }
@@ -314,7 +323,11 @@ b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tenso
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = a.B * a.S * a.H * (a.D / 2 / V);
   const int grid = grid_for(total, 256, 8);
-  B200_DISPATCH_HALF_FLOAT(x->dtype, T, { rope_kernel<T><<<grid, 256, 0, s>>>(a); });
+  const bool small = total + static_cast<int64_t>(grid) * 256 < (int64_t(1) << 32);
+  B200_DISPATCH_HALF_FLOAT(x->dtype, T, {
+    if (small) rope_kernel<T, uint32_t><<<grid, 256, 0, s>>>(a);
+    else rope_kernel<T, int64_t><<<grid, 256, 0, s>>>(a);
+  });
   return check_launch("b200_rope");
 }
 

@@ -1,0 +1,428 @@
+// bf16 / f16 matrix multiply on the 5th-generation tensor cores.
+//
+//   out[b] = alpha * A[b] @ B[b] + beta * Cin[b],  fp32 accumulation.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0     TMA producer: 128 x 64 tiles of A and BN x 64 tiles of B into a
+//              ring of shared-memory stages (128-byte swizzle), mbarrier-tracked
+//   warp 1     allocates tensor memory and issues tcgen05.mma (128 x BN x 16),
+//              one elected thread; commits free the stage / publish the tile
+//   warps 2-5  epilogue: tcgen05.ld the fp32 accumulator (each warp its 32-lane
+//              quarter), scale, add beta*Cin, round, store 64-byte row segments
+// Two accumulators live in tensor memory (2 x BN columns), so the epilogue of
+// tile i overlaps the main loop of tile i+1. Tiles are walked in groups of 8
+// row-tiles so that concurrently running CTAs share A and B tiles through L2.
+// Either operand may be K-major (K contiguous) or MN-major (M / N contiguous);
+// the layout goes into the tensor maps and the MMA descriptors, no copy is made.
+// Loads never use cluster multicast. Every barrier wait is bounded.
+#include "common.cuh"
+#include "gemm_simt.cuh"
+#include "tc_common.cuh"
+
+#include <mutex>
+
+namespace b200 {
+unsigned int* device_error_word();  // index.cu: address of the device error word
+
+namespace tc {
+
+bool encode_tmap_16bit(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                       const uint64_t* strides_bytes, const uint32_t* box, const char** err) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  });
+  if (!fn) {
+    *err = "cuTensorMapEncodeTiled is not available from this driver";
+    return false;
+  }
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base),
+                  reinterpret_cast<const cuuint64_t*>(dims), reinterpret_cast<const cuuint64_t*>(strides_bytes),
+                  reinterpret_cast<const cuuint32_t*>(box), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    *err = "cuTensorMapEncodeTiled rejected the operand layout";
+    return false;
+  }
+  return true;
+}
+
+}  // namespace tc
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;
+constexpr int BK = 64;           // 64 x 16-bit = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;
+constexpr int GROUP_M = 8;
+
+struct GemmParams {
+  int M, N, K, batch;
+  int a_mn_major, b_mn_major;    // 0: K contiguous, 1: M (resp. N) contiguous
+  int is_bf16;
+  float alpha, beta;
+  void* out;
+  int64_t o_sb, o_sm;            // out: column stride 1
+  const void* cin;
+  int64_t c_sb, c_sm, c_sn;
+  unsigned int* error_word;
+};
+
+template <int BN> struct GemmCfg {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (196608 / kStage) > 8 ? 8 : (196608 / kStage);
+  static constexpr int kSmem = kStages * kStage + 1024 /* alignment slack */ + 256 /* barriers */;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {64,128,256}
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
+  const int per_batch = tiles_m * tiles_n;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  const int group = t / (GROUP_M * tiles_n);
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  t -= group * GROUP_M * tiles_n;
+  tm = first_m + t % rows;
+  tn = t / rows;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStage);
+  uint64_t* full = bars;                       // [kStages]
+  uint64_t* empty = bars + Cfg::kStages;       // [kStages]
+  uint64_t* acc_full = empty + Cfg::kStages;   // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n * p.batch;
+  const int n_k = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int b, tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+        for (int k = 0; k < n_k; ++k) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStage;
+          uint8_t* sb = sa + Cfg::kStageA;
+          mbar_arrive_expect_tx(&full[stage], Cfg::kStage);
+          if (!p.a_mn_major) {
+            tma_load_3d(sa, &tmap_a, &full[stage], k * BK, tm * BM, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(sa + j * 8192, &tmap_a, &full[stage], tm * BM + j * 64, k * BK, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * BN, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * 8192, &tmap_b, &full[stage], tn * BN + j * 64, k * BK, b);
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, BN, p.is_bf16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
+      // K-major: rows of 128 B, 8-row groups 1024 B apart, 32 B per UMMA_K step.
+      // MN-major: 64-element groups 8192 B apart (one TMA box each), 8-k groups
+      // 1024 B apart, 2048 B per UMMA_K step.
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_step = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_step = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * BN);
+        for (int k = 0; k < n_k; ++k) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStage);
+          const uint32_t sb = sa + Cfg::kStageA;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = smem_desc_sw128(sa + kk * a_step, a_lbo, 1024u);
+            const uint64_t db = smem_desc_sw128(sb + kk * b_step, b_lbo, 1024u);
+            umma_f16(d_tmem, da, db, idesc, (k | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // stage reusable once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[ab]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;  // the TMEM lanes this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      int b, tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+      if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(row) * p.o_sm;
+      const uint16_t* crow = p.cin ? static_cast<const uint16_t*>(p.cin) + b * p.c_sb + static_cast<int64_t>(row) * p.c_sm
+                                   : nullptr;
+      const bool vec_ok = (p.o_sm % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) + 2 * b * p.o_sb) % 16 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * BN + c), r);
+        tmem_wait_ld();
+        const int col0 = tn * BN + c;
+        if (row_ok && col0 < p.N) {
+          alignas(16) uint16_t o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = p.alpha * __uint_as_float(r[j]);
+            if (crow && col0 + j < p.N) {
+              const uint16_t cb = crow[static_cast<int64_t>(col0 + j) * p.c_sn];
+              v += p.beta * (p.is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+            }
+            o[j] = p.is_bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+          }
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<int4*>(orow + col0 + q * 8) = *reinterpret_cast<const int4*>(o + q * 8);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) orow[col0 + j] = o[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[ab]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);  // bit 1: a barrier wait timed out
+}
+
+struct Operand {
+  const void* base;
+  bool mn_major;
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+};
+
+// Describes a (rows x K) operand (A: rows = M; B: rows = N) for TMA, or fails.
+bool describe_operand(const void* data, int64_t rows, int64_t K, int64_t batch, int64_t s_row, int64_t s_k,
+                      int64_t s_b, int tile_rows, Operand* o) {
+  if (reinterpret_cast<uintptr_t>(data) % 16) return false;
+  if (batch > 1 && (s_b % 8 != 0 || s_b <= 0)) return false;
+  auto align16 = [](uint64_t x) { return (x + 15) & ~uint64_t(15); };
+  o->base = data;
+  if ((s_k == 1 || K == 1) && s_row % 8 == 0 && s_row >= K) {
+    o->mn_major = false;
+    o->dims[0] = K; o->dims[1] = rows; o->dims[2] = batch;
+    o->strides[0] = static_cast<uint64_t>(s_row) * 2;
+    o->strides[1] = batch > 1 ? static_cast<uint64_t>(s_b) * 2 : align16(static_cast<uint64_t>(s_row) * rows * 2);
+    o->box[0] = BK; o->box[1] = tile_rows; o->box[2] = 1;
+    return true;
+  }
+  if ((s_row == 1 || rows == 1) && s_k % 8 == 0 && s_k >= rows) {
+    o->mn_major = true;
+    o->dims[0] = rows; o->dims[1] = K; o->dims[2] = batch;
+    o->strides[0] = static_cast<uint64_t>(s_k) * 2;
+    o->strides[1] = batch > 1 ? static_cast<uint64_t>(s_b) * 2 : align16(static_cast<uint64_t>(s_k) * K * 2);
+    o->box[0] = 64; o->box[1] = BK; o->box[2] = 1;
+    return true;
+  }
+  return false;
+}
+
+template <int BN>
+b200Status launch_tc(const Operand& oa, const Operand& ob, GemmParams p, cudaStream_t s) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap ta, tb;
+  const char* err = "";
+  B200_REQUIRE(encode_tmap_16bit(&ta, oa.base, 3, oa.dims, oa.strides, oa.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  B200_REQUIRE(encode_tmap_16bit(&tb, ob.base, 3, ob.dims, ob.strides, ob.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+  });
+  // the attribute is per device: set it again when this device has not seen it
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    last_dev = dev;
+  }
+  B200_REQUIRE(attr_err == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(attr_err));
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
+  const int sms = sm_count_current_device();
+  const int grid = tiles < sms ? tiles : sms;
+  gemm_tc_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, s>>>(ta, tb, p);
+  return check_launch("matmul (tcgen05)");
+}
+
+}  // namespace
+
+// Shared implementation of mm / addmm / bmm / baddbmm.
+b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, const b200Tensor* cin,
+                       double alpha, double beta, bool batched, cudaStream_t s, const char* name) {
+  B200_REQUIRE(valid(out) && valid(a) && valid(b), B200_BAD_PARAM, "%s: invalid tensor view", name);
+  const int nd = batched ? 3 : 2;
+  B200_REQUIRE(out->ndim == nd && a->ndim == nd && b->ndim == nd, B200_BAD_PARAM, "%s: operands must be %d-D", name, nd);
+  B200_REQUIRE(a->dtype == b->dtype && a->dtype == out->dtype, B200_BAD_PARAM, "%s: dtype mismatch", name);
+  const int o = batched ? 1 : 0;
+  const int64_t batch = batched ? out->sizes[0] : 1;
+  const int64_t M = out->sizes[o], N = out->sizes[o + 1], K = a->sizes[o + 1];
+  B200_REQUIRE(a->sizes[o] == M && b->sizes[o] == K && b->sizes[o + 1] == N &&
+               (!batched || (a->sizes[0] == batch && b->sizes[0] == batch)), B200_BAD_PARAM,
+               "%s: shapes do not multiply", name);
+  if (cin && beta != 0.0) {
+    B200_REQUIRE(valid(cin) && same_shape(cin, out) && cin->dtype == out->dtype, B200_BAD_PARAM,
+                 "%s: the addend must be expanded to the output's shape and share its dtype", name);
+  } else {
+    cin = nullptr;
+  }
+  if (M == 0 || N == 0 || batch == 0) return B200_OK;
+  if (K == 0) {  // out = beta * cin
+    if (!cin) return b200_fill(out, 0.0, s);
+    return b200_mul_scalar(out, cin, beta, s);
+  }
+
+  const bool tc_type = a->dtype == B200_BF16 || a->dtype == B200_F16;
+  const bool out_ok = (out->strides[o + 1] == 1 || N == 1) && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) &&
+                      batch < 65536;
+  if (tc_type && out_ok) {
+    // BN: the widest tile that still gives every SM work
+    const int sms = sm_count_current_device();
+    auto tiles = [&](int bn) { return ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * batch; };
+    int bn = 256;
+    if (tiles(256) < sms && N > 128) bn = 128;
+    if (tiles(bn) < sms && N > 64) bn = 64;
+    if (N <= 64) bn = 64; else if (N <= 128 && bn > 128) bn = 128;
+    Operand oa, ob;
+    const bool a_ok = describe_operand(a->data, M, K, batch, a->strides[o], a->strides[o + 1], batched ? a->strides[0] : 0, BM, &oa);
+    const bool b_ok = describe_operand(b->data, N, K, batch, b->strides[o + 1], b->strides[o], batched ? b->strides[0] : 0, bn, &ob);
+    if (a_ok && b_ok) {
+      GemmParams p{};
+      p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+      p.a_mn_major = oa.mn_major; p.b_mn_major = ob.mn_major;
+      p.is_bf16 = a->dtype == B200_BF16;
+      p.alpha = (float)alpha; p.beta = (float)beta;
+      p.out = out->data; p.o_sb = batched ? out->strides[0] : 0; p.o_sm = out->strides[o];
+      if (cin) {
+        p.cin = cin->data; p.c_sb = batched ? cin->strides[0] : 0; p.c_sm = cin->strides[o]; p.c_sn = cin->strides[o + 1];
+      }
+      p.error_word = device_error_word();
+      B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+      if (bn == 256) return launch_tc<256>(oa, ob, p, s);
+      if (bn == 128) return launch_tc<128>(oa, ob, p, s);
+      return launch_tc<64>(oa, ob, p, s);
+    }
+  }
+  simt::MatmulArgs q{};
+  q.a = a->data; q.b = b->data; q.cin = cin ? cin->data : nullptr; q.out = out->data;
+  q.M = M; q.N = N; q.K = K; q.batch = batch;
+  q.a_sb = batched ? a->strides[0] : 0; q.a_sm = a->strides[o]; q.a_sk = a->strides[o + 1];
+  q.b_sb = batched ? b->strides[0] : 0; q.b_sk = b->strides[o]; q.b_sn = b->strides[o + 1];
+  if (cin) { q.c_sb = batched ? cin->strides[0] : 0; q.c_sm = cin->strides[o]; q.c_sn = cin->strides[o + 1]; }
+  q.o_sb = batched ? out->strides[0] : 0; q.o_sm = out->strides[o]; q.o_sn = out->strides[o + 1];
+  q.alpha = alpha; q.beta = beta;
+  return simt::launch(q, a->dtype, s);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
+  return matmul_impl(out, a, b, nullptr, 1.0, 0.0, false, static_cast<cudaStream_t>(stream), "b200_mm");
+}
+b200Status b200_addmm(const b200Tensor* out, const b200Tensor* self, const b200Tensor* a, const b200Tensor* b,
+                      double beta, double alpha, b200Stream stream) {
+  return matmul_impl(out, a, b, self, alpha, beta, false, static_cast<cudaStream_t>(stream), "b200_addmm");
+}
+b200Status b200_bmm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
+  return matmul_impl(out, a, b, nullptr, 1.0, 0.0, true, static_cast<cudaStream_t>(stream), "b200_bmm");
+}
+b200Status b200_baddbmm(const b200Tensor* out, const b200Tensor* self, const b200Tensor* a, const b200Tensor* b,
+                        double beta, double alpha, b200Stream stream) {
+  return matmul_impl(out, a, b, self, alpha, beta, true, static_cast<cudaStream_t>(stream), "b200_baddbmm");
+}
+
+}  // extern "C"

@@ -20,6 +20,16 @@ namespace b200 {
 __device__ unsigned int g_device_error_word = 0;
 enum : unsigned int { kErrIndexOutOfRange = 1u };
 
+// Device address of the error word (for kernels in other translation units).
+unsigned int* device_error_word() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_device_error_word) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return static_cast<unsigned int*>(p);
+}
+
 namespace {
 
 constexpr int kThreads = 256;
@@ -706,7 +716,8 @@ using namespace b200;
 extern "C" {
 
 // Reads and clears the device error word (bit 0: an index was out of range and
-// was replaced by 0 / skipped). Synchronises the device; meant for debug modes.
+// was replaced by 0 / skipped; bit 1: a bounded barrier wait in a tensor-core
+// kernel gave up). Synchronises the device; meant for debug modes.
 b200Status b200_device_error_fetch(uint32_t* flags) {
   B200_REQUIRE(flags, B200_BAD_PARAM, "b200_device_error_fetch: null");
   unsigned int v = 0, zero = 0;
