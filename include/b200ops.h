@@ -211,6 +211,17 @@ b200Status b200_bmm(const b200Tensor* out, const b200Tensor* a, const b200Tensor
 b200Status b200_baddbmm(const b200Tensor* out, const b200Tensor* self, const b200Tensor* a,
                         const b200Tensor* b, double beta, double alpha, b200Stream stream);
 
+/* reference: aotops::_scaled_dot_product_flash_attention ->
+ * topsatenScaledDotProductFlashAttention (torch_gcu/csrc/aten/aot_ops/
+ * gcu_attention.cpp:21-80; backend choice RegisterSPDA.cpp:223-275).
+ * q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D), out like q (any strides with D contiguous, so
+ * the (B,S,H,D)-allocated, transposed output of the reference's shape inference
+ * is written in place), lse f32 (B,Hq,Sq) or NULL. bf16/f16, D 64 or 128, Hq a
+ * multiple of Hkv. is_causal needs Sq == Sk; dropout is not supported.         */
+b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tensor* lse, const b200Tensor* q,
+                               const b200Tensor* k, const b200Tensor* v, int32_t is_causal,
+                               double scale, b200Stream stream);
+
 /* ---- fused inference ops (no counterpart kernel in the reference, which runs
  *      them as chains of the ops above; they sit beside the reference's one
  *      efficient op, torch_gcu/csrc/efficient_ops/ops.cpp:335-342) ---------- */

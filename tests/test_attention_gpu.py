@@ -1,0 +1,92 @@
+"""Flash-attention forward through the C ABI against an fp32 CPU evaluation of
+softmax(scale*QK^T + mask)V on the same bf16 operands."""
+import pytest
+import torch
+
+from oracle import aten_cpu
+from test_ops_gpu import DEV, close, dev
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def cpu_ref(q, k, v, causal):
+    if causal:
+        return aten_cpu.sdpa_causal(q, k, v)
+    B, Hq, S, D = q.shape
+    G = Hq // k.shape[1]
+    kf, vf = k.float().repeat_interleave(G, 1), v.float().repeat_interleave(G, 1)
+    s = (q.float() @ kf.transpose(-1, -2)) * D ** -0.5
+    return (torch.softmax(s, -1) @ vf).to(q.dtype), torch.logsumexp(s, -1)
+
+
+def run(ops, q, k, v, causal):
+    B, Hq, S, D = q.shape
+    out = torch.empty(B, S, Hq, D, dtype=q.dtype, device=DEV).transpose(1, 2)  # allocated (B,S,H,D) like the reference
+    lse = torch.empty(B, Hq, S, dtype=torch.float32, device=DEV)
+    ops.sdpa_flash_fwd(out, lse, dev(q), dev(k), dev(v), causal)
+    assert ops.device_error_fetch() == 0
+    return out, lse
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,S,D", [(1, 4, 2, 16, 32 * 2), (1, 2, 2, 128, 128), (2, 8, 2, 256, 128),
+                                          (1, 4, 1, 384, 64), (1, 2, 1, 200, 128), (1, 4, 4, 77, 64),
+                                          (1, 8, 2, 1024, 128)])
+@pytest.mark.parametrize("causal", [True, False])
+def test_sdpa_prefill(ops, B, Hq, Hkv, S, D, causal):
+    g = torch.Generator().manual_seed(51)
+    q = torch.randn(B, Hq, S, D, generator=g).to(BF)
+    k = torch.randn(B, Hkv, S, D, generator=g).to(BF)
+    v = torch.randn(B, Hkv, S, D, generator=g).to(BF)
+    out, lse = run(ops, q, k, v, causal)
+    ro, rl = cpu_ref(q, k, v, causal)
+    close(out, ro, 1.6e-2, 1e-2)   # bf16 contraction tolerance
+    close(lse, rl, 1e-3, 1e-3)
+
+
+def test_sdpa_golden_and_strided_inputs(ops, golden):
+    g = torch.Generator().manual_seed(52)
+    B, S, Hq, Hkv, D = 2, 160, 8, 2, 128
+    # q/k/v as views into one fused projection output (B,S,(Hq+2Hkv)*D), as the decoder layer produces
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * D, generator=g).to(BF)
+    dq = dev(qkv)
+    def heads(t, lo, n):
+        return t[:, :, lo * D:(lo + n) * D].view(B, S, n, D).transpose(1, 2)
+    q, k, v = heads(qkv, 0, Hq), heads(qkv, Hq, Hkv), heads(qkv, Hq + Hkv, Hkv)
+    out = torch.empty(B, S, Hq, D, dtype=BF, device=DEV).transpose(1, 2)
+    lse = torch.empty(B, Hq, S, device=DEV)
+    ops.sdpa_flash_fwd(out, lse, heads(dq, 0, Hq), heads(dq, Hq, Hkv), heads(dq, Hq + Hkv, Hkv), True)
+    ro, rl = aten_cpu.sdpa_causal(q, k, v)
+    close(out, ro, 1.6e-2, 1e-2)
+    close(lse, rl, 1e-3, 1e-3)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sk,D,Sq", [(3, 8, 2, 300, 128, 1), (2, 4, 4, 128, 64, 1), (2, 32, 8, 1000, 128, 1),
+                                              (1, 8, 2, 513, 128, 5)])
+def test_sdpa_decode_packed_heads(ops, B, Hq, Hkv, Sk, D, Sq):
+    """A few query positions against a long KV cache, is_causal=False: the query
+    heads of one KV group share a tile."""
+    g = torch.Generator().manual_seed(53)
+    q = torch.randn(B, Hq, Sq, D, generator=g).to(BF)
+    k = torch.randn(B, Hkv, Sk, D, generator=g).to(BF)
+    v = torch.randn(B, Hkv, Sk, D, generator=g).to(BF)
+    out = torch.empty(B, Sq, Hq, D, dtype=BF, device=DEV).transpose(1, 2)
+    lse = torch.empty(B, Hq, Sq, device=DEV)
+    # KV cache longer than the valid length: a strided slice
+    cache_k = torch.zeros(B, Hkv, Sk + 24, D, dtype=BF, device=DEV)
+    cache_v = torch.zeros(B, Hkv, Sk + 24, D, dtype=BF, device=DEV)
+    cache_k[:, :, :Sk] = dev(k)
+    cache_v[:, :, :Sk] = dev(v)
+    ops.sdpa_flash_fwd(out, lse, dev(q), cache_k[:, :, :Sk], cache_v[:, :, :Sk], False)
+    assert ops.device_error_fetch() == 0
+    ro, rl = cpu_ref(q, k, v, False)
+    close(out, ro, 1.6e-2, 1e-2)
+    close(lse, rl, 1e-3, 1e-3)
+
+
+def test_sdpa_golden(ops, golden):
+    s = golden("op_small")["sdpa"]
+    q = s["q"]
+    out = torch.empty(1, 16, 4, 32, dtype=BF, device=DEV).transpose(1, 2)
+    with pytest.raises(ops.B200Error):  # head dim 32: not a tensor-core shape of this kernel
+        ops.sdpa_flash_fwd(out, None, dev(q), dev(s["k"]), dev(s["v"]), True)

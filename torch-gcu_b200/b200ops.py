@@ -299,6 +299,12 @@ def baddbmm(out, self, a, b, beta=1.0, alpha=1.0, stream=None):
                              ctypes.c_double(alpha), _stream(stream)))
 
 
+def sdpa_flash_fwd(out, lse, q, k, v, is_causal, scale=None, stream=None):
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    check(lib().b200_sdpa_flash_fwd(_ref(view(out)), _ref(view(lse)), _ref(view(q)), _ref(view(k)), _ref(view(v)),
+                                    ctypes.c_int32(1 if is_causal else 0), ctypes.c_double(scale), _stream(stream)))
+
+
 def device_error_fetch():
     flags = ctypes.c_uint32(0)
     check(lib().b200_device_error_fetch(ctypes.byref(flags)))

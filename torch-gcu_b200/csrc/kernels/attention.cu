@@ -1,0 +1,426 @@
+// Scaled-dot-product attention forward (flash style) on tcgen05 tensor cores.
+//
+//   out = softmax(scale * Q K^T  [+ causal mask]) V,   lse = logsumexp rows
+//   q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D), D in {64,128}, Hq a multiple of Hkv (GQA),
+//   bf16 or f16, last dim contiguous, other strides free.
+//
+// One CTA per (128 query rows, head, batch); 192 threads:
+//   warp 0     TMA: Q tile once, then K / V tiles (128 keys) through a 2-stage ring
+//   warp 1     tcgen05.mma: S_j = Q K_j^T into one of two S buffers in tensor
+//              memory (so S_{j+1} is computed while the softmax of S_j runs), then
+//              O += P_j V_j; V is consumed straight from its row-major tile as an
+//              MN-major operand
+//   warps 2-5  online softmax, one thread per query row: two passes over the S row
+//              in tensor memory (max, then exp2 / sum), P_j written to shared
+//              memory in the 128-byte-swizzled K-major layout the second MMA reads,
+//              O rescaled in tensor memory only when a row maximum moved; at the
+//              end O / l is rounded and stored, with lse.
+// When the mask is not causal and groups*Sq <= 128 (decode), the query heads that
+// share one KV head are packed into the 128 rows of one tile, so every K / V byte
+// is read once per KV head instead of once per query head.
+// Every barrier wait is bounded; loads never use cluster multicast.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+#include <math_constants.h>
+
+namespace b200 {
+unsigned int* device_error_word();
+
+namespace {
+
+using namespace tc;
+
+constexpr int kAttThreads = 192;
+constexpr int BQ = 128;   // query rows per tile (MMA M)
+constexpr int BKV = 128;  // keys per tile
+constexpr int kKVStages = 2;
+
+struct AttnParams {
+  int B, Hq, Hkv, Sq, Sk, D;
+  int causal, packed, is_bf16;
+  float scale_log2;  // scale * log2(e)
+  float scale;
+  void* out;
+  int64_t o_sb, o_sh, o_ss;  // element strides of out (B,Hq,Sq,D), D contiguous
+  float* lse;                // (B,Hq,Sq) contiguous, may be null
+  unsigned int* error_word;
+};
+
+template <int D> struct AttCfg {
+  static constexpr int kHalves = D / 64;                 // 64-column (128-byte) slabs per row
+  static constexpr int kQBytes = BQ * D * 2;
+  static constexpr int kKVBytes = BKV * D * 2;
+  static constexpr int kPBytes = BQ * BKV * 2;
+  static constexpr int kSmem = kQBytes + kKVStages * 2 * kKVBytes + kPBytes + 1024 + 256;
+  static constexpr int kOCol = 2 * BKV;                  // O accumulator after the two S buffers
+  static constexpr int kTmemCols = 512;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kAttThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  using Cfg = AttCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Cfg::kQBytes;                      // [stage][K | V]
+  uint8_t* sP = sKV + kKVStages * 2 * Cfg::kKVBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + Cfg::kPBytes);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;             // [2]
+  uint64_t* v_full = bars + 3;             // [2]
+  uint64_t* kv_empty = bars + 5;           // [2]
+  uint64_t* s_full = bars + 7;             // [2]
+  uint64_t* s_empty = bars + 9;            // [2]
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  int q0, hq, hkv, b = blockIdx.z;
+  if (p.packed) {
+    q0 = 0; hkv = blockIdx.y; hq = hkv * G;
+  } else {
+    const int qt = gridDim.x - 1 - blockIdx.x;  // longest (last) causal tiles first
+    q0 = qt * BQ; hq = blockIdx.y; hkv = hq / G;
+  }
+  int n_kv = (p.Sk + BKV - 1) / BKV;
+  if (p.causal) n_kv = min(n_kv, (q0 + BQ + BKV - 1) / BKV);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      if (p.packed) {
+        // box (64, Sq, G, 1): rows ordered (group head, position); rest of the tile unused
+        mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(Cfg::kHalves * 128 * p.Sq * G));
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sQ + h * (BQ * 128), &tmap_q, q_full, h * 64, 0, hq, b);
+      } else {
+        mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sQ + h * (BQ * 128), &tmap_q, q_full, h * 64, q0, hq, b);
+      }
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1u) ^ 1u, abort_flag)) break;
+        uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
+        uint8_t* sV = sK + Cfg::kKVBytes;
+        mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, j * BKV, hkv, b);
+        mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, j * BKV, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BQ, BKV, p.is_bf16 != 0, false, false);  // Q, K both K-major
+      const uint32_t idesc_o = make_idesc(BQ, D, p.is_bf16 != 0, false, true);     // P K-major, V MN-major
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto issue_s = [&](int j) {
+        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * Cfg::kKVBytes);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((j & 1) * BKV);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * (BQ * 128) + (kk % 4) * 32;
+          umma_f16(d_tmem, smem_desc_sw128(q_addr + off, 16u, 1024u), smem_desc_sw128(k_addr + off, 16u, 1024u),
+                   idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag) && n_kv > 0;
+      if (ok) ok = mbar_wait(&k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int jn = j + 1;
+          if (!mbar_wait(&k_full[jn & 1], (jn >> 1) & 1u, abort_flag)) { ok = false; break; }
+          if (!mbar_wait(&s_empty[jn & 1], ((jn >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(jn);
+        }
+        if (!mbar_wait(p_full, j & 1u, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sKV + (j & 1) * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
+        const uint32_t o_tmem = tmem_base + Cfg::kOCol;
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          // A = P: key slab kk/4, 32 bytes per step. B = V: 64-column slabs BKV*128 bytes
+          // apart (LBO), 8-key groups 1024 bytes apart (SBO), 16 keys = 2048 bytes per step.
+          const uint64_t da = smem_desc_sw128(p_addr + (kk / 4) * (BQ * 128) + (kk % 4) * 32, 16u, 1024u);
+          const uint64_t db = smem_desc_sw128(v_addr + kk * 2048, BKV * 128, 1024u);
+          umma_f16(o_tmem, da, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[j & 1]);
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------------ softmax / output --
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;             // row of the tile this thread owns
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    int qi, head;                                  // query position / head of this row
+    bool row_valid;
+    if (p.packed) {
+      const int g = r / p.Sq;
+      qi = r - g * p.Sq; head = hq + g; row_valid = r < G * p.Sq;
+    } else {
+      qi = q0 + r; head = hq; row_valid = qi < p.Sq;
+    }
+    float m = -CUDART_INF_F, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int buf = j & 1;
+      const int k0 = j * BKV;
+      if (!mbar_wait(&s_full[buf], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_tmem = tmem_base + lane_sel + static_cast<uint32_t>(buf * BKV);
+      const bool need_mask = (p.causal && k0 + BKV - 1 > q0) || (k0 + BKV > p.Sk);
+      const int limit = p.causal ? min(p.Sk, qi + 1) : p.Sk;  // keys [0, limit) are visible
+      // pass 1: row maximum
+      float mx = -CUDART_INF_F;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_tmem + c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (need_mask && k0 + c + i >= limit) s = -CUDART_INF_F;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;
+      const float alpha = exp2f((m - m_use) * p.scale_log2);  // m = -inf -> 0
+      // P_{j-1} and the O accumulator are in use until the previous P.V finished
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, m_new > m)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 16) {
+            uint32_t o[16];
+            tmem_ld_32x16(tmem_base + lane_sel + Cfg::kOCol + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(tmem_base + lane_sel + Cfg::kOCol + c, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      // pass 2: p = exp2((s - m) * scale*log2e), row sum, P tile to shared memory
+      float sum = 0.f;
+      const float mb = m_use * p.scale_log2;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(s_tmem + c, v);
+        tmem_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+          float p0 = exp2f(fmaf(s0, p.scale_log2, -mb)), p1 = exp2f(fmaf(s1, p.scale_log2, -mb));
+          if (need_mask) {
+            if (k0 + c + i >= limit) p0 = 0.f;
+            if (k0 + c + i + 1 >= limit) p1 = 0.f;
+          }
+          // the sum uses the rounded values, the ones the P.V product sees
+          uint16_t b0, b1;
+          if (p.is_bf16) { b0 = f32_to_bf16_bits(p0); b1 = f32_to_bf16_bits(p1); sum += bf16_bits_to_f32(b0) + bf16_bits_to_f32(b1); }
+          else { b0 = f32_to_f16_bits(p0); b1 = f32_to_f16_bits(p1); sum += f16_bits_to_f32(b0) + f16_bits_to_f32(b1); }
+          packed[i / 2] = static_cast<uint32_t>(b0) | (static_cast<uint32_t>(b1) << 16);
+        }
+        // row r, keys [c, c+32): slab c/64, four 16-byte chunks, XOR-swizzled by (r & 7)
+        uint8_t* prow = sP + (c / 64) * (BQ * 128) + r * 128;
+        const int chunk0 = (c % 64) / 8;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int chunk = (chunk0 + q) ^ (r & 7);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) =
+              make_uint4(packed[q * 4], packed[q * 4 + 1], packed[q * 4 + 2], packed[q * 4 + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      // S_j consumed; P_j visible to the tensor core (async proxy); O rescaled
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[buf]);
+        mbar_arrive(p_full);
+      }
+    }
+    // epilogue: O / l
+    if (ok && n_kv > 0) ok = mbar_wait(pv_done, (n_kv - 1) & 1u, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(head) * p.o_sh +
+                       static_cast<int64_t>(qi) * p.o_ss;
+      const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        if (n_kv > 0) {
+          tmem_ld_32x32(tmem_base + lane_sel + Cfg::kOCol + c, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_valid) {
+          alignas(16) uint16_t o[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = __uint_as_float(v[i]) * inv;
+            o[i] = p.is_bf16 ? f32_to_bf16_bits(x) : f32_to_f16_bits(x);
+          }
+          if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<int4*>(orow + c + q * 8) = *reinterpret_cast<const int4*>(o + q * 8);
+          } else {
+            for (int i = 0; i < 32; ++i) orow[c + i] = o[i];
+          }
+        }
+      }
+      if (row_valid && p.lse) {
+        const float lse = l > 0.f ? m * p.scale + logf(l) : -CUDART_INF_F;
+        p.lse[(static_cast<int64_t>(b) * p.Hq + head) * p.Sq + qi] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
+bool make_qkv_map(CUtensorMap* m, const b200Tensor* t, uint32_t box_rows, uint32_t box_heads, const char** err) {
+  // t: (B, H, S, D) view; tensor-map dims innermost first: D, S, H, B
+  const uint64_t dims[4] = {(uint64_t)t->sizes[3], (uint64_t)t->sizes[2], (uint64_t)t->sizes[1], (uint64_t)t->sizes[0]};
+  auto st = [&](int d) { return static_cast<uint64_t>(t->sizes[d] == 1 ? t->sizes[3] * 8 : t->strides[d]) * 2; };
+  const uint64_t strides[3] = {st(2), st(1), st(0)};
+  const uint32_t box[4] = {64, box_rows, box_heads, 1};
+  return tc::encode_tmap_16bit(m, t->data, 4, dims, strides, box, err);
+}
+
+template <int D>
+b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200Tensor* v, AttnParams p, cudaStream_t s) {
+  using Cfg = AttCfg<D>;
+  CUtensorMap tq, tk, tv;
+  const char* err = "";
+  const int G = p.Hq / p.Hkv;
+  const bool q_ok = p.packed ? make_qkv_map(&tq, q, (uint32_t)p.Sq, (uint32_t)G, &err) : make_qkv_map(&tq, q, BQ, 1, &err);
+  B200_REQUIRE(q_ok && make_qkv_map(&tk, k, BKV, 1, &err) && make_qkv_map(&tv, v, BKV, 1, &err), B200_NOT_SUPPORTED,
+               "b200_sdpa_flash_fwd: %s", err);
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  dim3 grid;
+  if (p.packed) grid = dim3(1, p.Hkv, p.B);
+  else grid = dim3((p.Sq + BQ - 1) / BQ, p.Hq, p.B);
+  attention_fwd_kernel<D><<<grid, kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
+  return check_launch("b200_sdpa_flash_fwd");
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tensor* lse, const b200Tensor* q,
+                                          const b200Tensor* k, const b200Tensor* v, int32_t is_causal, double scale,
+                                          b200Stream stream) {
+  B200_REQUIRE(valid(out) && valid(q) && valid(k) && valid(v), B200_BAD_PARAM, "b200_sdpa_flash_fwd: invalid tensor view");
+  B200_REQUIRE(q->ndim == 4 && k->ndim == 4 && v->ndim == 4 && out->ndim == 4, B200_BAD_PARAM,
+               "b200_sdpa_flash_fwd: q, k, v, out must be (B,H,S,D)");
+  B200_REQUIRE((q->dtype == B200_BF16 || q->dtype == B200_F16) && k->dtype == q->dtype && v->dtype == q->dtype &&
+               out->dtype == q->dtype, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: bf16 or f16 operands of one dtype");
+  AttnParams p{};
+  p.B = (int)q->sizes[0]; p.Hq = (int)q->sizes[1]; p.Sq = (int)q->sizes[2]; p.D = (int)q->sizes[3];
+  p.Hkv = (int)k->sizes[1]; p.Sk = (int)k->sizes[2];
+  B200_REQUIRE(same_shape(out, q) && same_shape(k, v) && k->sizes[0] == p.B && k->sizes[3] == p.D, B200_BAD_PARAM,
+               "b200_sdpa_flash_fwd: shape mismatch");
+  B200_REQUIRE(p.Hkv > 0 && p.Hq % p.Hkv == 0, B200_BAD_PARAM, "b200_sdpa_flash_fwd: Hq must be a multiple of Hkv");
+  B200_REQUIRE(p.D == 64 || p.D == 128, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: head dim 64 or 128");
+  B200_REQUIRE(!is_causal || p.Sq == p.Sk, B200_NOT_SUPPORTED,
+               "b200_sdpa_flash_fwd: causal needs Sq == Sk (a single decode query attends everything: is_causal=0)");
+  if (numel(q) == 0) return B200_OK;
+  B200_REQUIRE(p.Sk > 0, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: empty key sequence");
+  for (const b200Tensor* t : {q, k, v, out}) {
+    B200_REQUIRE(t->strides[3] == 1 && reinterpret_cast<uintptr_t>(t->data) % 16 == 0, B200_NOT_SUPPORTED,
+                 "b200_sdpa_flash_fwd: last dim must be contiguous and the base 16-byte aligned");
+    for (int d = 0; d < 3; ++d)
+      B200_REQUIRE(t->sizes[d] == 1 || t->strides[d] % 8 == 0, B200_NOT_SUPPORTED,
+                   "b200_sdpa_flash_fwd: strides must be multiples of 8 elements");
+  }
+  if (lse) {
+    B200_REQUIRE(valid(lse) && lse->dtype == B200_F32 && is_contiguous(lse) && numel(lse) == (int64_t)p.B * p.Hq * p.Sq,
+                 B200_BAD_PARAM, "b200_sdpa_flash_fwd: lse must be contiguous f32 (B,Hq,Sq)");
+    p.lse = static_cast<float*>(lse->data);
+  }
+  p.causal = is_causal ? 1 : 0;
+  const int G = p.Hq / p.Hkv;
+  p.packed = (!p.causal && G * p.Sq <= BQ && p.Sq <= 256 && G <= 256 && (G == 1 || q->strides[1] > 0)) ? 1 : 0;
+  p.is_bf16 = q->dtype == B200_BF16;
+  p.scale = static_cast<float>(scale);
+  p.scale_log2 = static_cast<float>(scale * 1.4426950408889634);
+  p.out = out->data; p.o_sb = out->strides[0]; p.o_sh = out->strides[1]; p.o_ss = out->strides[2];
+  p.error_word = device_error_word();
+  B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: device error word unavailable");
+  B200_REQUIRE(p.B <= 65535 && p.Hq <= 65535, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: batch / heads too large");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p.D == 128) return launch_attention<128>(q, k, v, p, s);
+  return launch_attention<64>(q, k, v, p, s);
+}
