@@ -1,0 +1,140 @@
+// Flash attention forward, the SDPA backend choice, and the fused efficient ops
+// (reference: aot_ops/gcu_attention.cpp:21-80, shape_inference/attention.cpp:
+// 67-192,424-446, RegisterSPDA.cpp:137-178,223-275; the fused RMSNorm+residual,
+// RoPE and SwiGLU entries have no reference kernel -- the reference runs them as
+// chains of pointwise ops -- and sit beside its one efficient op,
+// efficient_ops/ops.cpp:335-342).
+#include <ATen/native/transformers/sdp_utils_cpp.h>
+#include <torch/library.h>
+
+#include "aten/aot_ops.h"
+#include "aten/bridge.h"
+
+namespace torch_gcu {
+namespace aotops {
+
+std::tuple<at::Tensor, at::Tensor> sdpa_flash(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, bool is_causal,
+                                              std::optional<double> scale) {
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "flash attention expects (B,H,S,D) query, key and value");
+  const int64_t B = q.size(0), H = q.size(1), S = q.size(2), D = q.size(3);
+  // allocated (B,S,H,D) and returned transposed, as the reference's shape inference does
+  at::Tensor out = at::empty({B, S, H, D}, q.options()).transpose(1, 2);
+  at::Tensor lse = at::empty({B, H, S}, q.options().dtype(at::kFloat));
+  if (q.numel() == 0) return std::make_tuple(out, lse);
+  auto last_contig = [](const at::Tensor& t) { return t.stride(-1) == 1 ? t : t.contiguous(); };
+  at::Tensor qc = last_contig(q), kc = last_contig(k), vc = last_contig(v);
+  b200Tensor vo = to_b200(out), vl = to_b200(lse), vq = to_b200(qc), vk = to_b200(kc), vv = to_b200(vc);
+  const double sc = scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(D));
+  cudaStream_t stream = current_stream(q);
+  GCU_KERNEL_CALL(b200_sdpa_flash_fwd, stream, &vo, &vl, &vq, &vk, &vv, is_causal ? 1 : 0, sc);
+  return std::make_tuple(out, lse);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, c10::SymInt, c10::SymInt, at::Tensor, at::Tensor, at::Tensor>
+_scaled_dot_product_flash_attention(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, double dropout_p,
+                                    bool is_causal, bool return_debug_mask, std::optional<double> scale) {
+  TORCH_CHECK(dropout_p == 0.0, "flash attention on the gcu backend does not implement dropout");
+  TORCH_CHECK(!return_debug_mask, "flash attention on the gcu backend has no debug mask");
+  auto [out, lse] = sdpa_flash(query, key, value, is_causal, scale);
+  at::Tensor empty_long = at::empty({0}, query.options().dtype(at::kLong));
+  at::Tensor none;
+  return std::make_tuple(out, lse, at::Tensor(), at::Tensor(), c10::SymInt(query.size(2)), c10::SymInt(key.size(2)),
+                         empty_long, empty_long.clone(), at::empty({0}, query.options()));
+}
+
+// --------------------------------------------------------------- fused ops --
+std::tuple<at::Tensor, at::Tensor> rms_norm_residual(const at::Tensor& x, const std::optional<at::Tensor>& residual,
+                                                     const at::Tensor& weight, double eps) {
+  TORCH_CHECK(x.dim() >= 1 && weight.dim() == 1 && weight.size(0) == x.size(-1), "rms_norm_residual: weight must be (hidden,)");
+  at::Tensor xc = x.contiguous();
+  at::Tensor w = weight.scalar_type() == x.scalar_type() ? weight.contiguous() : weight.to(x.scalar_type()).contiguous();
+  at::Tensor y = at::empty_like(xc);
+  const c10::OptionalDeviceGuard guard(x.device());
+  cudaStream_t stream = current_stream(x);
+  b200Tensor vy = to_b200(y), vx = to_b200(xc), vw = to_b200(w);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->sizes() == x.sizes() && residual->scalar_type() == x.scalar_type(),
+                "rms_norm_residual: residual must match x");
+    at::Tensor rc = residual->contiguous();
+    at::Tensor h = at::empty_like(xc);
+    b200Tensor vr = to_b200(rc), vh = to_b200(h);
+    GCU_KERNEL_CALL(b200_rms_norm_residual, stream, &vy, &vh, &vx, &vr, &vw, eps);
+    return std::make_tuple(y, h);
+  }
+  GCU_KERNEL_CALL(b200_rms_norm_residual, stream, &vy, static_cast<const b200Tensor*>(nullptr), &vx,
+                  static_cast<const b200Tensor*>(nullptr), &vw, eps);
+  return std::make_tuple(y, xc);
+}
+
+at::Tensor rope(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& sin, const std::optional<at::Tensor>& positions,
+                bool inplace) {
+  TORCH_CHECK(x.dim() == 4, "rope: x must be (B,S,H,D)");
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat, "rope: cos/sin tables must be float32 (P, D/2)");
+  const c10::OptionalDeviceGuard guard(x.device());
+  at::Tensor src = x.stride(-1) == 1 ? x : x.contiguous();
+  at::Tensor out = inplace && src.is_same(x) ? x : at::empty_like(src, at::MemoryFormat::Contiguous);
+  at::Tensor c = cos.contiguous(), s = sin.contiguous();
+  b200Tensor vo = to_b200(out), vx = to_b200(src), vc = to_b200(c), vs = to_b200(s), vp;
+  at::Tensor pos;
+  if (positions.has_value() && positions->defined()) {
+    pos = positions->to(x.device(), at::kLong);
+    vp = to_b200(pos);
+  }
+  cudaStream_t stream = current_stream(x);
+  GCU_KERNEL_CALL(b200_rope, stream, &vo, &vx, &vc, &vs, pos.defined() ? &vp : static_cast<const b200Tensor*>(nullptr));
+  return out;
+}
+
+static at::Tensor swiglu_2d(const at::Tensor& gate, const at::Tensor& up, at::IntArrayRef out_shape) {
+  at::Tensor out = at::empty(out_shape, gate.options());
+  if (out.numel() == 0) return out;
+  const int64_t cols = out_shape.back();
+  at::Tensor o2 = out.view({-1, cols});
+  b200Tensor vo = to_b200(o2), vg = to_b200(gate), vu = to_b200(up);
+  const c10::OptionalDeviceGuard guard(gate.device());
+  cudaStream_t stream = current_stream(gate);
+  GCU_KERNEL_CALL(b200_swiglu, stream, &vo, &vg, &vu);
+  return out;
+}
+
+at::Tensor swiglu(const at::Tensor& gate, const at::Tensor& up) {
+  TORCH_CHECK(gate.sizes() == up.sizes() && gate.scalar_type() == up.scalar_type() && gate.dim() >= 1,
+              "swiglu: gate and up must agree in shape and dtype");
+  const int64_t cols = gate.size(-1);
+  at::Tensor g = gate.contiguous().view({-1, cols}), u = up.contiguous().view({-1, cols});
+  return swiglu_2d(g, u, gate.sizes());
+}
+
+// gate and up as the two halves of one projection output (..., 2F)
+at::Tensor swiglu_packed(const at::Tensor& gate_up) {
+  TORCH_CHECK(gate_up.dim() >= 1 && gate_up.size(-1) % 2 == 0, "swiglu_packed: last dim must be even");
+  const int64_t f = gate_up.size(-1) / 2;
+  at::Tensor gu = gate_up.contiguous().view({-1, 2 * f});
+  std::vector<int64_t> shape = gate_up.sizes().vec();
+  shape.back() = f;
+  return swiglu_2d(gu.narrow(1, 0, f), gu.narrow(1, f, f), shape);
+}
+
+// ------------------------------------------------------ SDPA backend choice --
+// flash when the kernel can take the problem, otherwise the math composite
+// (reference priority flash -> mem-efficient -> math, RegisterSPDA.cpp:223-275;
+// flash gate :137-178).
+static int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                const std::optional<at::Tensor>& attn_mask, double dropout_p, bool is_causal,
+                                std::optional<double>, bool) {
+  const bool has_mask = attn_mask.has_value() && attn_mask->defined();
+  const auto dt = query.scalar_type();
+  const bool flash_ok = !has_mask && dropout_p == 0.0 && query.dim() == 4 && key.dim() == 4 && value.dim() == 4 &&
+                        (dt == at::kBFloat16 || dt == at::kHalf) && key.scalar_type() == dt && value.scalar_type() == dt &&
+                        (query.size(-1) == 64 || query.size(-1) == 128) && key.size(-1) == query.size(-1) &&
+                        value.size(-1) == query.size(-1) && key.size(1) > 0 && query.size(1) % key.size(1) == 0 &&
+                        (!is_causal || query.size(2) == key.size(2)) && !query.requires_grad() && key.size(2) > 0;
+  return static_cast<int64_t>(flash_ok ? sdp::SDPBackend::flash_attention : sdp::SDPBackend::math);
+}
+
+}  // namespace aotops
+}  // namespace torch_gcu
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  m.impl("_fused_sdp_choice", TORCH_FN(torch_gcu::aotops::fused_sdp_choice));
+}

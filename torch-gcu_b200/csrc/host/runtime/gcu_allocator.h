@@ -1,0 +1,114 @@
+// Stream-ordered caching allocator for device memory, and the pinned host
+// allocator. It replaces the reference's block-splitting caching allocator
+// (reference: torch_gcu/csrc/gcu/gcu_caching_allocator.{h:231-305,cpp:593,815})
+// with a design that leans on stream order:
+//   * a freed block goes back to a per-stream cache and is handed out again to
+//     the same stream with no synchronisation and no driver call (work on one
+//     stream is ordered, so reuse is safe by construction);
+//   * a cache miss calls the backend's stream-ordered allocation
+//     (cudaMallocAsync from the device's pool, release threshold unlimited);
+//   * a block that other streams touched (recordStream) is parked until events
+//     recorded on those streams have completed;
+//   * out of memory: cached blocks are returned to the backend and the request
+//     retried once before an OutOfMemoryError is raised.
+// The device backend is an interface so the policy can be unit-tested on a
+// machine without a GPU against a fake backend.
+#pragma once
+
+#include <c10/core/Allocator.h>
+#include <c10/core/Device.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <deque>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+namespace torch_gcu {
+
+struct DeviceStats {
+  int64_t allocated_bytes = 0, allocated_bytes_peak = 0;  // handed out to tensors
+  int64_t reserved_bytes = 0, reserved_bytes_peak = 0;    // handed out + cached
+  int64_t num_allocs = 0, num_cache_hits = 0, num_backend_allocs = 0, num_backend_frees = 0;
+  int64_t num_alloc_retries = 0, num_ooms = 0, num_deferred_frees = 0;
+};
+
+// What the allocator needs from the device runtime.
+class MemoryBackend {
+ public:
+  virtual ~MemoryBackend() = default;
+  virtual void* alloc(int device, size_t bytes, cudaStream_t stream) = 0;  // nullptr when out of memory
+  virtual void free(int device, void* ptr, cudaStream_t stream) = 0;
+  virtual void* record_event(int device, cudaStream_t stream) = 0;         // opaque event handle
+  virtual bool event_done(void* event) = 0;
+  virtual void destroy_event(void* event) = 0;
+  virtual void synchronize(int device) = 0;
+};
+std::unique_ptr<MemoryBackend> make_cuda_backend();
+
+class StreamOrderedCachingAllocator {
+ public:
+  explicit StreamOrderedCachingAllocator(std::unique_ptr<MemoryBackend> backend);
+  ~StreamOrderedCachingAllocator();
+  void* malloc(int device, size_t bytes, cudaStream_t stream);
+  void free(void* ptr);
+  void record_stream(void* ptr, cudaStream_t stream);
+  void empty_cache();
+  DeviceStats stats(int device);
+  void reset_peak_stats(int device);
+  static size_t round_size(size_t bytes);
+
+ private:
+  struct Block {
+    void* ptr;
+    size_t size;
+    int device;
+    cudaStream_t stream;
+    std::vector<cudaStream_t> other_streams;
+    int pending_events = 0;
+  };
+  using Key = std::pair<cudaStream_t, size_t>;
+  struct PerDevice {
+    std::multimap<Key, Block*> cache;
+    DeviceStats stats;
+  };
+  void process_pending_locked();
+  void release_cached_locked(int device);
+  PerDevice& dev(int device);
+
+  std::unique_ptr<MemoryBackend> backend_;
+  std::mutex mutex_;
+  std::unordered_map<void*, Block*> live_;
+  std::unordered_map<int, PerDevice> devices_;
+  std::deque<std::pair<void*, Block*>> pending_;  // (event, block)
+};
+
+// The process-wide device allocator registered with c10 for PrivateUse1.
+class GCUDeviceAllocator final : public c10::Allocator {
+ public:
+  c10::DataPtr allocate(size_t nbytes) override;
+  c10::DeleterFnPtr raw_deleter() const override;
+  void copy_data(void* dest, const void* src, std::size_t count) const override;
+  static GCUDeviceAllocator* get();
+  StreamOrderedCachingAllocator& impl();
+  void record_stream(const c10::DataPtr& ptr, cudaStream_t stream);
+};
+
+// Pinned host memory (reference: gcu_caching_host_allocator.cpp): blocks are
+// cached by size and reused once the copies that used them have completed.
+class GCUHostAllocator final : public c10::Allocator {
+ public:
+  c10::DataPtr allocate(size_t nbytes) override;
+  c10::DeleterFnPtr raw_deleter() const override;
+  void copy_data(void* dest, const void* src, std::size_t count) const override;
+  static GCUHostAllocator* get();
+  // Notes that an async copy on `stream` reads or writes the pinned block at ptr.
+  void record_event(void* ptr, cudaStream_t stream);
+  bool is_pinned(const void* ptr);
+  void empty_cache();
+};
+
+}  // namespace torch_gcu

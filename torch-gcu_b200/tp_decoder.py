@@ -1,0 +1,184 @@
+"""Tensor-parallel Llama-style decoder harness (benchmark / test code, not a
+reference component: the reference ships no model code, only the communication
+backend that tensor parallelism is built on).
+
+One layer: RMSNorm -> fused QKV projection (column-parallel) -> RoPE -> causal
+GQA attention -> o_proj (row-parallel, all-reduce) -> residual + RMSNorm ->
+gate/up projection (column-parallel) -> SwiGLU -> down projection (row-parallel,
+all-reduce) -> residual. Heads and FFN columns are sharded over `tp` ranks;
+activations are replicated; the KV cache shards with the KV heads.
+
+backend "gcu": every operator runs through the registered PrivateUse1 kernels
+(mm, the fused efficient ops, flash attention, add) and the all-reduce through
+the registered "eccl" process group. backend "cpu": the same computation in
+plain fp32 torch, used by the gloo sharding test and as the CPU baseline.
+"""
+import torch
+import torch.nn.functional as F
+
+
+def _rope_cpu(x, cos, sin, positions=None):
+    B, S = x.shape[0], x.shape[1]
+    if positions is None:
+        positions = torch.arange(S).expand(B, S)
+    c = torch.cat((cos, cos), -1)[positions][:, :, None, :]
+    s = torch.cat((sin, sin), -1)[positions][:, :, None, :]
+    d = x.shape[-1] // 2
+    rot = torch.cat((-x[..., d:], x[..., :d]), -1)
+    return (x.float() * c + rot.float() * s).to(x.dtype)
+
+
+def _rms_cpu(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def rope_tables_cpu(n, head_dim, theta=10000.0):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    fr = torch.outer(torch.arange(n, dtype=torch.float32), inv)
+    return fr.cos().contiguous(), fr.sin().contiguous()
+
+
+def reference_layer_cpu(x, w, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0):
+    """Unsharded layer in plain torch on the CPU (fp32 math on the given weights)."""
+    B, S, _ = x.shape
+    cos, sin = rope_tables_cpu(S, head_dim, theta)
+    h = _rms_cpu(x, w["norm1"], eps)
+    qkv = h.float() @ w["wqkv"].float().t()
+    q, k, v = qkv.split([heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], -1)
+    q = _rope_cpu(q.view(B, S, heads, head_dim), cos, sin).transpose(1, 2)
+    k = _rope_cpu(k.view(B, S, kv_heads, head_dim), cos, sin).transpose(1, 2)
+    v = v.view(B, S, kv_heads, head_dim).transpose(1, 2)
+    g = heads // kv_heads
+    att = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
+    o = att.transpose(1, 2).reshape(B, S, heads * head_dim) @ w["wo"].float().t()
+    r = x.float() + o
+    h2 = _rms_cpu(r, w["norm2"], eps)
+    gu = h2 @ w["wgu"].float().t()
+    gate, up = gu.split(ffn, -1)
+    return r + (F.silu(gate) * up) @ w["wd"].float().t()
+
+
+class DecoderLayer:
+    def __init__(self, weights, tp, backend, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0,
+                 device=None):
+        assert heads % tp == 0 and kv_heads % tp == 0 and ffn % tp == 0
+        self.tp, self.backend, self.eps, self.theta = tp, backend, eps, theta
+        self.hidden, self.head_dim = hidden, head_dim
+        self.hq, self.hk, self.f = heads // tp, kv_heads // tp, ffn // tp
+        self.device = device
+        self.w = {k: (v.to(device) if device is not None else v) for k, v in weights.items()}
+        self._tables = {}
+        if backend == "gcu":
+            from torch_gcu.gcu import efficient
+            self.eff = efficient
+
+    def tables(self, n):
+        if n not in self._tables:
+            cos, sin = rope_tables_cpu(n, self.head_dim, self.theta)
+            if self.device is not None:
+                cos, sin = cos.to(self.device), sin.to(self.device)
+            self._tables[n] = (cos, sin)
+        return self._tables[n]
+
+    def _allreduce(self, t, group):
+        if self.tp > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=group)
+        return t
+
+    # ------------------------------------------------------------- prefill --
+    def forward_prefill(self, x, group=None, kv_out=None):
+        B, S, H = x.shape
+        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
+        cos, sin = self.tables(S)
+        if self.backend == "gcu":
+            eff = self.eff
+            h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
+            qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
+            q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+            eff.rope(q, cos, sin, None, True)
+            eff.rope(k, cos, sin, None, True)
+            if kv_out is not None:
+                kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
+                kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
+            att, _ = eff.sdpa_flash(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True)
+            o = torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t())
+            self._allreduce(o, group)
+            h2, r = eff.rms_norm_residual(o.view(B, S, H), x, w["norm2"], self.eps)
+            gu = torch.mm(h2.view(B * S, H), w["wgu"].t())
+            act = eff.swiglu_packed(gu)
+            down = torch.mm(act, w["wd"].t())
+            self._allreduce(down, group)
+            return torch.add(down.view(B, S, H), r)
+        # plain torch (fp32 math on whatever dtype the weights have)
+        h = _rms_cpu(x, w["norm1"], self.eps)
+        qkv = (h.float() @ w["wqkv"].float().t()).view(B, S, hq + 2 * hk, d)
+        q = _rope_cpu(qkv[:, :, :hq], cos, sin).transpose(1, 2)
+        k = _rope_cpu(qkv[:, :, hq:hq + hk], cos, sin).transpose(1, 2)
+        v = qkv[:, :, hq + hk:].transpose(1, 2)
+        g = hq // hk
+        att = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
+        o = att.transpose(1, 2).reshape(B, S, hq * d) @ w["wo"].float().t()
+        self._allreduce(o, group)
+        r = x.float() + o
+        h2 = _rms_cpu(r, w["norm2"], self.eps)
+        gu = h2 @ w["wgu"].float().t()
+        down = (F.silu(gu[..., :self.f]) * gu[..., self.f:]) @ w["wd"].float().t()
+        self._allreduce(down, group)
+        return r + down
+
+    # -------------------------------------------------------------- decode --
+    def forward_decode(self, x, kv, pos, group=None):
+        """One new token per sequence: x (B,1,hidden); kv = (k_cache, v_cache), each
+        (B, kv_heads/tp, T, D); the new K/V rows go to position `pos`, attention
+        covers [0, pos]."""
+        B, _, H = x.shape
+        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
+        cos, sin = self.tables(kv[0].shape[2])
+        assert self.backend == "gcu"
+        eff = self.eff
+        h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
+        qkv = torch.mm(h.view(B, H), w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+        positions = self._positions(B, pos)
+        eff.rope(q, cos, sin, positions, True)
+        eff.rope(k, cos, sin, positions, True)
+        kv[0][:, :, pos:pos + 1].copy_(k.transpose(1, 2))   # strided device copy into the cache slice
+        kv[1][:, :, pos:pos + 1].copy_(v.transpose(1, 2))
+        att, _ = eff.sdpa_flash(q.transpose(1, 2), kv[0][:, :, :pos + 1], kv[1][:, :, :pos + 1], False)
+        o = torch.mm(att.transpose(1, 2).reshape(B, hq * d), w["wo"].t())
+        self._allreduce(o, group)
+        h2, r = eff.rms_norm_residual(o.view(B, 1, H), x, w["norm2"], self.eps)
+        gu = torch.mm(h2.view(B, H), w["wgu"].t())
+        act = eff.swiglu_packed(gu)
+        down = torch.mm(act, w["wd"].t())
+        self._allreduce(down, group)
+        return torch.add(down.view(B, 1, H), r)
+
+    def _positions(self, B, pos):
+        key = ("pos", B, pos)
+        if key not in self._tables:
+            p = torch.full((B, 1), pos, dtype=torch.int64)
+            self._tables[key] = p.to(self.device) if self.device is not None else p
+        return self._tables[key]
+
+
+class DecoderStack:
+    """`n_layers` layers with independent random-init weights (seed = layer index)."""
+
+    def __init__(self, n_layers, tp, rank, backend, device, dtype, cfg):
+        import workloads
+        self.layers = [DecoderLayer(workloads.decoder_layer_weights(seed=i, dtype=dtype, tp=tp, rank=rank, **cfg), tp,
+                                    backend, device=device, **cfg) for i in range(n_layers)]
+        self.cfg, self.tp = cfg, tp
+
+    def prefill(self, x, group=None, caches=None):
+        for i, layer in enumerate(self.layers):
+            x = layer.forward_prefill(x, group, None if caches is None else caches[i])
+        return x
+
+    def decode(self, x, caches, pos, group=None):
+        for layer, kv in zip(self.layers, caches):
+            x = layer.forward_decode(x, kv, pos, group)
+        return x
