@@ -220,12 +220,11 @@ def test_streams_events_and_allocator(dev):
     assert torch.gcu.memory_allocated() > 0 and torch.gcu.max_memory_allocated() >= torch.gcu.memory_allocated()
     del t2, a, b
     torch.gcu.empty_cache()
-    pin = torch.randn(1000).pin_memory("gcu") if hasattr(torch.Tensor, "pin_memory") else None
-    if pin is not None:
-        assert pin.is_pinned("gcu")
-        d = pin.to(dev, non_blocking=True)
-        torch.gcu.synchronize()
-        assert torch.equal(d.cpu(), pin)
+    pin = torch.randn(1000).pin_memory()
+    assert pin.is_pinned()
+    d = pin.to(dev, non_blocking=True)
+    torch.gcu.synchronize()
+    assert torch.equal(d.cpu(), pin)
 
 
 def test_unsupported_operator_raises(dev):

@@ -1,0 +1,248 @@
+"""Operator sweep of the benchmark: BASELINE configurations 1-3 (the fp32
+(4096,4096) op sweep, the index ops on the bf16 (128256,4096) table, the fused
+bf16 RMSNorm / RoPE / SwiGLU ops), every operator called through the C ABI of
+libb200ops.so with its full-size seeded inputs resident in HBM.
+
+Timing: NSETS independent copies of every operator's buffers are used round-robin,
+one CUDA-event pair around NSETS back-to-back launches, so no launch finds its
+operands in the 126 MB L2 (between two uses of one buffer set the other sets
+stream at least 3x its footprint). Algorithmic bytes per call are the compulsory
+reads + writes of the user-visible tensors.
+"""
+import os
+import time
+
+import torch
+
+NSETS = 4
+
+class Op:
+    def __init__(self, name, nbytes, launches, gpu_inputs, gpu_run, cpu_run, host_inputs, result):
+        self.name = name
+        self.bytes = nbytes          # algorithmic bytes per call
+        self.launches = launches     # kernels (or copy nodes) per call
+        self.gpu_inputs = gpu_inputs  # dict name -> device tensor (mutable, for e2e)
+        self.gpu_run = gpu_run       # () -> None, enqueues on the current stream
+        self.cpu_run = cpu_run       # () -> tensor, CPU ATen
+        self.host_inputs = host_inputs  # dict name -> CPU tensor (pinned lazily)
+        self.result = result         # () -> device tensor holding the result
+
+
+def nbytes(*ts):
+    return sum(t.numel() * t.element_size() for t in ts)
+
+
+def make_data(scale=1.0):
+    """Seeded CPU tensors of configs 1-3. scale < 1 shrinks the row counts (used
+    by the bounded CPU sample only; the GPU arm always runs scale 1)."""
+    import workloads
+    R = lambda n: max(8, int(n * scale))  # noqa: E731
+    return dict(sw=workloads.op_sweep(rows=R(4096)),
+                ix=workloads.index_ops(vocab=R(128256), seq=R(2048), n_select=R(65536), gather_rows=R(8192),
+                                       scatter_src=R(262144), scatter_dst=R(65536)),
+                fu=workloads.fused_ops(tokens=R(16384), seq=R(2048)))
+
+
+def build_ops(dev, data, want_gpu=True):
+    """The operator list of one pass over `data`, with its own device buffers."""
+    from oracle import aten_cpu as cpu  # used ONLY inside the cpu_run closures (CPU baseline leg)
+    ops_mod = None
+    if want_gpu:
+        import b200ops as ops_mod
+    out = []
+    import ctypes
+    cd, ci64, ci32, csz = ctypes.c_double, ctypes.c_int64, ctypes.c_int32, ctypes.c_size_t
+
+    def i64s(v):
+        return (ctypes.c_int64 * len(v))(*v)
+
+    def B(name, *a, keep=()):
+        # pre-marshalled C-ABI call (GPU arm only; the CPU arm never invokes it)
+        return ops_mod.bind(name, *a, keep=keep) if want_gpu else None
+
+    def wsa(w_):
+        return ops_mod.ws_args(w_) if want_gpu else (None, None)
+
+    def to_dev(d):
+        if not want_gpu:
+            import collections
+            return collections.defaultdict(lambda: None)
+        return {k: v.to(dev) for k, v in d.items() if torch.is_tensor(v)}
+
+    # ---- config 1: fp32 op sweep ------------------------------------------
+    sw = data["sw"]
+    a, b, w, bias = sw["a"], sw["b"], sw["weight"], sw["bias"]
+    rows, cols = a.shape
+    g = to_dev(dict(a=a, b=b, w=w, bias=bias))
+    if want_gpu:
+        o32 = torch.empty_like(g["a"])
+        o16 = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev)
+        a16 = g["a"].to(torch.bfloat16)
+        osum = torch.empty(rows, device=dev)
+        mean = torch.empty(rows, device=dev)
+        rstd = torch.empty(rows, device=dev)
+    else:
+        o32 = o16 = a16 = osum = mean = rstd = None
+    a16_cpu = a.to(torch.bfloat16)
+    out.append(Op("add", 3 * nbytes(a), 1, g, B("add", o32, g["a"], g["b"], cd(1.0)),
+                  lambda: cpu.add(a, b), dict(a=a, b=b), lambda: o32))
+    out.append(Op("mul", 3 * nbytes(a), 1, g, B("mul", o32, g["a"], g["b"]),
+                  lambda: cpu.mul(a, b), dict(a=a, b=b), lambda: o32))
+    out.append(Op("silu", 2 * nbytes(a), 1, g, B("silu", o32, g["a"]),
+                  lambda: cpu.silu(a), dict(a=a), lambda: o32))
+    out.append(Op("cast_f32_bf16", nbytes(a) + nbytes(a) // 2, 1, g, B("copy", o16, g["a"]),
+                  lambda: cpu.cast(a, torch.bfloat16), dict(a=a), lambda: o16))
+    g16 = dict(a=a16)  # a16 is None on the CPU arm
+    out.append(Op("cast_bf16_f32", nbytes(a) + nbytes(a) // 2, 1, g16, B("copy", o32, g16["a"]),
+                  lambda: cpu.cast(a16_cpu, torch.float32), dict(a=a16_cpu), lambda: o32))
+    out.append(Op("sum_lastdim", nbytes(a) + rows * 4, 1, g, B("sum", osum, g["a"], i64s([1]), ci32(1), ci32(0), None, csz(0)),
+                  lambda: cpu.sum_dim(a, [-1]), dict(a=a), lambda: osum))
+    out.append(Op("softmax_lastdim", 2 * nbytes(a), 1, g, B("softmax", o32, g["a"], ci64(1)),
+                  lambda: cpu.softmax(a, -1), dict(a=a), lambda: o32))
+    out.append(Op("layer_norm", 2 * nbytes(a) + 2 * cols * 4 + 2 * rows * 4, 1, g,
+                  B("native_layer_norm", o32, mean, rstd, g["a"], ci64(rows), ci64(cols), g["w"], g["bias"], cd(1e-5)),
+                  lambda: cpu.native_layer_norm(a, (cols,), w, bias, 1e-5)[0], dict(a=a, w=w, bias=bias),
+                  lambda: o32))
+
+    # ---- config 2: index ops ------------------------------------------------
+    ix = data["ix"]
+    table, ids, sel = ix["table"], ix["ids"], ix["select_idx"]
+    gsrc, gidx, svals, srows = ix["gather_src"], ix["gather_idx"], ix["scatter_vals"], ix["scatter_rows"]
+    n_dst, scols = ix["scatter_dst"], ix["scatter_cols"]
+    gi = to_dev(dict(table=table, ids=ids.reshape(-1), sel=sel, gsrc=gsrc, gidx=gidx, svals=svals, srows=srows))
+    hidden = table.shape[1]
+    zeros_cpu = torch.zeros(n_dst, scols)
+    if want_gpu:
+        emb_out = torch.empty(ids.numel(), hidden, dtype=torch.bfloat16, device=dev)
+        sel_out = torch.empty(sel.numel(), hidden, dtype=torch.bfloat16, device=dev)
+        gat_out = torch.empty_like(gi["gsrc"])
+        gi["zeros"] = torch.zeros(n_dst, scols, device=dev)
+        sc_out = torch.empty(n_dst, scols, device=dev)
+        sidx = gi["srows"][:, None].expand(-1, scols)
+        ws = torch.empty(ops_mod.scatter_add_workspace_size(gi["zeros"], 0, sidx, gi["svals"]), dtype=torch.uint8,
+                         device=dev)
+        ip_self = torch.zeros(n_dst, scols, device=dev)
+
+        _ip = B("index_put", ip_self, gi["srows"], gi["svals"], ci32(1), *wsa(ws), keep=(ws,))
+
+        def run_index_put():
+            ip_self.zero_()  # restore the accumulator (a memset node, counted as a launch)
+            _ip()
+    else:
+        emb_out = sel_out = gat_out = sc_out = sidx = ws = ip_self = run_index_put = None
+    out.append(Op("embedding", 2 * ids.numel() * hidden * 2 + nbytes(ids), 1, gi,
+                  B("index_select", emb_out, gi["table"], ci64(0), gi["ids"]),
+                  lambda: cpu.embedding(table, ids), dict(table=table, ids=ids.reshape(-1)), lambda: emb_out))
+    out.append(Op("index_select", 2 * sel.numel() * hidden * 2 + nbytes(sel), 1, gi,
+                  B("index_select", sel_out, gi["table"], ci64(0), gi["sel"]),
+                  lambda: cpu.index_select(table, 0, sel), dict(table=table, sel=sel), lambda: sel_out))
+    out.append(Op("gather", nbytes(gidx) + 2 * nbytes(gsrc), 1, gi,
+                  B("gather", gat_out, gi["gsrc"], ci64(1), gi["gidx"]),
+                  lambda: cpu.gather(gsrc, 1, gidx), dict(gsrc=gsrc, gidx=gidx), lambda: gat_out))
+    sc_bytes = nbytes(svals) + nbytes(srows) + 2 * n_dst * scols * 4
+    out.append(Op("scatter_add", sc_bytes, 7, gi,
+                  B("scatter_add", sc_out, gi["zeros"], ci64(0), sidx, gi["svals"], *wsa(ws), keep=(ws,)),
+                  lambda: cpu.scatter_add(zeros_cpu, 0, srows[:, None].expand(-1, scols), svals),
+                  dict(svals=svals, srows=srows, zeros=zeros_cpu), lambda: sc_out))
+    out.append(Op("index_put_accumulate", sc_bytes, 8, gi, run_index_put,
+                  lambda: cpu.index_put(zeros_cpu, [srows], svals, True),
+                  dict(svals=svals, srows=srows), lambda: ip_self))
+
+    # ---- config 3: fused bf16 inference ops ---------------------------------
+    fu = data["fu"]
+    x, res, wn, q, k, gate, up, cos, sin = (fu[n] for n in ("x", "res", "weight", "q", "k", "gate", "up", "cos", "sin"))
+    gf = to_dev(dict(x=x, res=res, wn=wn, q=q, k=k, gate=gate, up=up, cos=cos, sin=sin))
+    if want_gpu:
+        y = torch.empty_like(gf["x"])
+        hres = torch.empty_like(gf["x"])
+        qo, ko = torch.empty_like(gf["q"]), torch.empty_like(gf["k"])
+        so = torch.empty_like(gf["gate"])
+
+        _rq = B("rope", qo, gf["q"], gf["cos"], gf["sin"], None)
+        _rk = B("rope", ko, gf["k"], gf["cos"], gf["sin"], None)
+
+        def run_rope():
+            _rq()
+            _rk()
+    else:
+        y = hres = qo = ko = so = run_rope = None
+    out.append(Op("rms_norm_residual", 4 * nbytes(x) + nbytes(wn), 1, gf,
+                  B("rms_norm_residual", y, hres, gf["x"], gf["res"], gf["wn"], cd(1e-6)),
+                  lambda: cpu.rms_norm_residual(x, res, wn, 1e-6)[0], dict(x=x, res=res, wn=wn), lambda: y))
+    out.append(Op("rope_q_k", 2 * (nbytes(q) + nbytes(k)), 2, gf, run_rope,
+                  lambda: (cpu.rope(q, cos, sin), cpu.rope(k, cos, sin))[0], dict(q=q, k=k, cos=cos, sin=sin),
+                  lambda: qo))
+    out.append(Op("swiglu", 3 * nbytes(gate), 1, gf, B("swiglu", so, gf["gate"], gf["up"]),
+                  lambda: cpu.swiglu(gate, up), dict(gate=gate, up=up), lambda: so))
+    return out
+
+
+
+
+def measure_ops(dev, steps, warmup, only=""):
+    """Returns (table rows, pass_ms, pass_bytes, launches, first buffer set)."""
+    data = make_data()
+    sets = [build_ops(dev, data) for _ in range(NSETS)]
+    if only:
+        keep = set(only.split(","))
+        sets = [[op for op in st if op.name in keep] for st in sets]
+    ops = sets[0]
+    stream = torch.cuda.current_stream(dev)
+
+    def one_pass(record):
+        for i in range(len(ops)):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(stream)
+            for st in sets:
+                st[i].gpu_run()
+            e.record(stream)
+            record[i].append((s, e))
+
+    for _ in range(max(warmup, 3)):
+        one_pass([[] for _ in ops])
+    torch.cuda.synchronize(dev)
+    events = [[] for _ in ops]
+    for _ in range(steps):
+        one_pass(events)
+    torch.cuda.synchronize(dev)
+    op_ms = [sum(s.elapsed_time(e) for s, e in ev) / steps / NSETS for ev in events]
+    return ops, op_ms
+
+
+def e2e_pass_ms(dev, ops, steps):
+    """Same operators with HOST buffers: pinned inputs H2D, the operator, result D2H."""
+    pinned = [{k: v.contiguous().pin_memory() for k, v in op.host_inputs.items()} for op in ops]
+    host_out = [torch.empty(op.result().shape, dtype=op.result().dtype).pin_memory() for op in ops]
+    h2d = sum(nbytes(*p.values()) for p in pinned)
+    d2h = sum(nbytes(t) for t in host_out)
+    stream = torch.cuda.current_stream(dev)
+
+    def one():
+        for op, pin, ho in zip(ops, pinned, host_out):
+            for kname, v in pin.items():
+                op.gpu_inputs[kname].view(-1).copy_(v.view(-1), non_blocking=True)
+            op.gpu_run()
+            ho.copy_(op.result(), non_blocking=True)
+    one()
+    torch.cuda.synchronize(dev)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(stream)
+    for _ in range(steps):
+        one()
+    e.record(stream)
+    torch.cuda.synchronize(dev)
+    return s.elapsed_time(e) / steps, h2d, d2h
+
+
+def cpu_pass_seconds(scale=0.25, repeats=1):
+    """CPU ATen over a bounded sample: the same 16 operators on `scale` of the rows."""
+    ops = build_ops(None, make_data(scale), want_gpu=False)
+    sample_bytes = sum(op.bytes for op in ops)
+
+    def one():
+        t0 = time.perf_counter()
+        for op in ops:
+            op.cpu_run()
+        return time.perf_counter() - t0
+    one()
+    return min(one() for _ in range(max(1, repeats))), sample_bytes

@@ -4,6 +4,8 @@
 // RoPE and SwiGLU entries have no reference kernel -- the reference runs them as
 // chains of pointwise ops -- and sit beside its one efficient op,
 // efficient_ops/ops.cpp:335-342).
+#include <ATen/native/DispatchStub.h>
+#include <ATen/native/transformers/attention.h>
 #include <ATen/native/transformers/sdp_utils_cpp.h>
 #include <torch/library.h>
 
@@ -119,7 +121,7 @@ at::Tensor swiglu_packed(const at::Tensor& gate_up) {
 // flash when the kernel can take the problem, otherwise the math composite
 // (reference priority flash -> mem-efficient -> math, RegisterSPDA.cpp:223-275;
 // flash gate :137-178).
-static int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
                                 const std::optional<at::Tensor>& attn_mask, double dropout_p, bool is_causal,
                                 std::optional<double>, bool) {
   const bool has_mask = attn_mask.has_value() && attn_mask->defined();
@@ -134,6 +136,12 @@ static int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, 
 
 }  // namespace aotops
 }  // namespace torch_gcu
+
+// The composite scaled_dot_product_attention asks the per-device dispatch stub;
+// the operator form is registered too for callers that go through the dispatcher.
+namespace at::native {
+REGISTER_PRIVATEUSE1_DISPATCH(_fused_sdp_choice_stub, &torch_gcu::aotops::fused_sdp_choice)
+}  // namespace at::native
 
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("_fused_sdp_choice", TORCH_FN(torch_gcu::aotops::fused_sdp_choice));

@@ -35,6 +35,10 @@ def is_bf16_supported() -> bool:
     return True
 
 
+def _is_in_bad_fork() -> bool:
+    return False
+
+
 def is_initialized() -> bool:
     return _initialized
 

@@ -45,6 +45,9 @@ class Stream(torch.Stream):
     def wait_stream(self, stream) -> None:
         self.wait_event(stream.record_event())
 
+    def wait_event(self, event) -> None:
+        super().wait_event(event._ev if isinstance(event, Event) else event)
+
     def record_event(self, event=None):
         if event is None:
             event = Event()
@@ -66,23 +69,37 @@ class ExternalStream(Stream):
         return super().__new__(cls, stream_id=sid, device_index=didx, device_type=dtype)
 
 
-class Event(torch.Event):
+class Event:
     """Event(enable_timing=False, blocking=False, interprocess=False) with record / wait /
-    query / elapsed_time / synchronize (reference: streams.py:144-237)."""
+    query / elapsed_time / synchronize (reference: streams.py:144-237). It wraps the
+    device-generic torch.Event, which the device guard implements."""
 
-    def __new__(cls, enable_timing=False, blocking=False, interprocess=False):
+    def __init__(self, enable_timing=False, blocking=False, interprocess=False):
         if interprocess:
             raise NotImplementedError("interprocess events are not supported by the gcu backend")
-        return super().__new__(cls, device="gcu", enable_timing=enable_timing)
+        self._ev = torch.Event(device="gcu", enable_timing=enable_timing)
 
     def record(self, stream=None):
         if stream is None:
             import torch_gcu.gcu as gcu
             stream = gcu.current_stream()
-        super().record(stream)
+        self._ev.record(stream)
 
     def wait(self, stream=None) -> None:
         if stream is None:
             import torch_gcu.gcu as gcu
             stream = gcu.current_stream()
-        super().wait(stream)
+        self._ev.wait(stream)
+
+    def query(self) -> bool:
+        return self._ev.query()
+
+    def elapsed_time(self, end_event) -> float:
+        return self._ev.elapsed_time(end_event._ev if isinstance(end_event, Event) else end_event)
+
+    def synchronize(self) -> None:
+        self._ev.synchronize()
+
+    @property
+    def device(self):
+        return self._ev.device
