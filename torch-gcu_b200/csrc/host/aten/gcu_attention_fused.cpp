@@ -44,6 +44,16 @@ _scaled_dot_product_flash_attention(const at::Tensor& query, const at::Tensor& k
                          empty_long, empty_long.clone(), at::empty({0}, query.options()));
 }
 
+// What PyTorch's composite scaled_dot_product_attention calls for a PrivateUse1
+// device when the backend choice is "overrideable": the same flash kernel.
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, c10::SymInt, c10::SymInt, at::Tensor, at::Tensor, at::Tensor>
+_scaled_dot_product_fused_attention_overrideable(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
+                                                 const std::optional<at::Tensor>& attn_bias, double dropout_p, bool is_causal,
+                                                 bool return_debug_mask, std::optional<double> scale) {
+  TORCH_CHECK(!(attn_bias.has_value() && attn_bias->defined()), "flash attention on the gcu backend takes no attention bias");
+  return aotops::_scaled_dot_product_flash_attention(query, key, value, dropout_p, is_causal, return_debug_mask, scale);
+}
+
 // --------------------------------------------------------------- fused ops --
 std::tuple<at::Tensor, at::Tensor> rms_norm_residual(const at::Tensor& x, const std::optional<at::Tensor>& residual,
                                                      const at::Tensor& weight, double eps) {
@@ -118,7 +128,8 @@ at::Tensor swiglu_packed(const at::Tensor& gate_up) {
 }
 
 // ------------------------------------------------------ SDPA backend choice --
-// flash when the kernel can take the problem, otherwise the math composite
+// flash (reported as "overrideable", the slot PyTorch gives PrivateUse1 backends)
+// when the kernel can take the problem, otherwise the math composite
 // (reference priority flash -> mem-efficient -> math, RegisterSPDA.cpp:223-275;
 // flash gate :137-178).
 int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const at::Tensor& value,
@@ -131,7 +142,7 @@ int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const a
                         (query.size(-1) == 64 || query.size(-1) == 128) && key.size(-1) == query.size(-1) &&
                         value.size(-1) == query.size(-1) && key.size(1) > 0 && query.size(1) % key.size(1) == 0 &&
                         (!is_causal || query.size(2) == key.size(2)) && !query.requires_grad() && key.size(2) > 0;
-  return static_cast<int64_t>(flash_ok ? sdp::SDPBackend::flash_attention : sdp::SDPBackend::math);
+  return static_cast<int64_t>(flash_ok ? sdp::SDPBackend::overrideable : sdp::SDPBackend::math);
 }
 
 }  // namespace aotops
