@@ -170,6 +170,24 @@ size_t b200_scatter_add_workspace_size(const b200Tensor* self, int64_t dim,
 b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64_t dim,
                             const b200Tensor* index, const b200Tensor* src,
                             void* workspace, size_t workspace_bytes, b200Stream stream);
+/* No counterpart in the reference. The same deterministic scatter_add for
+ * callers that must not allocate device memory while they run: code inside a
+ * region where cudaMalloc is forbidden or would serialise the device (a latency
+ * critical serving loop, a caller that owns no allocator, a plugin handed only
+ * input and output buffers). It takes no workspace: its scratch is a fixed 8 MiB
+ * array inside the library (held by every GPU that loads the library, until
+ * exit), enough for about 490 000 source rows in the row-index form; a larger
+ * problem is refused with B200_NOT_SUPPORTED and a message that says how much
+ * was needed. It calls no allocation routine of any kind.
+ * - The first call on each device looks up the array's device address; make
+ *   that first call before starting any stream capture on that device.
+ * - Every call uses the same array, so two calls whose kernels can overlap on
+ *   the GPU (different streams, different host threads) race: serialise them.
+ *   The array keeps the previous call's contents; nothing in it needs clearing
+ *   between calls, every call rewrites all it reads.                          */
+b200Status b200_scatter_add_static(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                                   const b200Tensor* index, const b200Tensor* src,
+                                   b200Stream stream);
 /* reference: aotops::_index_put_impl_ -> topsatenIndexPutImpl
  * (torch_gcu/csrc/aten/aot_ops/gcu_tensor_advanced_indexing.cpp:60-90).
  * self[index[i], ...] (+)= values[i, ...] for ONE index tensor over the

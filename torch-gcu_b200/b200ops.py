@@ -249,6 +249,12 @@ def scatter_add(out, self, dim, index, src, workspace, stream=None):
                                  _ref(view(src)), ws_ptr, ws_n, _stream(stream)))
 
 
+def scatter_add_static(out, self, dim, index, src, stream=None):
+    """scatter_add that allocates nothing: scratch is the library's built-in 8 MiB array."""
+    check(lib().b200_scatter_add_static(_ref(view(out)), _ref(view(self)), ctypes.c_int64(dim), _ref(view(index)),
+                                        _ref(view(src)), _stream(stream)))
+
+
 def index_put_workspace_size(self, index, values):
     return lib().b200_index_put_workspace_size(_ref(view(self)), _ref(view(index)), _ref(view(values)))
 

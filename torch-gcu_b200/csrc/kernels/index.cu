@@ -14,6 +14,8 @@
 // floating-point atomics anywhere, so results are run-to-run identical.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 // Device-side error word: kernels OR a bit in instead of trapping.
@@ -979,6 +981,47 @@ b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64
                                                          (const T*)src->data, sk, sv, n, out_numel);
   });
   return check_launch("b200_scatter_add");
+}
+
+// ---- scatter_add without any allocation -----------------------------------
+// Scratch for b200_scatter_add_static: lives in the library image, so every GPU
+// that loads the library holds these bytes until the process exits.
+#define B200_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+b200Status b200_scatter_add_static(const b200Tensor* out, const b200Tensor* self, int64_t dim,
+                                   const b200Tensor* index, const b200Tensor* src, b200Stream stream) {
+  // In host code `g_static_scratch` is only a handle for the symbol, not a device
+  // address: the address is looked up once per device, with that device current.
+  static void* scratch_of_device[64] = {nullptr};
+  static std::mutex setup_mutex;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  B200_REQUIRE(e == cudaSuccess && dev >= 0 && dev < 64, B200_LAUNCH_FAILED, "b200_scatter_add_static: %s",
+               e == cudaSuccess ? "device index out of range" : cudaGetErrorString(e));
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> g(setup_mutex);
+    if (!scratch_of_device[dev]) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p) {
+        (void)cudaGetLastError();
+        return fail(B200_LAUNCH_FAILED, "b200_scatter_add_static: cannot resolve the scratch array on device %d: %s", dev,
+                    cudaGetErrorString(e));
+      }
+      scratch_of_device[dev] = p;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  B200_REQUIRE(out && self && index && src, B200_BAD_PARAM, "b200_scatter_add_static: null tensor");
+  const size_t need = b200_scatter_add_workspace_size(self, dim, index, src);
+  B200_REQUIRE(need <= B200_STATIC_SCRATCH_BYTES, B200_NOT_SUPPORTED,
+               "b200_scatter_add_static: this problem needs %zu bytes of scratch, the built-in array holds %u; "
+               "use b200_scatter_add with a caller workspace", need, (unsigned)B200_STATIC_SCRATCH_BYTES);
+  // Nothing in the scratch has to start at zero: keys, histograms, sorted pairs and
+  // segment starts are all fully rewritten by every call before they are read.
+  return b200_scatter_add(out, self, dim, index, src, scratch, B200_STATIC_SCRATCH_BYTES, stream);
 }
 
 size_t b200_index_put_workspace_size(const b200Tensor* self, const b200Tensor* index,
