@@ -348,6 +348,55 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_micro(name):
+    """One operator, a few launches, a case a little larger than L2: the command the
+    `ncu --set full` captures under profiles/ are taken from."""
+    import b200ops as ops
+    import ctypes
+    dev = torch.device("cuda", 0)
+    bf = torch.bfloat16
+    if name == "gemm":
+        m, n, k = 8192, 4096, 4096
+        a = torch.randn(m, k, device=dev).to(bf)
+        w = (torch.randn(n, k, device=dev) * 0.02).to(bf)
+        out = torch.empty(m, n, dtype=bf, device=dev)
+        fn, work = ops.bind("mm", out, a, w.t()), {"flops": 2 * m * n * k}
+    elif name == "sdpa":
+        B, Hq, Hkv, S, D = 2, 32, 8, 2048, 128
+        q = torch.randn(B, Hq, S, D, device=dev).to(bf)
+        k_ = torch.randn(B, Hkv, S, D, device=dev).to(bf)
+        v_ = torch.randn(B, Hkv, S, D, device=dev).to(bf)
+        out = torch.empty(B, S, Hq, D, dtype=bf, device=dev).transpose(1, 2)
+        fn = ops.bind("sdpa_flash_fwd", out, None, q, k_, v_, ctypes.c_int32(1), ctypes.c_double(D ** -0.5))
+        work = {"flops": 4 * B * Hq * S * S * D // 2}
+    elif name == "swiglu":
+        g_, u_ = torch.randn(4096, 14336, device=dev).to(bf), torch.randn(4096, 14336, device=dev).to(bf)
+        out = torch.empty_like(g_)
+        fn, work = ops.bind("swiglu", out, g_, u_), {"bytes": 3 * g_.numel() * 2}
+    elif name == "scatter":
+        src = torch.randn(262144, 256, device=dev)
+        rows = torch.randint(0, 65536, (262144,), device=dev)
+        base = torch.zeros(65536, 256, device=dev)
+        out = torch.empty_like(base)
+        idx = rows[:, None].expand(-1, 256)
+        ws = torch.empty(ops.scatter_add_workspace_size(base, 0, idx, src), dtype=torch.uint8, device=dev)
+        fn = ops.bind("scatter_add", out, base, ctypes.c_int64(0), idx, src, *ops.ws_args(ws), keep=(ws,))
+        work = {"bytes": 404750336}
+    else:
+        raise SystemExit("unknown micro case " + name)
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    fn()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    print(json.dumps({"micro": name, "ms": round(ms, 4), **{k: v for k, v in work.items()},
+                      "rate": round(list(work.values())[0] / ms / 1e9, 1)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -356,8 +405,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
+    ap.add_argument("--micro", default="", help="gemm | sdpa | swiglu | scatter: a 3-launch case for profiler captures")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.micro:
+        run_micro(args.micro)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
