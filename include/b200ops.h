@@ -124,8 +124,8 @@ b200Status b200_fill(const b200Tensor* out, double value, b200Stream stream);
 /* ---- copy / cast (reference: aotops::_copy_from -> copy_device_to_device ->
  *      topsatenCopy, torch_gcu/csrc/aten/aot_ops/gcu_copy.cpp:34-198,402-442)
  * dst[i] = (dst dtype) src[i] for same-shaped (caller-expanded) views; any
- * strides, any pair of dtypes. fp32->bf16 is round-to-nearest-even with NaN
- * mapped to 0x7FC0, the rule of c10::BFloat16.                               */
+ * strides, any pair of dtypes. fp32->bf16 is round-to-nearest-even (NaN stays
+ * NaN, payload unspecified).                               */
 b200Status b200_copy(const b200Tensor* dst, const b200Tensor* src, b200Stream stream);
 
 /* ---- reductions ---------------------------------------------------------- */

@@ -341,6 +341,301 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
 }
 
+// ---------------------------------------------------------------------------
+// Prefill kernel: one CTA per (256 query rows, head, batch), 384 threads.
+//   warp 0      TMA: two Q tiles once, K / V tiles through a 2-stage ring
+//   warp 1      tcgen05.mma for both Q tiles in turn: S_t = Q_t K_j^T into that
+//               tile's S buffer, then O_t += P_t V_j with P_t read from tensor memory
+//   warps 4-7   softmax of tile 0, warps 8-11 softmax of tile 1 (2-3 idle), one thread per row:
+//               the whole S row (128 fp32) is read once into registers, P_t is
+//               written back over S_t as packed 16-bit pairs, so while one tile is
+//               in its softmax the tensor core works on the other
+// The running maximum is only advanced (and O rescaled) when it grew by more than
+// 2^8 in the exponent, so most iterations touch O not at all; l and O stay
+// consistent because both use the same stale maximum.
+constexpr int kPrefillThreads = 384;  // registers are granted per 4 warps, so 10 warps cost as much as 12
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+template <int D> struct PrefillCfg {
+  static constexpr int kHalves = D / 64;
+  static constexpr int kQBytes = BQ * D * 2;     // one Q tile
+  static constexpr int kKVBytes = BKV * D * 2;
+  static constexpr int kSmem = 2 * kQBytes + kKVStages * 2 * kKVBytes + 1024 + 256;
+  static constexpr int kSCol = 0;                // S_t at columns t*128 (P_t over its first 64)
+  static constexpr int kOCol = 256;              // O_t at columns 256 + t*128
+  static constexpr int kTmemCols = 512;
+};
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if (BF16) return f32x2_to_bf16x2_bits(lo, hi);
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+  using Cfg = PrefillCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                                    // [tile]
+  uint8_t* sKV = sQ + 2 * Cfg::kQBytes;                  // [stage][K | V]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kKVStages * 2 * Cfg::kKVBytes);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;             // [stage]
+  uint64_t* v_full = bars + 3;             // [stage]
+  uint64_t* kv_empty = bars + 5;           // [stage]
+  uint64_t* s_full = bars + 7;             // [tile]
+  uint64_t* p_full = bars + 9;             // [tile]
+  uint64_t* o_done = bars + 11;            // [tile]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int pair = gridDim.x - 1 - blockIdx.x;  // longest (last) causal pairs first
+  const int q0 = pair * 2 * BQ, hq = blockIdx.y, hkv = hq / G, b = blockIdx.z;
+  const int n_all = (p.Sk + BKV - 1) / BKV;
+  int n_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int q0t = q0 + t * BQ;
+    n_t[t] = q0t >= p.Sq ? 0 : (p.causal ? min(n_all, q0t / BKV + 1) : n_all);
+  }
+  const int n_max = max(n_t[0], n_t[1]);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_done[i], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      const int n_q = n_t[1] > 0 ? 2 : 1;
+      mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(n_q * Cfg::kQBytes));
+      for (int t = 0; t < n_q; ++t)
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h)
+          tma_load_4d(sQ + t * Cfg::kQBytes + h * (BQ * 128), &tmap_q, q_full, h * 64, q0 + t * BQ, hq, b);
+      for (int j = 0; j < n_max; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1u) ^ 1u, abort_flag)) break;
+        uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
+        uint8_t* sV = sK + Cfg::kKVBytes;
+        mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, j * BKV, hkv, b);
+        mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, j * BKV, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(BQ, BKV, BF16, false, false);  // Q, K both K-major
+      const uint32_t idesc_o = make_idesc(BQ, D, BF16, false, true);     // P from tensor memory, V MN-major
+      auto issue_s = [&](int t, int j) {
+        const uint32_t q_addr = smem_u32(sQ + t * Cfg::kQBytes);
+        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * Cfg::kKVBytes);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * (BQ * 128) + (kk % 4) * 32;
+          umma_f16(d_tmem, smem_desc_sw128(q_addr + off, 16u, 1024u), smem_desc_sw128(k_addr + off, 16u, 1024u),
+                   idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      };
+      bool ok = n_max > 0 && mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0, 0);
+        if (n_t[1] > 0) issue_s(1, 0);
+      }
+      for (int j = 0; j < n_max && ok; ++j) {
+        const int st = j & 1;
+        bool v_ready = false, k_ready = false;
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (j >= n_t[t]) continue;
+          if (!mbar_wait(&p_full[t], j & 1u, abort_flag)) { ok = false; break; }
+          if (!v_ready) {
+            if (!mbar_wait(&v_full[st], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
+            v_ready = true;
+          }
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
+          const uint32_t o_tmem = tmem_base + static_cast<uint32_t>(Cfg::kOCol + t * BKV);
+          const uint32_t p_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
+#pragma unroll
+          for (int kk = 0; kk < BKV / 16; ++kk) {
+            // A = P_t: 16 keys = 8 packed columns per step. B = V: 64-column slabs BKV*128 bytes
+            // apart (LBO), 8-key groups 1024 bytes apart (SBO), 16 keys = 2048 bytes per step.
+            const uint64_t db = smem_desc_sw128(v_addr + kk * 2048, BKV * 128, 1024u);
+            umma_f16_ts(o_tmem, p_tmem + kk * 8, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+          }
+          if (j + 1 < n_t[t]) {
+            if (!k_ready) {
+              if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+              k_ready = true;
+              tc_fence_after();
+            }
+            issue_s(t, j + 1);   // executes after the P.V above, which has then consumed P_t
+          } else {
+            umma_commit(&o_done[t]);
+          }
+        }
+        if (ok) umma_commit(&kv_empty[st]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------ softmax / output --
+    const int t = (warp - 4) >> 2;                 // tile of this warp
+    const int quarter = warp & 3;                  // tensor-memory lanes this warp may touch
+    const int r = quarter * 32 + lane;             // row of the tile this thread owns
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const int q0t = q0 + t * BQ;
+    const int qi = q0t + r;
+    const bool row_valid = qi < p.Sq;
+    const int n_kv = n_t[t];
+    const uint32_t s_tmem = tmem_base + lane_sel + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
+    const uint32_t o_tmem = tmem_base + lane_sel + static_cast<uint32_t>(Cfg::kOCol + t * BKV);
+    const float sl2 = p.scale_log2;
+    float m = -CUDART_INF_F;   // maximum the exponentials are taken against (raw score units)
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int k0 = j * BKV;
+      if (!mbar_wait(&s_full[t], j & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t s[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV; c += 32) tmem_ld_32x32_at(s_tmem + c, &s[c]);
+      tmem_wait_ld();
+      const bool need_mask = (p.causal && k0 + BKV - 1 > q0t) || (k0 + BKV > p.Sk);
+      if (need_mask) {
+        const int vis = (p.causal ? min(p.Sk, qi + 1) : p.Sk) - k0;  // columns [0, vis) are visible
+#pragma unroll
+        for (int i = 0; i < BKV; ++i)
+          if (i >= vis) s[i] = 0xff800000u;  // -inf
+      }
+      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < BKV; i += 8) {
+        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])));
+        mx2 = fmaxf(mx2, fmaxf(__uint_as_float(s[i + 4]), __uint_as_float(s[i + 5])));
+        mx3 = fmaxf(mx3, fmaxf(__uint_as_float(s[i + 6]), __uint_as_float(s[i + 7])));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // advance the maximum only when it grew by more than the threshold
+      const bool grow = (mx - m) * sl2 > kRescaleThreshold;   // true on the first tile (m = -inf)
+      float alpha = 1.f;
+      if (grow) {
+        alpha = ex2_approx((m - mx) * sl2);                    // m = -inf -> 0
+        m = mx;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // the P.V of the previous tile finished before this S was written, so O is stable
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32x32(o_tmem + c, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32(o_tmem + c, o);
+        }
+      }
+      const float mb = (m == -CUDART_INF_F ? 0.f : m) * sl2;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < BKV; i += 4) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
+        const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
+        const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        s[i / 2] = pack_pair<BF16>(p0, p1);
+        s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
+      }
+      l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+      tmem_st_32x32(s_tmem, &s[0]);
+      tmem_st_32x32(s_tmem + 32, &s[32]);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    // epilogue: O / l
+    if (ok && n_kv > 0) ok = mbar_wait(&o_done[t], 0, abort_flag);
+    if (ok && n_kv > 0) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(hq) * p.o_sh +
+                       static_cast<int64_t>(qi) * p.o_ss;
+      const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(o_tmem + c, v);
+        tmem_wait_ld();
+        if (row_valid) {
+          uint32_t o[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            o[i] = pack_pair<BF16>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+          if (vec_ok) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(orow + c + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              orow[c + 2 * i] = static_cast<uint16_t>(o[i] & 0xffffu);
+              orow[c + 2 * i + 1] = static_cast<uint16_t>(o[i] >> 16);
+            }
+          }
+        }
+      }
+      if (row_valid && p.lse) {
+        const float lse = l > 0.f ? m * p.scale + logf(l) : -CUDART_INF_F;
+        p.lse[(static_cast<int64_t>(b) * p.Hq + hq) * p.Sq + qi] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
 bool make_qkv_map(CUtensorMap* m, const b200Tensor* t, uint32_t box_rows, uint32_t box_heads, const char** err) {
   // t: (B, H, S, D) view; tensor-map dims innermost first: D, S, H, B
   const uint64_t dims[4] = {(uint64_t)t->sizes[3], (uint64_t)t->sizes[2], (uint64_t)t->sizes[1], (uint64_t)t->sizes[0]};
@@ -364,13 +659,20 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
   cudaGetDevice(&dev);
   if (dev != last_dev) {
     cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillCfg<D>::kSmem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PrefillCfg<D>::kSmem);
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
-  dim3 grid;
-  if (p.packed) grid = dim3(1, p.Hkv, p.B);
-  else grid = dim3((p.Sq + BQ - 1) / BQ, p.Hq, p.B);
-  attention_fwd_kernel<D><<<grid, kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
+  if (p.packed) {
+    attention_fwd_kernel<D><<<dim3(1, p.Hkv, p.B), kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
+  } else {
+    const dim3 grid((p.Sq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
+    if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
+    else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
+  }
   return check_launch("b200_sdpa_flash_fwd");
 }
 
@@ -394,6 +696,7 @@ extern "C" b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tenso
                "b200_sdpa_flash_fwd: shape mismatch");
   B200_REQUIRE(p.Hkv > 0 && p.Hq % p.Hkv == 0, B200_BAD_PARAM, "b200_sdpa_flash_fwd: Hq must be a multiple of Hkv");
   B200_REQUIRE(p.D == 64 || p.D == 128, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: head dim 64 or 128");
+  B200_REQUIRE(scale > 0.0, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: scale must be positive");
   B200_REQUIRE(!is_causal || p.Sq == p.Sk, B200_NOT_SUPPORTED,
                "b200_sdpa_flash_fwd: causal needs Sq == Sk (a single decode query attends everything: is_causal=0)");
   if (numel(q) == 0) return B200_OK;

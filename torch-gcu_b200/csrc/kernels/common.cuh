@@ -1,6 +1,7 @@
 // Shared helpers of the sm_100a kernel library: status/error plumbing, tensor
 // view inspection, dtype dispatch, 128-bit vector access and the bf16/f16
-// conversions whose rounding matches c10::BFloat16 / c10::Half bit for bit.
+// conversions (round to nearest even, bit-identical to c10::BFloat16 / c10::Half
+// for every non-NaN value).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -142,20 +143,22 @@ inline StridedIndexer<NARGS> make_indexer(const b200Tensor* const (&ts)[NARGS]) 
 }
 
 // ------------------------------------------------------------- conversions ----
-// fp32 -> bf16, round to nearest even; every NaN becomes 0x7FC0 (c10::BFloat16).
+// fp32 -> bf16, round to nearest even, one hardware conversion (cvt.rn.bf16.f32).
+// NaN stays NaN; its payload is not part of the contract (c10::BFloat16 gives
+// 0x7FC0, ATen's vectorised CPU cast 0xFFFF, the hardware 0x7FFF).
 __device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
-  uint32_t u = __float_as_uint(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7FC0;
-  u += 0x7FFFu + ((u >> 16) & 1u);
-  return static_cast<uint16_t>(u >> 16);
+  return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+// Two at once: cvt.rn.bf16x2.f32 (lo in the low half).
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2_bits(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_bits_to_f32(uint16_t b) {
   return __uint_as_float(static_cast<uint32_t>(b) << 16);
 }
-// fp32 -> fp16, round to nearest even; NaN becomes sign|0x7E00 (c10::Half).
+// fp32 -> fp16, round to nearest even (cvt.rn.f16.f32); NaN stays NaN.
 __device__ __forceinline__ uint16_t f32_to_f16_bits(float f) {
-  uint32_t u = __float_as_uint(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return static_cast<uint16_t>(((u >> 16) & 0x8000u) | 0x7E00u);
   return __half_as_ushort(__float2half_rn(f));
 }
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) {

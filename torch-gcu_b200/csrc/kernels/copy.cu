@@ -8,8 +8,8 @@
 //  * any other dtype pair or layout   -> indexed kernel, one element per step
 //
 // Conversion rules are those of c10: float->integer truncates toward zero,
-// anything->bool is (x != 0), fp32->bf16/f16 rounds to nearest even with the
-// NaN encodings of c10::BFloat16 / c10::Half, wider floats go through fp32.
+// anything->bool is (x != 0), fp32->bf16/f16 rounds to nearest even (NaN stays
+// NaN), wider floats go through fp32.
 #include "common.cuh"
 
 namespace b200 {

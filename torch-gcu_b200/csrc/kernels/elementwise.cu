@@ -56,7 +56,7 @@ template <> struct Silu<float> {
 };
 // 16-bit I/O: fast exp / reciprocal, error far below half an output ulp.
 struct SiluFast {
-  __device__ __forceinline__ float operator()(float x) const { return x * __frcp_rn(1.0f + __expf(-x)); }
+  __device__ __forceinline__ float operator()(float x) const { return __fdividef(x, 1.0f + __expf(-x)); }
 };
 
 template <typename M, int OP> struct Unary {

@@ -185,7 +185,7 @@ __device__ __forceinline__ Vec16<T> swiglu_vec(const Vec16<T>& g, const Vec16<T>
     if constexpr (sizeof(T) == 2) {
       // 16-bit output: the fast exp / reciprocal (a few fp32 ulp) are far below
       // half an output ulp, and keep the kernel off the instruction-issue limit
-      o.v[e] = store_from_math<T>(x * __frcp_rn(1.0f + __expf(-x)) * load_as_math(u.v[e]));
+      o.v[e] = store_from_math<T>(__fdividef(x, 1.0f + __expf(-x)) * load_as_math(u.v[e]));
     } else {
       o.v[e] = store_from_math<T>(x / (1.0f + expf(-x)) * load_as_math(u.v[e]));
     }
