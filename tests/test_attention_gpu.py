@@ -62,7 +62,8 @@ def test_sdpa_golden_and_strided_inputs(ops, golden):
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,Sk,D,Sq", [(3, 8, 2, 300, 128, 1), (2, 4, 4, 128, 64, 1), (2, 32, 8, 1000, 128, 1),
-                                              (1, 8, 2, 513, 128, 5)])
+                                              (1, 8, 2, 513, 128, 5), (2, 8, 2, 50, 128, 3), (1, 16, 2, 1147, 128, 2),
+                                              (2, 4, 1, 4096, 128, 4), (1, 4, 4, 2500, 128, 1), (1, 16, 1, 700, 128, 1)])
 def test_sdpa_decode_packed_heads(ops, B, Hq, Hkv, Sk, D, Sq):
     """A few query positions against a long KV cache, is_causal=False: the query
     heads of one KV group share a tile."""
@@ -90,3 +91,33 @@ def test_sdpa_golden(ops, golden):
     out = torch.empty(1, 16, 4, 32, dtype=BF, device=DEV).transpose(1, 2)
     with pytest.raises(ops.B200Error):  # head dim 32: not a tensor-core shape of this kernel
         ops.sdpa_flash_fwd(out, None, dev(q), dev(s["k"]), dev(s["v"]), True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, BF])
+@pytest.mark.parametrize("Sq,Sk,causal", [(640, 640, True), (300, 300, False), (1, 900, False), (2, 2000, False)])
+def test_sdpa_growing_maximum(ops, dtype, Sq, Sk, causal):
+    """Scores that keep growing along the key axis, so the running maximum moves in
+    every key tile and the accumulator has to be rescaled again and again; both
+    16-bit dtypes."""
+    g = torch.Generator().manual_seed(54)
+    B, Hq, Hkv, D = 1, 4, 1, 128
+    q = torch.randn(B, Hq, Sq, D, generator=g)
+    k = torch.randn(B, Hkv, Sk, D, generator=g)
+    v = torch.randn(B, Hkv, Sk, D, generator=g)
+    # add a component along q's mean direction that grows with the key position
+    ramp = torch.linspace(0, 6, Sk).view(1, 1, Sk, 1)
+    k = k + ramp * q.mean((1, 2), keepdim=True).sign() * 0.5
+    q = q.abs() * q.mean((1, 2), keepdim=True).sign()
+    q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
+    out = torch.empty(B, Sq, Hq, D, dtype=dtype, device=DEV).transpose(1, 2)
+    lse = torch.empty(B, Hq, Sq, device=DEV)
+    ops.sdpa_flash_fwd(out, lse, dev(q), dev(k), dev(v), causal)
+    assert ops.device_error_fetch() == 0
+    G = Hq // Hkv
+    kf, vf = k.float().repeat_interleave(G, 1), v.float().repeat_interleave(G, 1)
+    s = (q.float() @ kf.transpose(-1, -2)) * D ** -0.5
+    if causal:
+        s = s.masked_fill(torch.ones(Sq, Sk, dtype=torch.bool).triu(1), float("-inf"))
+    assert (s.max(-1).values - s[..., :128].max(-1).values).max() > 20   # the maximum really moves
+    close(out, (torch.softmax(s, -1) @ vf).to(dtype), 1.6e-2, 1e-2)
+    close(lse, torch.logsumexp(s, -1), 1e-3, 2e-3)

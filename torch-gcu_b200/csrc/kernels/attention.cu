@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "tc_common.cuh"
 
+#include <cooperative_groups.h>
 #include <math_constants.h>
 
 namespace b200 {
@@ -636,6 +637,321 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
 }
 
+// ---------------------------------------------------------------------------
+// Decode kernel (few query rows against a long KV cache, D = 128): the problem is
+// transposed so that the KEYS fill the 128 rows of the MMA and the R = groups*Sq
+// query rows (R <= 16, padded to N = 16) its narrow N side:
+//   S^T (128 keys x N)  = K_j (A, K-major)      x  Q^T (B, K-major)
+//   O^T (128 dims x N) += V_j^T (A, MN-major)   x  P^T (B, K-major, shared memory)
+// so every K / V byte is read once per KV head, tensor-core and softmax work scale
+// with N instead of 128, and one thread owns one key of the tile. The maximum over
+// keys is a warp reduction plus one 128-thread named barrier per tile. A cluster
+// of `splits` CTAs shares one (batch, KV head): each walks a contiguous slice of
+// the keys and the partial (O, m, l) are merged by CTA 0 through distributed
+// shared memory. 192 threads: warp 0 TMA (3-stage K / V ring), warp 1 MMA,
+// warps 2-5 softmax and output.
+constexpr int kDecThreads = 192;
+constexpr int kDecStages = 3;
+constexpr int kDecD = 128;
+
+template <int N> struct DecCfg {
+  static constexpr int kQBytes = N * 128 * 2;             // N rows, two 64-column slabs
+  static constexpr int kKVBytes = BKV * kDecD * 2;
+  static constexpr int kPBytes = N * 128 * 2;             // N rows x 128 keys, two 64-key slabs
+  static constexpr int kSmem = kQBytes + kDecStages * 2 * kKVBytes + 2 * kPBytes + 1024 + 1024;
+  static constexpr int kSCol = 0;                         // S^T buffers at 0 and N
+  static constexpr int kOCol = 2 * N;
+  static constexpr int kTmemCols = N == 16 ? 64 : 128;
+  static_assert(N == 16, "shared memory is budgeted for N = 16");
+};
+
+__device__ __forceinline__ float warp_max_f32(float v) {
+  // order-preserving map to unsigned, hardware integer reduction, and back
+  uint32_t u = __float_as_uint(v);
+  u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;
+  u = __reduce_max_sync(0xffffffffu, u);
+  u ^= (u >> 31) ? 0x80000000u : 0xffffffffu;
+  return __uint_as_float(u);
+}
+
+template <int N, bool BF16>
+__global__ void __launch_bounds__(kDecThreads, 1)
+attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                        const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int splits) {
+  using Cfg = DecCfg<N>;
+  constexpr int D = kDecD;
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ uint8_t smem_raw[];
+  // the same offset in every CTA of the cluster, so peers can be addressed by mapping
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sKV = sQ + Cfg::kQBytes;                       // [stage][K | V]
+  uint8_t* sP = sKV + kDecStages * 2 * Cfg::kKVBytes;     // [2]
+  uint8_t* tail = sP + 2 * Cfg::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;             // [3]
+  uint64_t* v_full = bars + 4;             // [3]
+  uint64_t* kv_empty = bars + 7;           // [3]
+  uint64_t* s_full = bars + 10;            // [2]
+  uint64_t* p_full = bars + 12;            // [2]
+  uint64_t* pv_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(tail + 128);      // [2][4][N] warp maxima; later [4][N] warp sums
+  float* comb_ml = red + 2 * 4 * N;                       // [2][N]: m, l of this CTA
+  float* comb_o = reinterpret_cast<float*>(sKV);          // [N][128] partial O, over the drained K/V ring
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int R = G * p.Sq;
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int hq0 = hkv * G;
+  const int n_tiles = (p.Sk + BKV - 1) / BKV;
+  const int per = (n_tiles + splits - 1) / splits;
+  const int t_begin = min(split * per, n_tiles), t_end = min(t_begin + per, n_tiles);
+  const int n_my = t_end - t_begin;
+
+  // zero the Q tile: the load fills only its first R rows
+  for (int i = threadIdx.x; i < Cfg::kQBytes / 16; i += kDecThreads) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < kDecStages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+    }
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0 && n_my > 0) {
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      // box (64, Sq, G, 1): rows ordered (group head, position)
+      mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(2 * 128 * R));
+#pragma unroll
+      for (int h = 0; h < 2; ++h) tma_load_4d(sQ + h * (N * 128), &tmap_q, q_full, h * 64, 0, hq0, b);
+      for (int i = 0; i < n_my; ++i) {
+        const int st = i % kDecStages, use = i / kDecStages;
+        if (!mbar_wait(&kv_empty[st], (use & 1u) ^ 1u, abort_flag)) break;
+        uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
+        uint8_t* sV = sK + Cfg::kKVBytes;
+        const int key0 = (t_begin + i) * BKV;
+        mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, key0, hkv, b);
+        mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, key0, hkv, b);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0 && n_my > 0) {
+      const uint32_t idesc_s = make_idesc(BKV, N, BF16, false, false);  // K tile, Q both K-major
+      const uint32_t idesc_o = make_idesc(D, N, BF16, true, false);     // V^T MN-major, P^T K-major
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_pv = [&](int i) -> bool {
+        const int st = i % kDecStages, use = i / kDecStages, buf = i & 1;
+        if (!mbar_wait(&p_full[buf], (i >> 1) & 1u, abort_flag)) return false;
+        if (!mbar_wait(&v_full[st], use & 1u, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
+        const uint32_t p_addr = smem_u32(sP + buf * Cfg::kPBytes);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          // A = V^T: 64-dim slabs BKV*128 bytes apart (LBO), 8-key groups 1024 bytes apart (SBO),
+          // 16 keys = 2048 bytes per step. B = P^T: key slab kk/4, 32 bytes per step.
+          const uint64_t da = smem_desc_sw128(v_addr + kk * 2048, BKV * 128, 1024u);
+          const uint64_t db = smem_desc_sw128(p_addr + (kk / 4) * (N * 128) + (kk % 4) * 32, 16u, 1024u);
+          umma_f16(tmem_base + Cfg::kOCol, da, db, idesc_o, (i | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[st]);
+        umma_commit(pv_done);
+        return true;
+      };
+      for (int i = 0; i < n_my && ok; ++i) {
+        const int st = i % kDecStages, use = i / kDecStages, buf = i & 1;
+        if (!mbar_wait(&k_full[st], use & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // S^T buffer `buf` was read by the softmax of tile i-2, whose P this thread has already waited for
+        const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t koff = (kk / 4) * (BKV * 128) + (kk % 4) * 32;
+          const uint32_t qoff = (kk / 4) * (N * 128) + (kk % 4) * 32;
+          umma_f16(tmem_base + Cfg::kSCol + buf * N, smem_desc_sw128(k_addr + koff, 16u, 1024u),
+                   smem_desc_sw128(q_addr + qoff, 16u, 1024u), idesc_s, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[buf]);
+        if (i > 0) ok = issue_pv(i - 1);
+      }
+      if (ok) issue_pv(n_my - 1);
+    }
+  } else {
+    // ------------------------------------------------------ softmax / output --
+    const int quarter = warp & 3;
+    const int tid = quarter * 32 + lane;            // key of the tile, later output dim
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale_log2;
+    float m[N], lsum[N];
+#pragma unroll
+    for (int n = 0; n < N; ++n) { m[n] = -CUDART_INF_F; lsum[n] = 0.f; }
+    bool ok = true;
+    for (int i = 0; i < n_my && ok; ++i) {
+      const int buf = i & 1;
+      if (!mbar_wait(&s_full[buf], (i >> 1) & 1u, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[N];
+      if (N == 16) tmem_ld_32x16(tmem_base + lane_sel + Cfg::kSCol + buf * N, *reinterpret_cast<uint32_t(*)[16]>(&sv[0]));
+      else tmem_ld_32x32_at(tmem_base + lane_sel + Cfg::kSCol + buf * N, &sv[0]);
+      tmem_wait_ld();
+      const bool visible = (t_begin + i) * BKV + tid < p.Sk;
+      float* redb = red + buf * 4 * N;
+#pragma unroll
+      for (int n = 0; n < N; ++n) {
+        if (!visible) sv[n] = 0xff800000u;
+        const float wm = warp_max_f32(__uint_as_float(sv[n]));
+        if (lane == 0) redb[quarter * N + n] = wm;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      float alpha[N];
+      bool grow = false;
+#pragma unroll
+      for (int n = 0; n < N; ++n) {
+        const float mx = fmaxf(fmaxf(redb[n], redb[N + n]), fmaxf(redb[2 * N + n], redb[3 * N + n]));
+        alpha[n] = 1.f;
+        if ((mx - m[n]) * sl2 > kRescaleThreshold) {   // also the first tile (m = -inf)
+          alpha[n] = ex2_approx((m[n] - mx) * sl2);
+          m[n] = mx;
+          grow = true;
+        }
+      }
+      if (grow) {   // same decision in every thread: m is replicated
+#pragma unroll
+        for (int n = 0; n < N; ++n) lsum[n] *= alpha[n];
+        if (i > 0) {
+          if (!mbar_wait(pv_done, (i - 1) & 1u, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          uint32_t o[N];
+          if (N == 16) tmem_ld_32x16(tmem_base + lane_sel + Cfg::kOCol, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
+          else tmem_ld_32x32_at(tmem_base + lane_sel + Cfg::kOCol, &o[0]);
+          tmem_wait_ld();
+#pragma unroll
+          for (int n = 0; n < N; ++n) o[n] = __float_as_uint(__uint_as_float(o[n]) * alpha[n]);
+          if (N == 16) tmem_st_32x16(tmem_base + lane_sel + Cfg::kOCol, *reinterpret_cast<const uint32_t(*)[16]>(&o[0]));
+          else tmem_st_32x32(tmem_base + lane_sel + Cfg::kOCol, &o[0]);
+          tmem_wait_st();
+        }
+      }
+      // P^T row n, key tid: slab tid/64, 16-byte chunk (tid%64)/8 XOR-swizzled by (n & 7)
+      uint8_t* pb = sP + buf * Cfg::kPBytes + (tid >> 6) * (N * 128) + (tid & 7) * 2;
+      const int chunk = (tid & 63) >> 3;
+#pragma unroll
+      for (int n = 0; n < N; ++n) {
+        const float mb = (m[n] == -CUDART_INF_F ? 0.f : m[n]) * sl2;
+        const float pe = ex2_approx(fmaf(__uint_as_float(sv[n]), sl2, -mb));
+        lsum[n] += pe;
+        const uint16_t bits = BF16 ? f32_to_bf16_bits(pe) : f32_to_f16_bits(pe);
+        *reinterpret_cast<uint16_t*>(pb + n * 128 + ((chunk ^ (n & 7)) << 4)) = bits;
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[buf]);
+    }
+    // this CTA's partial result: O^T row `tid` (an output dim), m, l
+    if (ok && n_my > 0) ok = mbar_wait(pv_done, (n_my - 1) & 1u, abort_flag);
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // every softmax thread is past its last read of `red`
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+      float v = lsum[n];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) red[quarter * N + n] = v;
+    }
+    uint32_t o[N];
+    if (ok && n_my > 0) {
+      tc_fence_after();
+      if (N == 16) tmem_ld_32x16(tmem_base + lane_sel + Cfg::kOCol, *reinterpret_cast<uint32_t(*)[16]>(&o[0]));
+      else tmem_ld_32x32_at(tmem_base + lane_sel + Cfg::kOCol, &o[0]);
+      tmem_wait_ld();
+    } else {
+#pragma unroll
+      for (int n = 0; n < N; ++n) o[n] = 0u;
+    }
+#pragma unroll
+    for (int n = 0; n < N; ++n) comb_o[n * 128 + tid] = __uint_as_float(o[n]);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid < N) {
+      float mm = m[0];   // m is a register array: select without dynamic indexing
+#pragma unroll
+      for (int n = 1; n < N; ++n) mm = tid == n ? m[n] : mm;
+      comb_ml[tid] = mm;
+      comb_ml[N + tid] = (red[tid] + red[N + tid]) + (red[2 * N + tid] + red[3 * N + tid]);
+    }
+  }
+
+  // ---- merge the splits: CTA 0 of the cluster reads every partial through DSMEM --
+  cluster.sync();
+  if (split == 0 && warp >= 2 && !*abort_flag) {
+    const int tid = (warp & 3) * 32 + lane;
+    for (int n = 0; n < R; ++n) {
+      float M = -CUDART_INF_F;
+      for (int c = 0; c < splits; ++c) {
+        const float* ml = cluster.map_shared_rank(comb_ml, c);
+        if (ml[N + n] > 0.f) M = fmaxf(M, ml[n]);
+      }
+      float L = 0.f, acc = 0.f;
+      for (int c = 0; c < splits; ++c) {
+        const float* ml = cluster.map_shared_rank(comb_ml, c);
+        const float lc = ml[N + n];
+        if (lc > 0.f) {
+          const float w = ex2_approx((ml[n] - M) * p.scale_log2);
+          L += w * lc;
+          acc += w * cluster.map_shared_rank(comb_o, c)[n * 128 + tid];
+        }
+      }
+      const int g = n / p.Sq, s = n - g * p.Sq;
+      const float val = L > 0.f ? acc / L : 0.f;
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(hq0 + g) * p.o_sh +
+                       static_cast<int64_t>(s) * p.o_ss;
+      orow[tid] = BF16 ? f32_to_bf16_bits(val) : f32_to_f16_bits(val);
+      if (tid == 0 && p.lse)
+        p.lse[(static_cast<int64_t>(b) * p.Hq + hq0 + g) * p.Sq + s] = L > 0.f ? M * p.scale + logf(L) : -CUDART_INF_F;
+    }
+  }
+  cluster.sync();   // peers keep their shared memory alive until CTA 0 has read it
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
 bool make_qkv_map(CUtensorMap* m, const b200Tensor* t, uint32_t box_rows, uint32_t box_heads, const char** err) {
   // t: (B, H, S, D) view; tensor-map dims innermost first: D, S, H, B
   const uint64_t dims[4] = {(uint64_t)t->sizes[3], (uint64_t)t->sizes[2], (uint64_t)t->sizes[1], (uint64_t)t->sizes[0]};
@@ -676,6 +992,44 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
   return check_launch("b200_sdpa_flash_fwd");
 }
 
+template <bool BF16>
+b200Status launch_decode(const b200Tensor* q, const b200Tensor* k, const b200Tensor* v, AttnParams p, cudaStream_t s) {
+  using Cfg = DecCfg<16>;
+  CUtensorMap tq, tk, tv;
+  const char* err = "";
+  const int G = p.Hq / p.Hkv;
+  B200_REQUIRE(make_qkv_map(&tq, q, (uint32_t)p.Sq, (uint32_t)G, &err) && make_qkv_map(&tk, k, BKV, 1, &err) &&
+               make_qkv_map(&tv, v, BKV, 1, &err), B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: %s", err);
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<16, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  // split the keys over a cluster until the grid covers the SMs a few times over
+  const int n_tiles = (p.Sk + BKV - 1) / BKV;
+  const int ctas = p.B * p.Hkv;
+  int splits = 1;
+  while (splits < 8 && ctas * splits < 4 * 148 && n_tiles >= splits * 4) splits *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, p.Hkv, p.B);
+  cfg.blockDim = dim3(kDecThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<16, BF16>, tq, tk, tv, p, splits);
+  B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
+  return check_launch("b200_sdpa_flash_fwd");
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -713,7 +1067,7 @@ extern "C" b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tenso
                  B200_BAD_PARAM, "b200_sdpa_flash_fwd: lse must be contiguous f32 (B,Hq,Sq)");
     p.lse = static_cast<float*>(lse->data);
   }
-  p.causal = is_causal ? 1 : 0;
+  p.causal = (is_causal && p.Sq > 1) ? 1 : 0;   // a single query row sees every key either way
   const int G = p.Hq / p.Hkv;
   p.packed = (!p.causal && G * p.Sq <= BQ && p.Sq <= 256 && G <= 256 && (G == 1 || q->strides[1] > 0)) ? 1 : 0;
   p.is_bf16 = q->dtype == B200_BF16;
@@ -724,6 +1078,8 @@ extern "C" b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tenso
   B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: device error word unavailable");
   B200_REQUIRE(p.B <= 65535 && p.Hq <= 65535, B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: batch / heads too large");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p.packed && p.D == 128 && G * p.Sq <= 16)
+    return p.is_bf16 ? launch_decode<true>(q, k, v, p, s) : launch_decode<false>(q, k, v, p, s);
   if (p.D == 128) return launch_attention<128>(q, k, v, p, s);
   return launch_attention<64>(q, k, v, p, s);
 }
