@@ -176,7 +176,7 @@ b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64
  * critical serving loop, a caller that owns no allocator, a plugin handed only
  * input and output buffers). It takes no workspace: its scratch is a fixed 8 MiB
  * array inside the library (held by every GPU that loads the library, until
- * exit), enough for about 490 000 source rows in the row-index form; a larger
+ * exit), enough for about 470 000 source rows in the row-index form; a larger
  * problem is refused with B200_NOT_SUPPORTED and a message that says how much
  * was needed. It calls no allocation routine of any kind.
  * - The first call on each device looks up the array's device address; make

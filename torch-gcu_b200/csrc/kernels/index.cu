@@ -239,11 +239,11 @@ index_generic_kernel(U* out, const U* src, int64_t n, StridedIndexer<2 + kMaxInd
 
 // ------------------------------------------------ stable LSD radix sort ----
 // Sorts n (key, value) uint32 pairs by key, 8 bits per pass, stable.
-// Tile = 256 threads x 16 items; warp w owns items [w*512, (w+1)*512) of the
+// Tile = 256 threads x 4 items; warp w owns items [w*128, (w+1)*128) of the
 // tile, read 32 consecutive items per round.
 constexpr int kSortThreads = 256;
-constexpr int kItemsPerThread = 16;
-constexpr int kTile = kSortThreads * kItemsPerThread;  // 4096
+constexpr int kItemsPerThread = 4;
+constexpr int kTile = kSortThreads * kItemsPerThread;  // 1024
 constexpr int kWarps = kSortThreads / 32;
 constexpr int kMaxPasses = 4;
 
@@ -267,55 +267,65 @@ radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int pass, int nb
   hist[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x] = sh[threadIdx.x];
 }
 
-// One block: exclusive scan of 256*nblocks counters, in place.
-__global__ void __launch_bounds__(1024)
-radix_scan_kernel(uint32_t* hist, int64_t per_pass) {
-  __shared__ uint32_t warp_tot[32];
-  __shared__ uint32_t carry_s;
-  uint32_t* h = hist;
-  if (threadIdx.x == 0) carry_s = 0;
-  __syncthreads();
+// Exclusive scan over the 256 threads of a block; *total gets the sum. `sh` holds
+// one word per warp and may be reused after the call returns.
+__device__ __forceinline__ uint32_t block_scan_256(uint32_t v, uint32_t* sh, uint32_t* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int64_t base = 0; base < per_pass; base += 1024) {
-    const int64_t i = base + threadIdx.x;
-    const uint32_t v = i < per_pass ? h[i] : 0u;
-    uint32_t inc = v;
+  uint32_t inc = v;
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
-      if (lane >= o) inc += t;
-    }
-    if (lane == 31) warp_tot[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t w = warp_tot[lane];
-      uint32_t winc = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        uint32_t t = __shfl_up_sync(0xffffffffu, winc, o);
-        if (lane >= o) winc += t;
-      }
-      warp_tot[lane] = winc - w;  // exclusive
-    }
-    __syncthreads();
-    const uint32_t carry = carry_s;
-    if (i < per_pass) h[i] = carry + warp_tot[warp] + inc - v;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry_s = carry + warp_tot[31] + inc;
-    __syncthreads();
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
   }
+  __syncthreads();   // earlier readers of sh are done
+  if (lane == 31) sh[warp] = inc;
+  __syncthreads();
+  uint32_t before = 0, all = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const uint32_t c = sh[w];
+    if (w < warp) before += c;
+    all += c;
+  }
+  *total = all;
+  return before + inc - v;
+}
+
+// Block d scans, in place, the row of tile counts of digit d (exclusive) and
+// leaves the digit's total in totals[d]; the scatter kernel adds the scan over
+// the 256 totals itself.
+__global__ void __launch_bounds__(kSortThreads)
+radix_scan_rows_kernel(uint32_t* __restrict__ hist, int nblocks, uint32_t* __restrict__ totals) {
+  __shared__ uint32_t sh[kWarps];
+  uint32_t* row = hist + static_cast<int64_t>(blockIdx.x) * nblocks;
+  uint32_t carry = 0;
+  for (int base = 0; base < nblocks; base += kSortThreads) {
+    const int i = base + threadIdx.x;
+    const uint32_t v = i < nblocks ? row[i] : 0u;
+    uint32_t total;
+    const uint32_t ex = block_scan_256(v, sh, &total);
+    if (i < nblocks) row[i] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = carry;
 }
 
 // vals_in == nullptr: the value of item i is i (first pass).
 __global__ void __launch_bounds__(kSortThreads)
 radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
-                     int pass, int nblocks, const uint32_t* __restrict__ hist_scanned) {
+                     int pass, int nblocks, const uint32_t* __restrict__ hist_scanned,
+                     const uint32_t* __restrict__ totals) {
   __shared__ uint32_t warp_count[kWarps][256];  // sweep 1: counts; then exclusive base per warp
   __shared__ uint32_t digit_base[256];
+  __shared__ uint32_t scan_sh[kWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kWarps * 256; i += kSortThreads) (&warp_count[0][0])[i] = 0;
-  digit_base[threadIdx.x] = hist_scanned[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x];
+  {
+    uint32_t all;
+    const uint32_t first = block_scan_256(totals[threadIdx.x], scan_sh, &all);   // where digit threadIdx.x starts
+    digit_base[threadIdx.x] = first + hist_scanned[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x];
+  }
   __syncthreads();
 
   const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItemsPerThread * 32);
@@ -493,17 +503,17 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
     for (uint32_t p = beg; p < end; p += 32) {
       const uint32_t cnt = min(32u, end - p);
       const uint32_t mine = lane < cnt ? sorted_src[p + lane] : 0xffffffffu;
-      uint32_t k = 0;
-      for (; k + 4 <= cnt; k += 4) {  // four source rows in flight, added in order
+      for (uint32_t k = 0; k < cnt; k += 4) {  // four source rows in flight, added in order
         VecT b0[4], b1[4];
         bool okr[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const uint32_t sid = __shfl_sync(0xffffffffu, mine, k + u);
-          okr[u] = sid < n_src;  // out-of-range sources were parked with an invalid id
+          const uint32_t sid = __shfl_sync(0xffffffffu, mine, (k + u) & 31u);
+          // past the end of the segment, or an out-of-range source parked with an invalid id
+          okr[u] = k + u < cnt && sid < n_src;
           const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(okr[u] ? sid : 0u) * inner);
-          if (h0) b0[u] = srow[c0];
-          if (h1) b1[u] = srow[c1];
+          if (h0 && okr[u]) b0[u] = srow[c0];
+          if (h1 && okr[u]) b1[u] = srow[c1];
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -513,19 +523,6 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
             if (h0) a0[e] = seq_add(a0[e], to_accum<A>(b0[u].v[e]));
             if (h1) a1[e] = seq_add(a1[e], to_accum<A>(b1[u].v[e]));
           }
-        }
-      }
-      for (; k < cnt; ++k) {
-        const uint32_t sid = __shfl_sync(0xffffffffu, mine, k);
-        if (sid >= n_src) continue;
-        const VecT* srow = reinterpret_cast<const VecT*>(src + static_cast<int64_t>(sid) * inner);
-        VecT b0, b1;
-        if (h0) b0 = srow[c0];
-        if (h1) b1 = srow[c1];
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          if (h0) a0[e] = seq_add(a0[e], to_accum<A>(b0.v[e]));
-          if (h1) a1[e] = seq_add(a1[e], to_accum<A>(b1.v[e]));
         }
       }
     }
@@ -583,7 +580,7 @@ SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range) */, in
   p.nblocks = static_cast<int>((n + kTile - 1) / kTile);
   if (p.nblocks < 1) p.nblocks = 1;
   p.keys_bytes = align256(static_cast<size_t>(n) * 4);
-  p.hist_bytes = align256(static_cast<size_t>(256) * p.nblocks * 4);
+  p.hist_bytes = align256((static_cast<size_t>(256) * p.nblocks + 256) * 4);   // tile counts, then digit totals
   p.seg_bytes = n_dst_rows >= 0 ? align256(static_cast<size_t>(n_dst_rows + 2) * 4) : 0;
   p.total = 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
   return p;
@@ -596,8 +593,9 @@ b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint3
   uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
   for (int pass = 0; pass < p.passes; ++pass) {
     radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, p.n, pass, p.nblocks, hist);
-    radix_scan_kernel<<<1, 1024, 0, s>>>(hist, static_cast<int64_t>(256) * p.nblocks);
-    radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist);
+    uint32_t* totals = hist + static_cast<size_t>(256) * p.nblocks;
+    radix_scan_rows_kernel<<<256, kSortThreads, 0, s>>>(hist, p.nblocks, totals);
+    radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist, totals);
     uint32_t* t = kin; kin = kout; kout = t;
     vin = vout;
     vout = vother;
