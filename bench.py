@@ -369,6 +369,14 @@ def run_micro(name):
         out = torch.empty(B, S, Hq, D, dtype=bf, device=dev).transpose(1, 2)
         fn = ops.bind("sdpa_flash_fwd", out, None, q, k_, v_, ctypes.c_int32(1), ctypes.c_double(D ** -0.5))
         work = {"flops": 4 * B * Hq * S * S * D // 2}
+    elif name == "decode":
+        B, Hq, Hkv, Sk, D = 16, 32, 8, 4096, 128
+        q = torch.randn(B, Hq, 1, D, device=dev).to(bf)
+        k_ = torch.randn(B, Hkv, Sk, D, device=dev).to(bf)
+        v_ = torch.randn(B, Hkv, Sk, D, device=dev).to(bf)
+        out = torch.empty(B, 1, Hq, D, dtype=bf, device=dev).transpose(1, 2)
+        fn = ops.bind("sdpa_flash_fwd", out, None, q, k_, v_, ctypes.c_int32(0), ctypes.c_double(D ** -0.5))
+        work = {"bytes": 2 * B * Hkv * Sk * D * 2}
     elif name == "swiglu":
         g_, u_ = torch.randn(4096, 14336, device=dev).to(bf), torch.randn(4096, 14336, device=dev).to(bf)
         out = torch.empty_like(g_)
@@ -405,7 +413,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
-    ap.add_argument("--micro", default="", help="gemm | sdpa | swiglu | scatter: a 3-launch case for profiler captures")
+    ap.add_argument("--micro", default="", help="gemm | sdpa | decode | swiglu | scatter: a 3-launch case for profiler captures")
     args = ap.parse_args()
     if args.micro:
         run_micro(args.micro)
