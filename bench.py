@@ -255,9 +255,13 @@ def gemm_roofline(dev, tf_peak, peak_kind, world):
     w = (torch.randn(n, k) * 0.02).bfloat16().to(dev)
     ms = _time_gcu(lambda: torch.mm(a, w.t()))
     tf = 2 * m * n * k / ms / 1e9
+    # DRAM traffic: the profiler capture of the same kernel on 8192x4096x4096 (profiles/) moved 164.8 MB for
+    # 167.8 MB of operands and output; traffic grows with the operand bytes, so that ratio is applied here.
+    operand_bytes = 2 * (m * k + n * k + m * n)
     return {"bound": "tensor", "kernel": "gemm_tc_kernel<256> (gate/up projection %dx%dx%d)" % (m, n, k),
             "achieved": round(tf, 1), "peak": tf_peak, "unit": "TFLOP/s", "frac": round(tf / tf_peak, 3),
-            "traffic": None, "peak_kind": peak_kind + " bf16 burst"}
+            "traffic": int(operand_bytes * 164.8 / 167.8), "traffic_unit": "bytes per launch, scaled from a smaller capture",
+            "peak_kind": peak_kind + " bf16 burst"}
 
 
 def contraction_table(dev, tf_peak):

@@ -139,3 +139,49 @@ def test_layer_projection_shapes(ops):
         rows = torch.tensor([0, 1, 127, 128, 255, 300, 511])
         ref = (x[rows].float() @ w.float().t())
         close(out[rows], ref.to(BF), 1.6e-2, 1e-2)
+
+
+def _sampled_close(out, a_f, b_f, rows, cols, K, extra=None, alpha=1.0, beta=1.0):
+    ref = alpha * (a_f[rows] @ b_f[:, cols])
+    if extra is not None:
+        ref = ref + beta * extra.float()[rows][:, cols]
+    close(out[dev(rows)][:, dev(cols)], ref.to(out.dtype), 1.6e-2, 1e-2 * max(1.0, (K / 64) ** 0.5))
+
+
+@pytest.mark.parametrize("M,N,K", [(3000, 3500, 520), (4096, 4096, 256), (2309, 4100, 72)])
+def test_mm_large_enough_for_cta_pairs(ops, M, N, K):
+    """Products with at least 148 tiles of 256 x 256 run on the two-CTA kernel: ragged
+    edges in M, N and K, every operand layout, scaling and an addend; checked on
+    sampled rows and columns that cover both CTAs of a pair and the tile borders."""
+    g = torch.Generator().manual_seed(47)
+    a = torch.randn(M, K, generator=g).to(BF)
+    b = torch.randn(K, N, generator=g).to(BF)
+    af, bf_ = a.float(), b.float()
+    rows = torch.tensor(sorted({0, 1, 127, 128, 129, 255, 256, 383, 384, 511, 512, M // 2, M - 130, M - 2, M - 1}))
+    cols = torch.tensor(sorted({0, 31, 32, 127, 128, 255, 256, 257, N // 2, N - 129, N - 33, N - 1}))
+    out = torch.empty(M, N, dtype=BF, device=DEV)
+    layouts = [(dev(a), dev(b.t().contiguous()).t()),                      # both K-contiguous
+               (dev(a), dev(b)),                                           # B N-contiguous
+               (dev(a.t().contiguous()).t(), dev(b)),                      # A M-contiguous
+               (dev(a.t().contiguous()).t(), dev(b.t().contiguous()).t())]
+    for x, y in layouts:
+        out.zero_()
+        ops.mm(out, x, y)
+        assert ops.device_error_fetch() == 0
+        _sampled_close(out, af, bf_, rows, cols, K)
+    add = torch.randn(M, N, generator=g).to(BF)
+    ops.addmm(out, dev(add), layouts[0][0], layouts[0][1], beta=-0.5, alpha=0.25)
+    _sampled_close(out, af, bf_, rows, cols, K, add, alpha=0.25, beta=-0.5)
+    # whole-matrix check against the one fp32 product, loose: catches a misplaced tile
+    ops.mm(out, layouts[0][0], layouts[0][1])
+    full = (af @ bf_)
+    assert (out.float().cpu() - full).abs().max().item() <= 0.02 * full.abs().max().item() + 0.5
+
+
+def test_bmm_large_enough_for_cta_pairs(ops):
+    g = torch.Generator().manual_seed(48)
+    a = torch.randn(40, 500, 136, generator=g).to(torch.float16)
+    b = torch.randn(40, 136, 520, generator=g).to(torch.float16)
+    out = torch.empty(40, 500, 520, dtype=torch.float16, device=DEV)
+    ops.bmm(out, dev(a), dev(b))
+    tc_close(out, a, b)

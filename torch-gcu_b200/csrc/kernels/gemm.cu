@@ -335,6 +335,267 @@ b200Status launch_tc(const Operand& oa, const Operand& ob, GemmParams p, cudaStr
   return check_launch("matmul (tcgen05)");
 }
 
+// ---------------------------------------------------------------------------
+// Two-CTA variant (cta_group::2): a cluster of two CTAs on neighbouring SMs owns a
+// 256 x 256 output tile. Each CTA loads its 128 rows of A and its 128 columns of B
+// (32 KB per stage instead of 48, six stages instead of four), one thread of the
+// even CTA issues 256 x 256 x 16 MMAs that read both CTAs' shared memory, and each
+// CTA's tensor memory receives its own 128 accumulator rows. Operand traffic per SM
+// drops by a third, which is what bounds the one-CTA kernel.
+//   full[s]      lives in the even CTA; both CTAs' TMA loads complete on it
+//   empty[s]     in each CTA, released by a commit that arrives in both CTAs
+//   acc_full[a]  in each CTA (same commit form); acc_empty[a] in the even CTA,
+//                eight arrivals: the four epilogue warps of both CTAs
+constexpr int BN2 = 256;            // columns of the pair's tile
+constexpr int BM2 = 2 * BM;         // rows of the pair's tile
+constexpr int kStageHalfB = (BN2 / 2) * BK * 2;
+constexpr int kStage2 = BM * BK * 2 + kStageHalfB;   // 32 KB per CTA
+constexpr int kStages2 = 6;
+constexpr int kSmem2 = kStages2 * kStage2 + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Tile load into this CTA's shared memory whose completion is counted on a barrier of the even CTA.
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once
+// every MMA issued so far has completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(mask)
+               : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStage2);
+  uint64_t* full = bars;                       // [kStages2], used in the even CTA
+  uint64_t* empty = bars + kStages2;           // [kStages2]
+  uint64_t* acc_full = empty + kStages2;       // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2], used in the even CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();     // 0: issues the MMAs
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int tiles_m = (p.M + BM2 - 1) / BM2, tiles_n = (p.N + BN2 - 1) / BN2;
+  const int n_tiles = tiles_m * tiles_n * p.batch;
+  const int n_k = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages2; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // both CTAs' barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer --
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        int b, tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+        const int row0 = tm * BM2 + static_cast<int>(rank) * BM;          // this CTA's rows of A
+        const int col0 = tn * BN2 + static_cast<int>(rank) * (BN2 / 2);   // this CTA's columns of B
+        for (int k = 0; k < n_k; ++k) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * kStage2;
+          uint8_t* sb = sa + BM * BK * 2;
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * kStage2);   // the bytes of both CTAs
+          if (!p.a_mn_major) {
+            tma_load_3d_pair(sa, &tmap_a, bar, k * BK, row0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d_pair(sa + j * 8192, &tmap_a, bar, row0 + j * 64, k * BK, b);
+          }
+          if (!p.b_mn_major) {
+            tma_load_3d_pair(sb, &tmap_b, bar, k * BK, col0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN2 / 2 / 64; ++j) tma_load_3d_pair(sb + j * 8192, &tmap_b, bar, col0 + j * 64, k * BK, b);
+          }
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer --
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(BM2, BN2, p.is_bf16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_step = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_step = p.b_mn_major ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+        const int ab = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[ab], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(ab * BN2);
+        for (int k = 0; k < n_k; ++k) {
+          if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * kStage2);
+          const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = smem_desc_sw128(sa + kk * a_step, a_lbo, 1024u);
+            const uint64_t db = smem_desc_sw128(sb + kk * b_step, b_lbo, 1024u);
+            umma_f16_pair(d_tmem, da, db, idesc, (k | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage]);
+          if (++stage == kStages2) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(&acc_full[ab]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue --
+    const int quarter = warp & 3;
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++it) {
+      const int ab = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1u;
+      int b, tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+      if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM2 + static_cast<int>(rank) * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(row) * p.o_sm;
+      const uint16_t* crow = p.cin ? static_cast<const uint16_t*>(p.cin) + b * p.c_sb + static_cast<int64_t>(row) * p.c_sm
+                                   : nullptr;
+      const bool vec_ok = (p.o_sm % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) + 2 * b * p.o_sb) % 16 == 0);
+#pragma unroll 1
+      for (int c = 0; c < BN2; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * BN2 + c), r);
+        tmem_wait_ld();
+        const int col0 = tn * BN2 + c;
+        if (row_ok && col0 < p.N) {
+          alignas(16) uint16_t o[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float v = p.alpha * __uint_as_float(r[j]);
+            if (crow && col0 + j < p.N) {
+              const uint16_t cb = crow[static_cast<int64_t>(col0 + j) * p.c_sn];
+              v += p.beta * (p.is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+            }
+            o[j] = p.is_bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+          }
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<int4*>(orow + col0 + q * 8) = *reinterpret_cast<const int4*>(o + q * 8);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) orow[col0 + j] = o[j];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // nothing of the peer is touched after this point
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
+b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaStream_t s) {
+  CUtensorMap ta, tb;
+  const char* err = "";
+  B200_REQUIRE(encode_tmap_16bit(&ta, oa.base, 3, oa.dims, oa.strides, oa.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  B200_REQUIRE(encode_tmap_16bit(&tb, ob.base, 3, ob.dims, ob.strides, ob.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + BN2 - 1) / BN2) * p.batch;
+  const int pairs = sm_count_current_device() / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  gemm_tc2_kernel<<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
+  return check_launch("matmul (tcgen05, two-CTA)");
+}
+
+// B200_GEMM_PAIR=0 keeps every product on the one-CTA kernel (for A/B timing).
+bool pair_kernel_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("B200_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 }  // namespace
 
 // Shared implementation of mm / addmm / bmm / baddbmm.
@@ -373,6 +634,9 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
     if (tiles(256) < sms && N > 128) bn = 128;
     if (tiles(bn) < sms && N > 64) bn = 64;
     if (N <= 64) bn = 64; else if (N <= 128 && bn > 128) bn = 128;
+    // enough 256 x 256 tiles for two rounds of CTA pairs: the two-CTA kernel
+    const bool pair_kernel = ((M + BM2 - 1) / BM2) * ((N + BN2 - 1) / BN2) * batch >= sms && pair_kernel_enabled();
+    if (pair_kernel) bn = BN2 / 2;   // B is loaded in per-CTA halves
     Operand oa, ob;
     const bool a_ok = describe_operand(a->data, M, K, batch, a->strides[o], a->strides[o + 1], batched ? a->strides[0] : 0, BM, &oa);
     const bool b_ok = describe_operand(b->data, N, K, batch, b->strides[o + 1], b->strides[o], batched ? b->strides[0] : 0, bn, &ob);
@@ -388,6 +652,7 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
       }
       p.error_word = device_error_word();
       B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+      if (pair_kernel) return launch_tc2(oa, ob, p, s);
       if (bn == 256) return launch_tc<256>(oa, ob, p, s);
       if (bn == 128) return launch_tc<128>(oa, ob, p, s);
       return launch_tc<64>(oa, ob, p, s);
