@@ -185,3 +185,25 @@ def test_bmm_large_enough_for_cta_pairs(ops):
     out = torch.empty(40, 500, 520, dtype=torch.float16, device=DEV)
     ops.bmm(out, dev(a), dev(b))
     tc_close(out, a, b)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (100, 520, 1000), (1, 6144, 4096), (128, 1032, 2048)])
+def test_mm_skinny_split_k(ops, M, N, K):
+    """Few rows against a large weight matrix (the decode step): K is split over a
+    cluster and the partial tiles are summed in a fixed order, so two runs agree
+    bit for bit."""
+    g = torch.Generator().manual_seed(49)
+    a = torch.randn(M, K, generator=g).to(BF)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(BF)
+    out = torch.empty(M, N, dtype=BF, device=DEV)
+    ops.mm(out, dev(a), dev(w).t())
+    assert ops.device_error_fetch() == 0
+    tc_close(out, a, w.t())
+    again = torch.empty_like(out)
+    ops.mm(again, dev(a), dev(w).t())
+    assert torch.equal(out, again)
+    ops.mm(again, dev(a.t().contiguous()).t(), dev(w.t().contiguous()))      # both operands MN-contiguous
+    tc_close(again, a, w.t())
+    add = torch.randn(M, N, generator=g).to(BF)
+    ops.addmm(again, dev(add), dev(a), dev(w).t(), beta=0.5, alpha=2.0)
+    tc_close(again, a, w.t(), add, alpha=2.0, beta=0.5)

@@ -19,6 +19,7 @@
 #include "gemm_simt.cuh"
 #include "tc_common.cuh"
 
+#include <cooperative_groups.h>
 #include <mutex>
 
 namespace b200 {
@@ -587,6 +588,198 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
   return check_launch("matmul (tcgen05, two-CTA)");
 }
 
+// ---------------------------------------------------------------------------
+// Split-K variant for skinny products (M <= 128, e.g. one decode token per
+// sequence): streaming the weight matrix is all that matters, so the grid is one
+// wave of CTAs, two per SM, each with a 96 KB ring in flight. A cluster of `splits`
+// CTAs (2, 4 or 8) shares one 128 x 128 output tile; each CTA runs the TMA / MMA pipeline over its slice of K, parks its fp32
+// partial tile in shared memory, and after a cluster barrier every CTA sums one
+// band of rows over all partials through distributed shared memory, always in rank
+// order, so the result does not depend on timing.
+constexpr int BNS = 128;
+constexpr int kStageS = BM * BK * 2 + BNS * BK * 2;   // 32 KB
+constexpr int kStagesS = 3;                           // 96 KB: two CTAs per SM
+constexpr int kPartialStride = BNS + 1;               // padded: conflict-free rows and columns
+constexpr int kSmemS = kStagesS * kStageS + 1024 + 256;
+static_assert(BM * kPartialStride * 4 <= kStagesS * kStageS, "the partial tile reuses the drained stage ring");
+
+__global__ void __launch_bounds__(kGemmThreads, 2)
+gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmParams p, const int splits) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStagesS * kStageS);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kStagesS;
+  uint64_t* acc_full = empty + kStagesS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* partial = reinterpret_cast<float*>(smem);   // [BM][kPartialStride], valid after the ring drained
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BNS - 1) / BNS;
+  int b, tm, tn;
+  tile_coords(static_cast<int>(blockIdx.x) / splits, tiles_m, tiles_n, b, tm, tn);
+  const int n_k = (p.K + BK - 1) / BK;
+  const int per = (n_k + splits - 1) / splits;
+  const int k_begin = min(rank * per, n_k), k_end = min(k_begin + per, n_k);
+  const int n_my = k_end - k_begin;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStagesS; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, BNS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      for (int i = 0; i < n_my; ++i) {
+        const int stage = i % kStagesS;
+        const uint32_t phase = (i / kStagesS) & 1u;
+        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) break;
+        uint8_t* sa = smem + stage * kStageS;
+        uint8_t* sb = sa + BM * BK * 2;
+        const int k = k_begin + i;
+        mbar_arrive_expect_tx(&full[stage], kStageS);
+        if (!p.a_mn_major) {
+          tma_load_3d(sa, &tmap_a, &full[stage], k * BK, tm * BM, b);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, &tmap_a, &full[stage], tm * BM + j * 64, k * BK, b);
+        }
+        if (!p.b_mn_major) {
+          tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * BNS, b);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BNS / 64; ++j) tma_load_3d(sb + j * 8192, &tmap_b, &full[stage], tn * BNS + j * 64, k * BK, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_my > 0) {
+      const uint32_t idesc = make_idesc(BM, BNS, p.is_bf16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
+      const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u, a_step = p.a_mn_major ? 2048u : 32u;
+      const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u, b_step = p.b_mn_major ? 2048u : 32u;
+      bool ok = true;
+      for (int i = 0; i < n_my; ++i) {
+        const int stage = i % kStagesS;
+        const uint32_t phase = (i / kStagesS) & 1u;
+        if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * kStageS);
+        const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_f16(tmem_base, smem_desc_sw128(sa + kk * a_step, a_lbo, 1024u), smem_desc_sw128(sb + kk * b_step, b_lbo, 1024u),
+                   idesc, (i | kk) != 0 ? 1u : 0u);
+        umma_commit(&empty[stage]);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // this CTA's partial tile: tensor memory -> shared memory (zeros when the slice of K is empty)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    bool ok = true;
+    if (n_my > 0) ok = mbar_wait(acc_full, 0, abort_flag);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < BNS; c += 32) {
+      uint32_t r[32];
+      if (n_my > 0 && ok) {
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c), r);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) partial[row * kPartialStride + c + j] = __uint_as_float(r[j]);
+    }
+  }
+
+  tc_fence_before();
+  cluster.sync();
+  if (warp >= 2) {
+    // rows [rank * band, (rank + 1) * band) of the tile, summed over the partials in rank order
+    const int tid = (warp - 2) * 32 + lane;
+    const int band = (BM + splits - 1) / splits;
+    const int band_rows = max(0, min(BM, (rank + 1) * band) - rank * band);
+    for (int e = tid; e < band_rows * BNS; e += 128) {
+      const int lr = rank * band + e / BNS, col = e % BNS;
+      const int grow = tm * BM + lr, gcol = tn * BNS + col;
+      float acc = 0.f;
+      for (int c = 0; c < splits; ++c) acc += cluster.map_shared_rank(partial, c)[lr * kPartialStride + col];
+      if (grow < p.M && gcol < p.N) {
+        float v = p.alpha * acc;
+        if (p.cin) {
+          const uint16_t cb = static_cast<const uint16_t*>(p.cin)[b * p.c_sb + static_cast<int64_t>(grow) * p.c_sm +
+                                                                static_cast<int64_t>(gcol) * p.c_sn];
+          v += p.beta * (p.is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+        }
+        static_cast<uint16_t*>(p.out)[b * p.o_sb + static_cast<int64_t>(grow) * p.o_sm + gcol] =
+            p.is_bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+      }
+    }
+  }
+  cluster.sync();   // peers keep their partials alive until everyone has read them
+
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, BNS);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
+b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int splits, cudaStream_t s) {
+  CUtensorMap ta, tb;
+  const char* err = "";
+  B200_REQUIRE(encode_tmap_16bit(&ta, oa.base, 3, oa.dims, oa.strides, oa.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  B200_REQUIRE(encode_tmap_16bit(&tb, ob.base, 3, ob.dims, ob.strides, ob.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemS);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BNS - 1) / BNS) * p.batch;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * splits);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = kSmemS;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, ta, tb, p, splits);
+  B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
+  return check_launch("matmul (tcgen05, split-K)");
+}
+
 // B200_GEMM_PAIR=0 keeps every product on the one-CTA kernel (for A/B timing).
 bool pair_kernel_enabled() {
   static const bool on = [] {
@@ -637,6 +830,14 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
     // enough 256 x 256 tiles for two rounds of CTA pairs: the two-CTA kernel
     const bool pair_kernel = ((M + BM2 - 1) / BM2) * ((N + BN2 - 1) / BN2) * batch >= sms && pair_kernel_enabled();
     if (pair_kernel) bn = BN2 / 2;   // B is loaded in per-CTA halves
+    // skinny product that cannot fill the SMs with tiles alone: split K over a cluster
+    int splits = 1;
+    if (!pair_kernel && M <= BM && pair_kernel_enabled()) {
+      // one wave of two CTAs per SM: double the splits while tiles x splits fits and a slice keeps >= 4 k-steps
+      const int64_t t128 = ((N + BNS - 1) / BNS) * batch, n_k = (K + BK - 1) / BK;
+      while (splits < 8 && t128 * splits * 2 <= 2 * sms && n_k >= splits * 2 * 4) splits *= 2;
+      if (splits > 1) bn = BNS;
+    }
     Operand oa, ob;
     const bool a_ok = describe_operand(a->data, M, K, batch, a->strides[o], a->strides[o + 1], batched ? a->strides[0] : 0, BM, &oa);
     const bool b_ok = describe_operand(b->data, N, K, batch, b->strides[o + 1], b->strides[o], batched ? b->strides[0] : 0, bn, &ob);
@@ -653,6 +854,7 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
       p.error_word = device_error_word();
       B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
       if (pair_kernel) return launch_tc2(oa, ob, p, s);
+      if (splits > 1) return launch_splitk(oa, ob, p, splits, s);
       if (bn == 256) return launch_tc<256>(oa, ob, p, s);
       if (bn == 128) return launch_tc<128>(oa, ob, p, s);
       return launch_tc<64>(oa, ob, p, s);
