@@ -249,16 +249,19 @@ def _time_gcu(fn, reps=10):
 
 
 def gemm_roofline(dev, tf_peak, peak_kind, world):
-    """The dominant kernel of the step: the gate/up projection GEMM of one layer."""
+    """The dominant kernel of the step: the gate/up projection GEMM of one layer, with the
+    SwiGLU applied in its epilogue (two-CTA tcgen05 kernel)."""
+    from torch_gcu.gcu import efficient
     m, k, n = PREFILL_B * PREFILL_S, CFG["hidden"], 2 * CFG["ffn"] // world
     a = torch.randn(m, k).bfloat16().to(dev)
     w = (torch.randn(n, k) * 0.02).bfloat16().to(dev)
-    ms = _time_gcu(lambda: torch.mm(a, w.t()))
+    ms = _time_gcu(lambda: efficient.linear_swiglu(a, w))
     tf = 2 * m * n * k / ms / 1e9
-    # DRAM traffic: the profiler capture of the same kernel on 8192x4096x4096 (profiles/) moved 164.8 MB for
-    # 167.8 MB of operands and output; traffic grows with the operand bytes, so that ratio is applied here.
-    operand_bytes = 2 * (m * k + n * k + m * n)
-    return {"bound": "tensor", "kernel": "gemm_tc_kernel<256> (gate/up projection %dx%dx%d)" % (m, n, k),
+    # DRAM traffic: the profiler capture of the plain two-operand kernel on 8192x4096x4096 (profiles/) moved
+    # 164.8 MB for 167.8 MB of operands and output; traffic grows with those bytes, so that ratio is applied
+    # to this launch's operands and its (M, N/2) output.
+    operand_bytes = 2 * (m * k + n * k + m * n // 2)
+    return {"bound": "tensor", "kernel": "gemm_tc2_kernel<swiglu> (gate/up projection %dx%dx%d, SwiGLU in the epilogue)" % (m, n, k),
             "achieved": round(tf, 1), "peak": tf_peak, "unit": "TFLOP/s", "frac": round(tf / tf_peak, 3),
             "traffic": int(operand_bytes * 164.8 / 167.8), "traffic_unit": "bytes per launch, scaled from a smaller capture",
             "peak_kind": peak_kind + " bf16 burst"}

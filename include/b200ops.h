@@ -262,6 +262,14 @@ b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tenso
  * last dim (gate and up may be the two halves of one projection output).      */
 b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200Tensor* up,
                        b200Stream stream);
+/* Gate/up projection with the SwiGLU fused into the GEMM epilogue:
+ *   out (M,F) = silu(a @ w[0:F].T) * (a @ w[F:2F].T),
+ * a (M,K) and w (2F,K) bf16 / f16 with K contiguous (the nn.Linear weight of a
+ * fused gate/up projection, gate rows first). The activation is evaluated on the
+ * fp32 accumulators and rounded once; the (M,2F) intermediate is never written.
+ * No reference counterpart: the reference runs mm followed by pointwise ops.     */
+b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up,
+                          b200Stream stream);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

@@ -167,6 +167,13 @@ def test_fused_efficient_ops(dev):
     gate, up = torch.randn(17, 512, generator=g).to(bf), torch.randn(17, 512, generator=g).to(bf)
     s = efficient.swiglu(gate.to(dev), up.to(dev))
     assert torch.allclose(s.cpu().float(), aten_cpu.swiglu(gate, up).float(), rtol=2 ** -7, atol=1e-3)
+    xs = torch.randn(2, 300, 256, generator=g).to(torch.bfloat16)
+    wgu = (torch.randn(2 * 384, 256, generator=g) * 0.1).to(torch.bfloat16)
+    for xin in (xs, xs[:, :4]):   # the fused-epilogue GEMM (>= 512 rows) and the few-row path
+        ls = efficient.linear_swiglu(xin.to(dev), wgu.to(dev))
+        gu = xin.float() @ wgu.float().t()
+        ref = torch.nn.functional.silu(gu[..., :384]) * gu[..., 384:]
+        assert ls.shape == ref.shape and torch.allclose(ls.cpu().float(), ref, rtol=3e-2, atol=3e-2)
     s2 = efficient.swiglu_packed(torch.cat([gate, up], -1).to(dev))
     assert torch.equal(s2.cpu(), s.cpu())
 

@@ -207,3 +207,25 @@ def test_mm_skinny_split_k(ops, M, N, K):
     add = torch.randn(M, N, generator=g).to(BF)
     ops.addmm(again, dev(add), dev(a), dev(w).t(), beta=0.5, alpha=2.0)
     tc_close(again, a, w.t(), add, alpha=2.0, beta=0.5)
+
+
+@pytest.mark.parametrize("M,F,K,dtype", [(2048, 1024, 256, BF), (1000, 1100, 520, BF), (300, 136, 72, torch.float16),
+                                         (4096, 3584, 512, BF)])
+def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):
+    """Gate/up projection with silu(gate) * up applied in the GEMM epilogue, against
+    fp32 CPU arithmetic on the same operands; ragged M, F and K."""
+    g = torch.Generator().manual_seed(50)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(2 * F, K, generator=g) * (2.0 / K ** 0.5)).to(dtype)
+    out = torch.empty(M, F, dtype=dtype, device=DEV)
+    ops.mm_swiglu(out, dev(a), dev(w))
+    assert ops.device_error_fetch() == 0
+    gu = a.float() @ w.float().t()
+    ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    close(out, ref.to(dtype), 1.6e-2, 2e-2)
+    # the unfused pair of calls rounds the projection to 16 bits first: close, not identical
+    gu_dev = torch.empty(M, 2 * F, dtype=dtype, device=DEV)
+    ops.mm(gu_dev, dev(a), dev(w).t())
+    two = torch.empty_like(out)
+    ops.swiglu(two, gu_dev[:, :F], gu_dev[:, F:])
+    close(out, two.cpu(), 3e-2, 3e-2)

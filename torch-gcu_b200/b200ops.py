@@ -287,6 +287,11 @@ def swiglu(out, gate, up, stream=None):
     check(lib().b200_swiglu(_ref(view(out)), _ref(view(gate)), _ref(view(up)), _stream(stream)))
 
 
+def mm_swiglu(out, a, w_gate_up, stream=None):
+    """out (M,F) = silu(a @ w[:F].T) * (a @ w[F:].T), the SwiGLU fused into the GEMM epilogue."""
+    check(lib().b200_mm_swiglu(_ref(view(out)), _ref(view(a)), _ref(view(w_gate_up)), _stream(stream)))
+
+
 def mm(out, a, b, stream=None):
     check(lib().b200_mm(_ref(view(out)), _ref(view(a)), _ref(view(b)), _stream(stream)))
 

@@ -81,6 +81,7 @@ struct GemmParams {
   const void* cin;
   int64_t c_sb, c_sm, c_sn;
   unsigned int* error_word;
+  int up_offset;                 // fused SwiGLU: row of B where the "up" half starts (= output columns F)
 };
 
 template <int BN> struct GemmCfg {
@@ -397,9 +398,16 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+// SWIGLU: B is a (2F x K) gate/up weight (gate rows first). The even CTA loads 128
+// gate rows, the odd CTA the matching 128 up rows, so accumulator columns [0,128)
+// hold gate and [128,256) up for the same 128 output columns, and the epilogue
+// stores silu(gate) * up (computed on the fp32 accumulators): the 2F-wide
+// intermediate never exists in memory. p.N is F here.
+template <bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmParams p) {
+  constexpr int BNO = SWIGLU ? BN2 / 2 : BN2;   // output columns per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStage2);
@@ -413,7 +421,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();     // 0: issues the MMAs
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int tiles_m = (p.M + BM2 - 1) / BM2, tiles_n = (p.N + BN2 - 1) / BN2;
+  const int tiles_m = (p.M + BM2 - 1) / BM2, tiles_n = (p.N + BNO - 1) / BNO;
   const int n_tiles = tiles_m * tiles_n * p.batch;
   const int n_k = (p.K + BK - 1) / BK;
 
@@ -452,7 +460,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         int b, tm, tn;
         tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
         const int row0 = tm * BM2 + static_cast<int>(rank) * BM;          // this CTA's rows of A
-        const int col0 = tn * BN2 + static_cast<int>(rank) * (BN2 / 2);   // this CTA's columns of B
+        const int col0 = SWIGLU ? tn * BNO + static_cast<int>(rank) * p.up_offset   // gate rows / up rows of B
+                                : tn * BN2 + static_cast<int>(rank) * (BN2 / 2);    // this CTA's columns of B
         for (int k = 0; k < n_k; ++k) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * kStage2;
@@ -526,6 +535,40 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint16_t* crow = p.cin ? static_cast<const uint16_t*>(p.cin) + b * p.c_sb + static_cast<int64_t>(row) * p.c_sm
                                    : nullptr;
       const bool vec_ok = (p.o_sm % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) + 2 * b * p.o_sb) % 16 == 0);
+      if (SWIGLU) {
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * BN2);
+#pragma unroll 1
+        for (int c = 0; c < BNO; c += 32) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_row + c, rg);
+          tmem_ld_32x32(t_row + BNO + c, ru);
+          tmem_wait_ld();
+          const int col0 = tn * BNO + c;
+          if (row_ok && col0 < p.N) {
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float g0 = __uint_as_float(rg[2 * j]), g1 = __uint_as_float(rg[2 * j + 1]);
+              const float v0 = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(ru[2 * j]);
+              const float v1 = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(ru[2 * j + 1]);
+              if (p.is_bf16) {
+                o[j] = f32x2_to_bf16x2_bits(v0, v1);
+              } else {
+                __half2 h = __floats2half2_rn(v0, v1);
+                o[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+            }
+            if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(orow + col0 + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                orow[col0 + j] = static_cast<uint16_t>(j & 1 ? o[j >> 1] >> 16 : o[j >> 1] & 0xffffu);
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN2; c += 32) {
         uint32_t r[32];
@@ -552,6 +595,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[ab]), 0));
@@ -568,6 +612,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
 }
 
+template <bool SWIGLU>
 b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaStream_t s) {
   CUtensorMap ta, tb;
   const char* err = "";
@@ -577,14 +622,15 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev != last_dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
-  const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + BN2 - 1) / BN2) * p.batch;
+  constexpr int bno = SWIGLU ? BN2 / 2 : BN2;
+  const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + bno - 1) / bno) * p.batch;
   const int pairs = sm_count_current_device() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tc2_kernel<<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
+  gemm_tc2_kernel<SWIGLU><<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
   return check_launch("matmul (tcgen05, two-CTA)");
 }
 
@@ -853,7 +899,7 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
       }
       p.error_word = device_error_word();
       B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
-      if (pair_kernel) return launch_tc2(oa, ob, p, s);
+      if (pair_kernel) return launch_tc2<false>(oa, ob, p, s);
       if (splits > 1) return launch_splitk(oa, ob, p, splits, s);
       if (bn == 256) return launch_tc<256>(oa, ob, p, s);
       if (bn == 128) return launch_tc<128>(oa, ob, p, s);
@@ -871,11 +917,44 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
   return simt::launch(q, a->dtype, s);
 }
 
+// out (M, F) = silu(a @ w[:F].T) * (a @ w[F:].T); a (M, K) and w (2F, K) with K contiguous.
+b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w, cudaStream_t s) {
+  const char* name = "b200_mm_swiglu";
+  B200_REQUIRE(valid(out) && valid(a) && valid(w), B200_BAD_PARAM, "%s: invalid tensor view", name);
+  B200_REQUIRE(out->ndim == 2 && a->ndim == 2 && w->ndim == 2, B200_BAD_PARAM, "%s: operands must be 2-D", name);
+  B200_REQUIRE((a->dtype == B200_BF16 || a->dtype == B200_F16) && w->dtype == a->dtype && out->dtype == a->dtype,
+               B200_NOT_SUPPORTED, "%s: bf16 or f16 operands of one dtype", name);
+  const int64_t M = a->sizes[0], K = a->sizes[1], F = out->sizes[1];
+  B200_REQUIRE(out->sizes[0] == M && w->sizes[0] == 2 * F && w->sizes[1] == K, B200_BAD_PARAM,
+               "%s: expected a (M,K), w (2F,K), out (M,F)", name);
+  if (M == 0 || F == 0) return B200_OK;
+  B200_REQUIRE(K > 0, B200_BAD_PARAM, "%s: K must be positive", name);
+  B200_REQUIRE(M < (1ll << 31) && F < (1ll << 30) && K < (1ll << 31) && (out->strides[1] == 1 || F == 1),
+               B200_NOT_SUPPORTED, "%s: sizes or output layout not supported", name);
+  Operand oa, ob;
+  const bool a_ok = describe_operand(a->data, M, K, 1, a->strides[0], a->strides[1], 0, BM, &oa) && !oa.mn_major;
+  const bool b_ok = describe_operand(w->data, 2 * F, K, 1, w->strides[0], w->strides[1], 0, BN2 / 2, &ob) && !ob.mn_major;
+  B200_REQUIRE(a_ok && b_ok, B200_NOT_SUPPORTED, "%s: operands must be K-contiguous, 16-byte aligned, leading dimension a multiple of 8", name);
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)F; p.K = (int)K; p.batch = 1;
+  p.is_bf16 = a->dtype == B200_BF16;
+  p.alpha = 1.f; p.beta = 0.f;
+  p.out = out->data; p.o_sm = out->strides[0];
+  p.up_offset = (int)F;
+  p.error_word = device_error_word();
+  B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+  return launch_tc2<true>(oa, ob, p, s);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
 extern "C" {
+
+b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up, b200Stream stream) {
+  return mm_swiglu_impl(out, a, w_gate_up, static_cast<cudaStream_t>(stream));
+}
 
 b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
   return matmul_impl(out, a, b, nullptr, 1.0, 0.0, false, static_cast<cudaStream_t>(stream), "b200_mm");

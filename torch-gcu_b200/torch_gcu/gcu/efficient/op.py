@@ -53,6 +53,12 @@ def swiglu_packed(gate_up: Tensor):
     return _C._swiglu_packed(gate_up)
 
 
+def linear_swiglu(x: Tensor, w_gate_up: Tensor):
+    """silu(x @ w[:F].T) * (x @ w[F:].T) for a fused gate/up weight (2F, K): one GEMM whose
+    epilogue applies the activation, so the (…, 2F) projection output is never materialised."""
+    return _C._linear_swiglu(x, w_gate_up)
+
+
 def sdpa_flash(q: Tensor, k: Tensor, v: Tensor, is_causal: bool, scale: Optional[float] = None):
     """Flash attention forward for q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D); returns (out, logsumexp)."""
     return _C._sdpa_flash(q, k, v, is_causal, scale)

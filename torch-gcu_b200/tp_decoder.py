@@ -106,8 +106,9 @@ class DecoderLayer:
             o = torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t())
             self._allreduce(o, group)
             h2, r = eff.rms_norm_residual(o.view(B, S, H), x, w["norm2"], self.eps)
-            gu = torch.mm(h2.view(B * S, H), w["wgu"].t())
-            act = eff.swiglu_packed(gu)
+            act = eff.linear_swiglu(h2.view(B * S, H), w["wgu"])   # gate/up GEMM with the SwiGLU in its epilogue
+            if self.tp == 1:
+                return torch.addmm(r.view(B * S, H), act, w["wd"].t()).view(B, S, H)   # residual in the epilogue
             down = torch.mm(act, w["wd"].t())
             self._allreduce(down, group)
             return torch.add(down.view(B, S, H), r)
@@ -150,8 +151,9 @@ class DecoderLayer:
         o = torch.mm(att.transpose(1, 2).reshape(B, hq * d), w["wo"].t())
         self._allreduce(o, group)
         h2, r = eff.rms_norm_residual(o.view(B, 1, H), x, w["norm2"], self.eps)
-        gu = torch.mm(h2.view(B, H), w["wgu"].t())
-        act = eff.swiglu_packed(gu)
+        act = eff.linear_swiglu(h2.view(B, H), w["wgu"])
+        if self.tp == 1:
+            return torch.addmm(r.view(B, H), act, w["wd"].t()).view(B, 1, H)
         down = torch.mm(act, w["wd"].t())
         self._allreduce(down, group)
         return torch.add(down.view(B, 1, H), r)
