@@ -133,9 +133,9 @@ def run_gpu(args):
     dev = torch.device("gcu", local)
     group = None
     if world > 1:
-        # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # keep stdout to the one JSON line: at the VERSION and WARN levels NCCL prints its banner there
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() in ("VERSION", "WARN"):
+            os.environ["NCCL_DEBUG"] = "NONE"
         dist.init_process_group("eccl", rank=rank, world_size=world)
         group = dist.group.WORLD
     bf = torch.bfloat16

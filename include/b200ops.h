@@ -81,6 +81,13 @@ const char* b200_version(void);
 int b200_device_count(void);            /* 0 when no usable GPU / driver     */
 int b200_sm_count(int device);          /* multiprocessors of `device`, or -1 */
 size_t b200_dtype_size(int32_t dtype);  /* bytes per element, 0 if unknown    */
+/* The persistent GEMM kernels fill every SM with one CTA whose shared memory
+ * leaves no room for another kernel's CTA, so a collective launched beside them
+ * on another stream would wait for the GEMM to end. Reserving n SMs makes those
+ * kernels launch on (SM count - n) SMs; process-wide, default 0. No reference
+ * counterpart (the vendor library schedules its own kernels).                  */
+void b200_set_reserved_sms(int n);
+int b200_get_reserved_sms(void);
 /* Index kernels never trap on an out-of-range index: they substitute index 0
  * (or drop the element) and set bit 0 of a device-side error word. This call
  * synchronises the device, returns the word and clears it; the host uses it in

@@ -157,6 +157,8 @@ PYBIND11_MODULE(_C, m) {
     return f;
   });
   m.def("_kernel_library_version", [] { return std::string(b200_version()); });
+  m.def("_set_reserved_sms", [](int n) { b200_set_reserved_sms(n); });
+  m.def("_get_reserved_sms", [] { return b200_get_reserved_sms(); });
 
   m.def("_c10d_gcu_init", [m]() mutable {
     static bool done = false;

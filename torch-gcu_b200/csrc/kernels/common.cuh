@@ -39,7 +39,8 @@ inline b200Status check_launch(const char* what) {
   return B200_OK;
 }
 
-int sm_count_current_device();  // cached per device (runtime.cu)
+int sm_count_current_device();
+int gemm_sm_budget();   // SM count minus the SMs reserved through b200_set_reserved_sms  // cached per device (runtime.cu)
 
 // ------------------------------------------------------------ tensor view ----
 inline int64_t numel(const b200Tensor* t) {

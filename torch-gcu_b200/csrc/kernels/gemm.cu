@@ -331,7 +331,7 @@ b200Status launch_tc(const Operand& oa, const Operand& ob, GemmParams p, cudaStr
   }
   B200_REQUIRE(attr_err == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(attr_err));
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
-  const int sms = sm_count_current_device();
+  const int sms = gemm_sm_budget();
   const int grid = tiles < sms ? tiles : sms;
   gemm_tc_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, s>>>(ta, tb, p);
   return check_launch("matmul (tcgen05)");
@@ -628,7 +628,7 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
   }
   constexpr int bno = SWIGLU ? BN2 / 2 : BN2;
   const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + bno - 1) / bno) * p.batch;
-  const int pairs = sm_count_current_device() / 2;
+  const int pairs = gemm_sm_budget() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
   gemm_tc2_kernel<SWIGLU><<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
   return check_launch("matmul (tcgen05, two-CTA)");

@@ -11,6 +11,14 @@ char* error_buffer() {
   return buf;
 }
 
+int sm_count_current_device();
+// SMs the persistent GEMM kernels leave free (for a collective running beside them).
+static std::atomic<int> g_reserved_sms{0};
+int gemm_sm_budget() {
+  const int n = sm_count_current_device() - g_reserved_sms.load(std::memory_order_relaxed);
+  return n < 2 ? 2 : n;
+}
+
 int sm_count_current_device() {
   // Immutable once written; racing writers store the same value.
   static std::atomic<int> cache[64];
@@ -32,6 +40,9 @@ extern "C" {
 const char* b200_last_error(void) { return b200::error_buffer(); }
 
 const char* b200_version(void) { return "b200ops 0.1 (sm_100a)"; }
+
+void b200_set_reserved_sms(int n) { b200::g_reserved_sms.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
+int b200_get_reserved_sms(void) { return b200::g_reserved_sms.load(std::memory_order_relaxed); }
 
 int b200_device_count(void) {
   int n = 0;

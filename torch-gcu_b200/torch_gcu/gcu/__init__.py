@@ -122,6 +122,16 @@ class device_of(device):
         super().__init__(obj.get_device() if getattr(obj, "is_gcu", False) else -1)
 
 
+def set_reserved_sms(n: int) -> None:
+    """Leave n SMs free of the persistent GEMM kernels, so that a collective launched on another
+    stream (the process group's) can run beside them instead of after them. 0 restores the default."""
+    _C._set_reserved_sms(int(n))
+
+
+def get_reserved_sms() -> int:
+    return _C._get_reserved_sms()
+
+
 def synchronize(device: _device_t = None) -> None:
     _lazy_init()
     with torch_gcu.gcu.device(device):

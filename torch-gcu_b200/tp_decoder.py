@@ -88,28 +88,43 @@ class DecoderLayer:
         return t
 
     # ------------------------------------------------------------- prefill --
+    def attn_part(self, x, kv_out=None):
+        """RMSNorm -> qkv -> RoPE -> attention -> o_proj; returns this rank's partial (B*S, hidden)."""
+        B, S, H = x.shape
+        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        cos, sin = self.tables(S)
+        h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
+        qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+        eff.rope(q, cos, sin, None, True)
+        eff.rope(k, cos, sin, None, True)
+        if kv_out is not None:
+            kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
+            kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
+        att, _ = eff.sdpa_flash(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True)
+        return torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t())
+
+    def mlp_part(self, o, x):
+        """o: the reduced attention output. Returns (down, r): this rank's partial MLP output
+        (with the residual already added when tp == 1) and the residual stream."""
+        B, S, H = x.shape
+        w, eff = self.w, self.eff
+        h2, r = eff.rms_norm_residual(o.view(B, S, H), x, w["norm2"], self.eps)
+        act = eff.linear_swiglu(h2.view(B * S, H), w["wgu"])   # gate/up GEMM with the SwiGLU in its epilogue
+        if self.tp == 1:
+            return torch.addmm(r.view(B * S, H), act, w["wd"].t()).view(B, S, H), r   # residual in the epilogue
+        return torch.mm(act, w["wd"].t()), r
+
     def forward_prefill(self, x, group=None, kv_out=None):
         B, S, H = x.shape
         hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
         cos, sin = self.tables(S)
         if self.backend == "gcu":
-            eff = self.eff
-            h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
-            qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
-            q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
-            eff.rope(q, cos, sin, None, True)
-            eff.rope(k, cos, sin, None, True)
-            if kv_out is not None:
-                kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
-                kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
-            att, _ = eff.sdpa_flash(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True)
-            o = torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t())
+            o = self.attn_part(x, kv_out)
             self._allreduce(o, group)
-            h2, r = eff.rms_norm_residual(o.view(B, S, H), x, w["norm2"], self.eps)
-            act = eff.linear_swiglu(h2.view(B * S, H), w["wgu"])   # gate/up GEMM with the SwiGLU in its epilogue
+            down, r = self.mlp_part(o, x)
             if self.tp == 1:
-                return torch.addmm(r.view(B * S, H), act, w["wd"].t()).view(B, S, H)   # residual in the epilogue
-            down = torch.mm(act, w["wd"].t())
+                return down
             self._allreduce(down, group)
             return torch.add(down.view(B, S, H), r)
         # plain torch (fp32 math on whatever dtype the weights have)
@@ -175,10 +190,58 @@ class DecoderStack:
                                     backend, device=device, **cfg) for i in range(n_layers)]
         self.cfg, self.tp = cfg, tp
 
-    def prefill(self, x, group=None, caches=None):
+    def prefill(self, x, group=None, caches=None, overlap=None):
+        if overlap is None:
+            # measured on B200: at tp 2 the all-reduce is a small share and the plain schedule wins
+            # (561 k vs 549 k tokens/s); at tp 8 the two-microbatch schedule gives 1.40 M vs 1.14 M
+            import os
+            overlap = os.environ.get("TP_DECODER_OVERLAP", "1" if self.tp >= 4 else "0") != "0"
+        if self.tp > 1 and overlap and self.layers[0].backend == "gcu" and x.shape[0] % 2 == 0:
+            return self._prefill_two_microbatches(x, group, caches)
         for i, layer in enumerate(self.layers):
             x = layer.forward_prefill(x, group, None if caches is None else caches[i])
         return x
+
+    def _prefill_two_microbatches(self, x, group, caches):
+        """The batch is cut in two halves that walk the layers one phase apart, so that the
+        all-reduce of one half (on the process group's own stream) runs under the other half's
+        GEMMs and attention. Same arithmetic per row as the unsplit pass."""
+        import os
+        import torch.distributed as dist
+        # the collective's CTAs need SMs of their own next to the persistent GEMM kernels
+        reserve = int(os.environ.get("TP_DECODER_COMM_SMS", "32"))
+        before = torch.gcu.get_reserved_sms()
+        torch.gcu.set_reserved_sms(reserve)
+        try:
+            return self._two_microbatches(x, group, caches)
+        finally:
+            torch.gcu.set_reserved_sms(before)
+
+    def _two_microbatches(self, x, group, caches):
+        import torch.distributed as dist
+        half = x.shape[0] // 2
+        xs = [x[:half], x[half:]]
+        B, S, H = xs[0].shape
+        pending = [None, None]   # all-reduce of the previous layer's MLP output, per half
+        carry = [None, None]     # (down, r) that the pending all-reduce completes
+        for i, layer in enumerate(self.layers):
+            o, wo = [None, None], [None, None]
+            for m in (0, 1):
+                if pending[m] is not None:
+                    pending[m].wait()
+                    xs[m] = torch.add(carry[m][0].view(B, S, H), carry[m][1])
+                kv = None if caches is None else tuple(c[m * half:(m + 1) * half] for c in caches[i])
+                o[m] = layer.attn_part(xs[m], kv)
+                wo[m] = dist.all_reduce(o[m], group=group, async_op=True)
+            for m in (0, 1):
+                wo[m].wait()
+                carry[m] = layer.mlp_part(o[m], xs[m])
+                pending[m] = dist.all_reduce(carry[m][0], group=group, async_op=True)
+        out = []
+        for m in (0, 1):
+            pending[m].wait()
+            out.append(torch.add(carry[m][0].view(B, S, H), carry[m][1]))
+        return torch.cat(out, 0)
 
     def decode(self, x, caches, pos, group=None):
         for layer, kv in zip(self.layers, caches):
