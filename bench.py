@@ -171,13 +171,53 @@ def run_gpu(args):
     with ClockSampler(local) as clocks:
         prefill_ms = timed(lambda: stack.prefill(x, group), steps)
 
+    # ---- end to end: host buffers in, host buffer out, every step -------------------
+    # The step's input goes up from pinned memory on a copy stream while the previous step
+    # computes, and its result comes down on a second copy stream while the next step
+    # computes: what a serving loop built on torch.gcu streams and events does. All K
+    # uploads and K downloads lie inside the timed region.
     out_host = torch.empty_like(x_host).pin_memory()
+    s_in, s_out = torch.gcu.Stream(), torch.gcu.Stream()
+    x_dev = [torch.empty_like(x), torch.empty_like(x)]
+    uploaded = [None, None]   # event: x_dev[i] holds the step's input
+    consumed = [None, None]   # event: the pass reading x_dev[i] has been enqueued and finished
 
-    def e2e_step():
-        xd = x_host.to(dev, non_blocking=True)
-        out_host.copy_(stack.prefill(xd, group), non_blocking=True)
-    e2e_step()
-    e2e_ms = timed(e2e_step, steps)
+    def upload(slot):
+        with torch.gcu.stream(s_in):
+            if consumed[slot] is not None:
+                s_in.wait_event(consumed[slot])
+            x_dev[slot].copy_(x_host, non_blocking=True)
+            uploaded[slot] = s_in.record_event()
+
+    def e2e_loop(n):
+        cur = torch.gcu.current_stream()
+        upload(0)
+        for i in range(n):
+            slot = i & 1
+            if i + 1 < n:
+                upload(slot ^ 1)
+            cur.wait_event(uploaded[slot])
+            y = stack.prefill(x_dev[slot], group)
+            consumed[slot] = cur.record_event()
+            y.record_stream(s_out)
+            with torch.gcu.stream(s_out):
+                s_out.wait_event(consumed[slot])
+                out_host.copy_(y, non_blocking=True)
+        cur.wait_stream(s_out)
+
+    e2e_loop(2)
+    barrier()
+    s_ev, e_ev = torch.gcu.Event(enable_timing=True), torch.gcu.Event(enable_timing=True)
+    s_ev.record()
+    e2e_loop(steps)
+    e_ev.record()
+    barrier()
+    t = torch.tensor([s_ev.elapsed_time(e_ev) / steps], dtype=torch.float32)
+    if world > 1:
+        td = t.to(dev)
+        dist.all_reduce(td, op=dist.ReduceOp.MAX)
+        t = td.cpu()
+    e2e_ms = t.item()
 
     # ---- decode ------------------------------------------------------------------
     hk = CFG["kv_heads"] // world
