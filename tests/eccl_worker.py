@@ -45,6 +45,43 @@ inp = torch.arange(world * 4, dtype=torch.float32).to(dev)
 rs = torch.empty(4).to(dev)
 dist.reduce_scatter_tensor(rs, inp)
 assert torch.equal(rs.cpu(), world * torch.arange(rank * 4, rank * 4 + 4, dtype=torch.float32))
+# reduce_scatter, list form
+ins = [torch.full((6,), float(rank + 1 + r)).to(dev) for r in range(world)]
+rl = torch.empty(6).to(dev)
+dist.reduce_scatter(rl, ins)
+assert torch.equal(rl.cpu(), torch.full((6,), float(sum(k + 1 + rank for k in range(world)))))
+# reduce to a root
+rd = torch.full((7,), float(rank + 1)).to(dev)
+dist.reduce(rd, dst=world - 1)
+if rank == world - 1:
+    assert torch.equal(rd.cpu(), torch.full((7,), float(sum(range(1, world + 1)))))
+# all_to_all_single, equal splits: row block r of rank k goes to rank r
+a2a_in = (torch.arange(world * 2, dtype=torch.float32).view(world, 2) + 100 * rank).reshape(-1).to(dev)
+a2a_out = torch.empty(world * 2).to(dev)
+dist.all_to_all_single(a2a_out, a2a_in)
+exp = torch.cat([torch.arange(rank * 2, rank * 2 + 2, dtype=torch.float32) + 100 * k for k in range(world)])
+assert torch.equal(a2a_out.cpu(), exp)
+# send / recv around a ring
+if world > 1:
+    msg = torch.full((9,), float(rank)).to(dev)
+    got = torch.empty(9).to(dev)
+    if rank % 2 == 0:
+        dist.send(msg, (rank + 1) % world)
+        dist.recv(got, (rank - 1) % world)
+    else:
+        dist.recv(got, (rank - 1) % world)
+        dist.send(msg, (rank + 1) % world)
+    assert torch.equal(got.cpu(), torch.full((9,), float((rank - 1) % world)))
+# coalescing: two all-reduces issued as one group
+backend = dist.group.WORLD._get_backend(dev)
+c1, c2 = torch.full((5,), 1.0).to(dev), torch.full((3,), float(rank)).to(dev)
+backend._group_start()
+w1 = dist.all_reduce(c1, async_op=True)
+w2 = dist.all_reduce(c2, async_op=True)
+backend._group_end()
+w1.wait()
+w2.wait()
+assert torch.equal(c1.cpu(), torch.full((5,), float(world))) and torch.equal(c2.cpu(), torch.full((3,), float(sum(range(world)))))
 # out-of-place all-reduce extra of the backend
 import torch_gcu.distributed as gd  # noqa: E402
 o = torch.empty(5).to(dev)

@@ -273,10 +273,17 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::collective(std::vector<at::Tens
   GCU_CUDA_CHECK(cudaEventRecord(c.handoff, compute));
   GCU_CUDA_CHECK(cudaStreamWaitEvent(c.stream, c.handoff, 0));
   fn(c.comm, c.stream);
-  GCU_CUDA_CHECK(cudaEventRecord(work->end_event_, c.stream));
   work->outputs_ = outputs;
   work->stashed_ = std::move(inputs);
   work->stashed_.insert(work->stashed_.end(), outputs.begin(), outputs.end());
+  if (coalescing_depth_ > 0) {
+    // inside an open group nothing has been launched yet: the end event is recorded, and the
+    // work handed to the watchdog, when the group closes
+    coalesced_.emplace_back(work, c.stream);
+    last_coalesced_ = work;
+    return work;
+  }
+  GCU_CUDA_CHECK(cudaEventRecord(work->end_event_, c.stream));
   enqueue(work);
   return work;
 }
@@ -356,6 +363,100 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::_reduce_scatter_base(at::Tensor
     ECCL_CHECK(ncclReduceScatter(in.data_ptr(), out.data_ptr(), static_cast<size_t>(out.numel()), to_nccl_dtype(in.scalar_type()),
                                  to_nccl_op(opts.reduceOp, in.scalar_type()), comm, s));
   }, c10d::OpType::_REDUCE_SCATTER_BASE);
+}
+
+// List form: the inputs of all ranks are packed into one buffer first
+// (reference: ProcessGroupECCL.cpp:3168-3330).
+c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::reduce_scatter(std::vector<at::Tensor>& outputs,
+                                                               std::vector<std::vector<at::Tensor>>& inputs,
+                                                               const c10d::ReduceScatterOptions& opts) {
+  TORCH_CHECK(outputs.size() == 1 && inputs.size() == 1, "eccl reduce_scatter: expecting one output tensor and one input list");
+  TORCH_CHECK(static_cast<int>(inputs[0].size()) == size_, "eccl reduce_scatter: the input list must have world_size entries");
+  at::Tensor out = outputs[0];
+  check_tensor(out, "reduce_scatter");
+  for (const auto& t : inputs[0]) {
+    check_tensor(t, "reduce_scatter");
+    TORCH_CHECK(t.numel() == out.numel() && t.scalar_type() == out.scalar_type(), "eccl reduce_scatter: every input must match the output");
+  }
+  at::Tensor flat = at::empty({size_, out.numel()}, out.options());
+  for (int r = 0; r < size_; ++r) flat[r].copy_(inputs[0][r].reshape({-1}));
+  return _reduce_scatter_base(out, flat, opts);
+}
+
+c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::reduce(std::vector<at::Tensor>& tensors, const c10d::ReduceOptions& opts) {
+  TORCH_CHECK(tensors.size() == 1, "eccl reduce: expecting one tensor");
+  at::Tensor t = tensors[0];
+  check_tensor(t, "reduce");
+  const int root = static_cast<int>(opts.rootRank);
+  TORCH_CHECK(root >= 0 && root < size_, "eccl reduce: invalid root rank ", root);
+  return collective({t}, {t}, [&](ncclComm_t comm, cudaStream_t s) {
+    ECCL_CHECK(ncclReduce(t.data_ptr(), t.data_ptr(), static_cast<size_t>(t.numel()), to_nccl_dtype(t.scalar_type()),
+                          to_nccl_op(opts.reduceOp, t.scalar_type()), root, comm, s));
+  }, c10d::OpType::REDUCE);
+}
+
+// Equal or explicit splits along dim 0, as grouped sends and receives.
+c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::alltoall_base(at::Tensor& output, at::Tensor& input,
+                                                              std::vector<int64_t>& outputSplitSizes,
+                                                              std::vector<int64_t>& inputSplitSizes, const c10d::AllToAllOptions&) {
+  check_tensor(input, "alltoall_base");
+  check_tensor(output, "alltoall_base");
+  TORCH_CHECK(input.scalar_type() == output.scalar_type(), "eccl alltoall_base: input and output must have the same type");
+  auto splits = [&](const at::Tensor& t, const std::vector<int64_t>& given, const char* what) {
+    std::vector<int64_t> v = given;
+    if (v.empty()) {
+      TORCH_CHECK(t.dim() >= 1 && t.size(0) % size_ == 0, "eccl alltoall_base: ", what, " dim 0 must divide by world_size");
+      v.assign(size_, t.size(0) / size_);
+    }
+    TORCH_CHECK(static_cast<int>(v.size()) == size_, "eccl alltoall_base: ", what, " split list must have world_size entries");
+    int64_t total = 0;
+    for (int64_t x : v) { TORCH_CHECK(x >= 0, "eccl alltoall_base: negative split"); total += x; }
+    TORCH_CHECK(total == (t.dim() ? t.size(0) : 0), "eccl alltoall_base: ", what, " splits do not sum to dim 0");
+    return v;
+  };
+  const std::vector<int64_t> in_s = splits(input, inputSplitSizes, "input"), out_s = splits(output, outputSplitSizes, "output");
+  at::Tensor in = input, out = output;
+  const int64_t in_row = in.size(0) ? in.nbytes() / in.size(0) : 0, out_row = out.size(0) ? out.nbytes() / out.size(0) : 0;
+  return collective({in}, {out}, [&](ncclComm_t comm, cudaStream_t s) {
+    ECCL_CHECK(ncclGroupStart());
+    int64_t io = 0, oo = 0;
+    for (int r = 0; r < size_; ++r) {
+      if (in_s[r]) ECCL_CHECK(ncclSend(static_cast<const char*>(in.data_ptr()) + io * in_row, in_s[r] * in_row, ncclUint8, r, comm, s));
+      if (out_s[r]) ECCL_CHECK(ncclRecv(static_cast<char*>(out.data_ptr()) + oo * out_row, out_s[r] * out_row, ncclUint8, r, comm, s));
+      io += in_s[r];
+      oo += out_s[r];
+    }
+    ECCL_CHECK(ncclGroupEnd());
+  }, c10d::OpType::ALLTOALL_BASE);
+}
+
+void ProcessGroupECCL::group_start() {
+  ECCL_CHECK(ncclGroupStart());
+  ++coalescing_depth_;
+}
+void ProcessGroupECCL::group_end() {
+  TORCH_CHECK(coalescing_depth_ > 0, "eccl: _group_end without a matching _group_start");
+  --coalescing_depth_;
+  ECCL_CHECK(ncclGroupEnd());
+  if (coalescing_depth_ == 0) {
+    for (auto& [work, stream] : coalesced_) {
+      c10::OptionalDeviceGuard dg(work->device_);
+      GCU_CUDA_CHECK(cudaEventRecord(work->end_event_, stream));
+      enqueue(work);
+    }
+    coalesced_.clear();
+  }
+}
+void ProcessGroupECCL::startCoalescing() {
+  last_coalesced_.reset();
+  group_start();
+}
+c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::endCoalescing() {
+  group_end();
+  // every collective of the group completes with the group: the last one's work stands for all
+  auto w = last_coalesced_;
+  last_coalesced_.reset();
+  return w;
 }
 
 // A 1-element allreduce on the group's device, waited for on the host

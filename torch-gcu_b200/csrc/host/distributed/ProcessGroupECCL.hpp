@@ -97,6 +97,19 @@ class ProcessGroupECCL : public c10d::Backend {
                                            const c10d::AllgatherOptions& opts = c10d::AllgatherOptions()) override;
   c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& output, at::Tensor& input,
                                                       const c10d::ReduceScatterOptions& opts = c10d::ReduceScatterOptions()) override;
+  c10::intrusive_ptr<c10d::Work> reduce_scatter(std::vector<at::Tensor>& outputs, std::vector<std::vector<at::Tensor>>& inputs,
+                                                const c10d::ReduceScatterOptions& opts = c10d::ReduceScatterOptions()) override;
+  c10::intrusive_ptr<c10d::Work> reduce(std::vector<at::Tensor>& tensors,
+                                        const c10d::ReduceOptions& opts = c10d::ReduceOptions()) override;
+  c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& output, at::Tensor& input, std::vector<int64_t>& outputSplitSizes,
+                                               std::vector<int64_t>& inputSplitSizes,
+                                               const c10d::AllToAllOptions& opts = c10d::AllToAllOptions()) override;
+  // Coalescing: the collectives issued between the two calls go out as one NCCL group
+  // (reference: ProcessGroupECCL.cpp:3976-4048, Python _group_start / _group_end).
+  void startCoalescing() override;
+  c10::intrusive_ptr<c10d::Work> endCoalescing() override;
+  void group_start();
+  void group_end();
   c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts = c10d::BarrierOptions()) override;
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>& tensors, int dstRank, int tag) override;
   c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>& tensors, int srcRank, int tag) override;
@@ -137,6 +150,9 @@ class ProcessGroupECCL : public c10d::Backend {
   std::mutex mutex_;
   std::unordered_map<int, Comm> comms_;  // by device index
   uint64_t seq_ = 0;
+  int coalescing_depth_ = 0;
+  c10::intrusive_ptr<c10d::Work> last_coalesced_;
+  std::vector<std::pair<c10::intrusive_ptr<WorkECCL>, cudaStream_t>> coalesced_;
   uint64_t comm_counter_ = 0;
   bool blocking_wait_ = false;
   c10::Device last_device_ = c10::Device(c10::DeviceType::PrivateUse1, 0);

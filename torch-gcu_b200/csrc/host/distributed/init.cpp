@@ -39,6 +39,8 @@ void init_distributed_bindings(py::module& root) {
       .def("abort", &PG::abort, py::call_guard<py::gil_scoped_release>())
       .def("shutdown", &PG::shutdown, py::call_guard<py::gil_scoped_release>())
       .def_static("_check_tensor", [](const at::Tensor& t) { PG::check_tensor(t, "check"); })
+      .def("_group_start", &PG::group_start, py::call_guard<py::gil_scoped_release>())
+      .def("_group_end", &PG::group_end, py::call_guard<py::gil_scoped_release>())
       .def_property_readonly("options", &PG::getOptions);
 }
 
