@@ -238,3 +238,60 @@ def test_unsupported_operator_raises(dev):
     a = torch.randn(4, 4).to(dev)
     with pytest.raises(NotImplementedError, match="no CPU fallback"):
         torch.linalg.inv(a)
+
+
+def test_graph_capture_and_replay(dev):
+    """A sequence of operators recorded once and replayed: results follow the static input,
+    memory created during the capture stays private to the graph."""
+    g = torch.Generator().manual_seed(7)
+    bf = torch.bfloat16
+    w = (torch.randn(256, 128, generator=g) * 0.1).to(bf)
+    x1, x2 = torch.randn(64, 128, generator=g).to(bf), torch.randn(64, 128, generator=g).to(bf)
+    wd, static_in = w.to(dev), x1.to(dev)
+
+    def step(x):
+        h = torch.mm(x, wd.t())
+        h = torch.nn.functional.silu(h) + 1.0
+        return torch.softmax(h.float(), -1)
+
+    eager1 = step(static_in).cpu()          # also warms up every kernel once
+    graph = torch.gcu.GCUGraph()
+    with torch.gcu.graph(graph):
+        static_out = step(static_in)
+    assert graph.captured and graph.num_nodes >= 4
+    graph.replay()
+    torch.gcu.synchronize()
+    assert torch.equal(static_out.cpu(), eager1)
+    static_in.copy_(x2.to(dev))
+    graph.replay()
+    torch.gcu.synchronize()
+    assert torch.equal(static_out.cpu(), step(x2.to(dev)).cpu())
+    # eager allocations made after the capture never alias the graph's buffers
+    junk = [torch.full((64, 256), 7.0, device=dev) for _ in range(8)]
+    graph.replay()
+    torch.gcu.synchronize()
+    assert torch.equal(static_out.cpu(), step(x2.to(dev)).cpu())
+    assert all(j.cpu().eq(7.0).all() for j in junk)
+    graph.reset()
+    assert not graph.captured
+
+
+def test_graph_decode_step_matches_eager(dev):
+    """One decode step of the decoder harness, captured and replayed."""
+    import workloads
+    from tp_decoder import DecoderStack
+    cfg = dict(hidden=512, heads=8, kv_heads=2, head_dim=128, ffn=1024)
+    stack = DecoderStack(2, 1, 0, "gcu", dev, torch.bfloat16, cfg)
+    g = torch.Generator().manual_seed(8)
+    B, T = 4, 300
+    caches = [(torch.randn(B, 2, T, 128, generator=g).bfloat16().to(dev), torch.randn(B, 2, T, 128, generator=g).bfloat16().to(dev))
+              for _ in range(2)]
+    x = torch.randn(B, 1, 512, generator=g).bfloat16().to(dev)
+    ref = stack.decode(x, caches, T - 1).cpu()
+    graph = torch.gcu.GCUGraph()
+    with torch.gcu.graph(graph):
+        out = stack.decode(x, caches, T - 1)
+    for _ in range(3):
+        graph.replay()
+    torch.gcu.synchronize()
+    assert torch.equal(out.cpu(), ref)

@@ -55,6 +55,10 @@ def test_caching_allocator_policy(torch_gcu):
     assert r["cached_block_back"] and r["deferred_not_reused"] and r["deferred_reused_after_event"]
     assert r["oom_retry_succeeded"] and r["num_alloc_retries"] >= 1
     assert r["oom_raises"] and r["num_ooms"] == 1
+    assert r["capture_ignores_general_cache"] and r["capture_reuses_own_block"]
+    assert r["eager_does_not_get_pool_block"] and r["eager_gets_general_block"]
+    assert r["plain_allocs_in_capture"] == 2 and r["plain_frees_after_release"] == 1
+    assert r["plain_frees_after_output_died"] == 2
     assert r["allocated_after_all_freed"] == 0 and r["reserved_after_empty_cache"] == 0
     assert r["backend_outstanding"] == 0 and r["cache_hits"] >= 3
 

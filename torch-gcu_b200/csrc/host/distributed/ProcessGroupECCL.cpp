@@ -71,6 +71,7 @@ ProcessGroupECCL::WorkECCL::~WorkECCL() {
 }
 
 bool ProcessGroupECCL::WorkECCL::isCompleted() {
+  if (captured_) return true;
   {
     std::lock_guard<std::mutex> g(mutex_);
     if (exception_) return true;
@@ -284,6 +285,14 @@ c10::intrusive_ptr<c10d::Work> ProcessGroupECCL::collective(std::vector<at::Tens
     return work;
   }
   GCU_CUDA_CHECK(cudaEventRecord(work->end_event_, c.stream));
+  // A collective recorded into a graph has no completion of its own to watch: its event belongs
+  // to the capture and may not be queried; only the stream hand-off in wait() applies.
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(compute, &cap) != cudaSuccess) (void)cudaGetLastError();
+  if (cap == cudaStreamCaptureStatusActive) {
+    work->captured_ = true;
+    return work;
+  }
   enqueue(work);
   return work;
 }

@@ -65,6 +65,7 @@ class ProcessGroupECCL : public c10d::Backend {
     void synchronizeStream();
     uint64_t seq_;
     c10::Device device_;
+    bool captured_ = false;   // issued while the compute stream was capturing a graph
     cudaEvent_t end_event_ = nullptr;
     std::chrono::milliseconds timeout_;
     std::chrono::steady_clock::time_point start_;

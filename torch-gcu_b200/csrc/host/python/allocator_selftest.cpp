@@ -51,6 +51,21 @@ class FakeBackend final : public MemoryBackend {
     ++syncs;
     for (FakeEvent* e : events) e->done = true;
   }
+  int plain_allocs = 0, plain_frees = 0;
+  void* alloc_plain(int, size_t bytes) override {
+    if (used + bytes > capacity) return nullptr;
+    void* p = std::malloc(bytes);
+    sizes[p] = bytes;
+    used += bytes;
+    ++plain_allocs;
+    return p;
+  }
+  void free_plain(int, void* ptr) override {
+    used -= sizes[ptr];
+    sizes.erase(ptr);
+    std::free(ptr);
+    ++plain_frees;
+  }
 };
 
 }  // namespace
@@ -112,6 +127,30 @@ py::dict allocator_selftest() {
   }
   r["oom_raises"] = threw;
   r["num_ooms"] = a.stats(0).num_ooms;
+
+  // 4b. graph-capture pool: private blocks, reused inside the pool only, returned with the pool
+  {
+    void* eager = a.malloc(0, 2000, s1);
+    a.free(eager);                                   // sits in the general cache of s1
+    const uint64_t pool = a.begin_capture(0, s1);
+    void* c1 = a.malloc(0, 2000, s1);
+    r["capture_ignores_general_cache"] = (c1 != eager);
+    a.free(c1);
+    void* c2 = a.malloc(0, 2000, s1);                // later in the same capture: same block again
+    r["capture_reuses_own_block"] = (c2 == c1);
+    void* out = a.malloc(0, 4000, s1);               // stays alive past the capture (a graph output)
+    a.free(c2);
+    a.end_capture(0, s1);
+    void* after = a.malloc(0, 2000, s1);             // eager code never gets the pool's block
+    r["eager_does_not_get_pool_block"] = (after != c1);
+    r["eager_gets_general_block"] = (after == eager);
+    a.free(after);
+    r["plain_allocs_in_capture"] = fb->plain_allocs;  // 2
+    a.release_pool(pool);
+    r["plain_frees_after_release"] = fb->plain_frees; // 1: the cached block; `out` is still alive
+    a.free(out);
+    r["plain_frees_after_output_died"] = fb->plain_frees;  // 2
+  }
 
   // 5. stats and empty_cache
   a.empty_cache();

@@ -11,6 +11,7 @@
 #include "aten/aot_ops.h"
 #include "aten/bridge.h"
 #include "runtime/gcu_allocator.h"
+#include "runtime/gcu_graph.h"
 #include "runtime/gcu_runtime.h"
 
 namespace torch_gcu {
@@ -157,6 +158,15 @@ PYBIND11_MODULE(_C, m) {
     return f;
   });
   m.def("_kernel_library_version", [] { return std::string(b200_version()); });
+  py::class_<GCUGraph>(m, "_GCUGraph")
+      .def(py::init<>())
+      .def("capture_begin", &GCUGraph::capture_begin)
+      .def("capture_end", &GCUGraph::capture_end)
+      .def("replay", &GCUGraph::replay, py::call_guard<py::gil_scoped_release>())
+      .def("reset", &GCUGraph::reset)
+      .def("captured", &GCUGraph::captured)
+      .def("num_nodes", &GCUGraph::num_nodes);
+  m.def("_gcu_isCurrentStreamCapturing", &current_stream_is_capturing);
   m.def("_set_reserved_sms", [](int n) { b200_set_reserved_sms(n); });
   m.def("_get_reserved_sms", [] { return b200_get_reserved_sms(); });
 

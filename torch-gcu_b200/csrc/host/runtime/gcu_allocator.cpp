@@ -52,6 +52,25 @@ class CudaBackend final : public MemoryBackend {
     DeviceSwitch sw(device);
     (void)cudaDeviceSynchronize();
   }
+  void* alloc_plain(int device, size_t bytes) override {
+    DeviceSwitch sw(device);
+    // cudaMalloc is refused on a capturing thread unless the thread's capture mode is relaxed
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    (void)cudaThreadExchangeStreamCaptureMode(&mode);
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    (void)cudaThreadExchangeStreamCaptureMode(&mode);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      if (e == cudaErrorMemoryAllocation) return nullptr;
+      TORCH_CHECK(false, "cudaMalloc failed: ", cudaGetErrorString(e));
+    }
+    return p;
+  }
+  void free_plain(int device, void* ptr) override {
+    DeviceSwitch sw(device);
+    if (cudaFree(ptr) != cudaSuccess) (void)cudaGetLastError();
+  }
 
  private:
   struct DeviceSwitch {
@@ -131,10 +150,36 @@ void* StreamOrderedCachingAllocator::malloc(int device, size_t bytes, cudaStream
   if (bytes == 0) return nullptr;
   const size_t size = round_size(bytes);
   std::lock_guard<std::mutex> g(mutex_);
-  process_pending_locked();
+  if (capturing_.empty()) process_pending_locked();   // event queries are not legal while a capture is open
   PerDevice& d = dev(device);
   d.stats.num_allocs++;
   Block* block = nullptr;
+  auto cap = capturing_.find({device, stream});
+  if (cap != capturing_.end()) {
+    Pool& pool = pools_[cap->second];
+    auto pit = pool.cache.lower_bound(size);
+    if (pit != pool.cache.end() && pit->first <= size + size / 4) {
+      block = pit->second;
+      pool.cache.erase(pit);
+      d.stats.num_cache_hits++;
+    } else {
+      void* p = backend_->alloc_plain(device, size);
+      if (!p) {
+        d.stats.num_ooms++;
+        TORCH_CHECK_WITH(OutOfMemoryError, false, "GCU(B200) out of memory during graph capture: tried to allocate ", size,
+                         " bytes on device ", device);
+      }
+      d.stats.num_backend_allocs++;
+      d.stats.reserved_bytes += static_cast<int64_t>(size);
+      d.stats.reserved_bytes_peak = std::max(d.stats.reserved_bytes_peak, d.stats.reserved_bytes);
+      block = new Block{p, size, device, stream, {}, 0, cap->second};
+    }
+    pool.live++;
+    d.stats.allocated_bytes += static_cast<int64_t>(block->size);
+    d.stats.allocated_bytes_peak = std::max(d.stats.allocated_bytes_peak, d.stats.allocated_bytes);
+    live_[block->ptr] = block;
+    return block->ptr;
+  }
   auto it = d.cache.lower_bound(Key(stream, size));
   if (it != d.cache.end() && it->first.first == stream && it->first.second <= size + size / 4) {
     block = it->second;
@@ -160,7 +205,7 @@ void* StreamOrderedCachingAllocator::malloc(int device, size_t bytes, cudaStream
     d.stats.num_backend_allocs++;
     d.stats.reserved_bytes += static_cast<int64_t>(size);
     d.stats.reserved_bytes_peak = std::max(d.stats.reserved_bytes_peak, d.stats.reserved_bytes);
-    block = new Block{p, size, device, stream, {}, 0};
+    block = new Block{p, size, device, stream, {}, 0, 0};
   }
   d.stats.allocated_bytes += static_cast<int64_t>(block->size);
   d.stats.allocated_bytes_peak = std::max(d.stats.allocated_bytes_peak, d.stats.allocated_bytes);
@@ -177,6 +222,23 @@ void StreamOrderedCachingAllocator::free(void* ptr) {
   live_.erase(it);
   PerDevice& d = dev(b->device);
   d.stats.allocated_bytes -= static_cast<int64_t>(b->size);
+  if (b->pool != 0) {
+    // a capture pool's block: order inside the graph is fixed by the captured dependencies,
+    // so no events; it stays with its pool until the graph is gone
+    Pool& pool = pools_[b->pool];
+    pool.live--;
+    b->other_streams.clear();
+    if (pool.released) {
+      backend_->free_plain(b->device, b->ptr);
+      d.stats.reserved_bytes -= static_cast<int64_t>(b->size);
+      d.stats.num_backend_frees++;
+      delete b;
+      if (pool.live == 0) pools_.erase(b->pool);
+    } else {
+      pool.cache.emplace(b->size, b);
+    }
+    return;
+  }
   if (b->other_streams.empty()) {
     d.cache.emplace(Key(b->stream, b->size), b);
   } else {
@@ -198,6 +260,38 @@ void StreamOrderedCachingAllocator::record_stream(void* ptr, cudaStream_t stream
   if (stream == b->stream) return;
   if (std::find(b->other_streams.begin(), b->other_streams.end(), stream) == b->other_streams.end())
     b->other_streams.push_back(stream);
+}
+
+uint64_t StreamOrderedCachingAllocator::begin_capture(int device, cudaStream_t stream) {
+  std::lock_guard<std::mutex> g(mutex_);
+  TORCH_CHECK(capturing_.find({device, stream}) == capturing_.end(), "gcu allocator: this stream is already capturing");
+  const uint64_t id = next_pool_++;
+  pools_[id].device = device;
+  capturing_[{device, stream}] = id;
+  return id;
+}
+
+void StreamOrderedCachingAllocator::end_capture(int device, cudaStream_t stream) {
+  std::lock_guard<std::mutex> g(mutex_);
+  capturing_.erase({device, stream});
+}
+
+void StreamOrderedCachingAllocator::release_pool(uint64_t id) {
+  std::lock_guard<std::mutex> g(mutex_);
+  auto it = pools_.find(id);
+  if (it == pools_.end()) return;
+  Pool& pool = it->second;
+  PerDevice& d = dev(pool.device);
+  for (auto& kv : pool.cache) {
+    Block* b = kv.second;
+    backend_->free_plain(b->device, b->ptr);
+    d.stats.reserved_bytes -= static_cast<int64_t>(b->size);
+    d.stats.num_backend_frees++;
+    delete b;
+  }
+  pool.cache.clear();
+  pool.released = true;   // blocks still held by tensors are returned as those tensors die
+  if (pool.live == 0) pools_.erase(it);
 }
 
 void StreamOrderedCachingAllocator::empty_cache() {

@@ -10,7 +10,13 @@
 //   * a block that other streams touched (recordStream) is parked until events
 //     recorded on those streams have completed;
 //   * out of memory: cached blocks are returned to the backend and the request
-//     retried once before an OutOfMemoryError is raised.
+//     retried once before an OutOfMemoryError is raised;
+//   * while a stream captures a graph, its allocations come from a private pool
+//     (plain device allocations, legal during capture) that keeps every block it
+//     ever handed out until the graph is destroyed: blocks freed during capture
+//     are reused later in the same capture, never by eager code, so a replay
+//     never writes into memory someone else has been given
+//     (reference: gcu_caching_allocator.h:247-261 private pools for GCUGraph).
 // The device backend is an interface so the policy can be unit-tested on a
 // machine without a GPU against a fake backend.
 #pragma once
@@ -46,6 +52,9 @@ class MemoryBackend {
   virtual bool event_done(void* event) = 0;
   virtual void destroy_event(void* event) = 0;
   virtual void synchronize(int device) = 0;
+  // Plain (not stream-ordered) allocation, usable while the calling thread captures a graph.
+  virtual void* alloc_plain(int device, size_t bytes) = 0;   // nullptr when out of memory
+  virtual void free_plain(int device, void* ptr) = 0;
 };
 std::unique_ptr<MemoryBackend> make_cuda_backend();
 
@@ -57,6 +66,11 @@ class StreamOrderedCachingAllocator {
   void free(void* ptr);
   void record_stream(void* ptr, cudaStream_t stream);
   void empty_cache();
+  // Graph capture: allocations made on `stream` between begin and end come from pool `id`
+  // (returned by begin); release_pool gives the pool's memory back once no graph replays into it.
+  uint64_t begin_capture(int device, cudaStream_t stream);
+  void end_capture(int device, cudaStream_t stream);
+  void release_pool(uint64_t id);
   DeviceStats stats(int device);
   void reset_peak_stats(int device);
   static size_t round_size(size_t bytes);
@@ -69,6 +83,13 @@ class StreamOrderedCachingAllocator {
     cudaStream_t stream;
     std::vector<cudaStream_t> other_streams;
     int pending_events = 0;
+    uint64_t pool = 0;   // 0: the general allocator; otherwise the capture pool that owns the block
+  };
+  struct Pool {
+    int device;
+    std::multimap<size_t, Block*> cache;   // freed blocks, reusable inside this pool only
+    int64_t live = 0;                      // blocks handed out and not yet freed
+    bool released = false;                 // graph gone: blocks leave as they are freed
   };
   using Key = std::pair<cudaStream_t, size_t>;
   struct PerDevice {
@@ -84,6 +105,9 @@ class StreamOrderedCachingAllocator {
   std::unordered_map<void*, Block*> live_;
   std::unordered_map<int, PerDevice> devices_;
   std::deque<std::pair<void*, Block*>> pending_;  // (event, block)
+  std::map<std::pair<int, cudaStream_t>, uint64_t> capturing_;   // (device, stream) -> pool
+  std::unordered_map<uint64_t, Pool> pools_;
+  uint64_t next_pool_ = 1;
 };
 
 // The process-wide device allocator registered with c10 for PrivateUse1.

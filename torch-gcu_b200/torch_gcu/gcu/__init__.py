@@ -17,6 +17,7 @@ from .memory import (empty_cache, max_memory_allocated, max_memory_reserved, mem
 from .random import (get_rng_state, initial_seed, manual_seed, manual_seed_all, seed, seed_all,  # noqa: F401
                      set_rng_state)
 from .streams import Event, ExternalStream, Stream  # noqa: F401
+from .graphs import GCUGraph, graph, is_current_stream_capturing  # noqa: F401
 
 _device_t = Union[torch.device, str, int, None]
 _initialized = False
