@@ -230,7 +230,18 @@ def run_gpu(args):
     pos = DECODE_T - 1
     for _ in range(warmup):
         stack.decode(xd, caches, pos, group)
-    decode_ms = timed(lambda: stack.decode(xd, caches, pos, group), max(steps, 5))
+    decode_eager_ms = timed(lambda: stack.decode(xd, caches, pos, group), max(steps, 5))
+    # the same step recorded into a graph and replayed: one launch instead of ~140 (with more than
+    # one rank the all-reduces are recorded too; TP_DECODER_GRAPH=0 keeps the eager loop)
+    decode_ms, decode_graph = decode_eager_ms, False
+    if os.environ.get("TP_DECODER_GRAPH", "1") != "0":
+        graph = torch.gcu.GCUGraph()
+        with torch.gcu.graph(graph):
+            stack.decode(xd, caches, pos, group)
+        for _ in range(warmup):
+            graph.replay()
+        decode_ms, decode_graph = timed(graph.replay, max(steps, 5)), True
+        graph.reset()
     del caches
 
     result = None
@@ -255,6 +266,7 @@ def run_gpu(args):
             "prefill": {"tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1),
                         "frac_of_bf16_sustained": round(flops_rank / prefill_ms / 1e9 / tf_sust, 3)},
             "decode": {"tokens_per_s": round(DECODE_B / decode_ms * 1e3, 1), "ms_per_step": round(decode_ms, 4),
+                       "graph_replay": decode_graph, "eager_ms_per_step": round(decode_eager_ms, 4),
                        "batch": DECODE_B, "kv_tokens": DECODE_T,
                        "hbm_gbs_per_gpu": round((weights_b + kv_b) / decode_ms / 1e6, 1),
                        "frac_of_measured_hbm": round((weights_b + kv_b) / decode_ms / 1e6 / hbm_peak, 3)},
