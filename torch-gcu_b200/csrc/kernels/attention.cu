@@ -648,17 +648,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 // keys is a warp reduction plus one 128-thread named barrier per tile. A cluster
 // of `splits` CTAs shares one (batch, KV head): each walks a contiguous slice of
 // the keys and the partial (O, m, l) are merged by CTA 0 through distributed
-// shared memory. 192 threads: warp 0 TMA (3-stage K / V ring), warp 1 MMA,
-// warps 2-5 softmax and output.
+// shared memory. 192 threads: warp 0 TMA, warp 1 MMA, warps 2-5 softmax and output.
+// K and V tiles travel through one ring of three 32 KB slots (K0 V0 K1 | V1 K2 V2 | ...),
+// each slot released as soon as the MMA that reads it has finished, so a CTA needs
+// 110 KB and two of them share an SM: one streams while the other sets up or merges.
 constexpr int kDecThreads = 192;
-constexpr int kDecStages = 3;
+constexpr int kDecSlots = 3;
 constexpr int kDecD = 128;
 
 template <int N> struct DecCfg {
   static constexpr int kQBytes = N * 128 * 2;             // N rows, two 64-column slabs
   static constexpr int kKVBytes = BKV * kDecD * 2;
   static constexpr int kPBytes = N * 128 * 2;             // N rows x 128 keys, two 64-key slabs
-  static constexpr int kSmem = kQBytes + kDecStages * 2 * kKVBytes + 2 * kPBytes + 1024 + 1024;
+  static constexpr int kSmem = kQBytes + kDecSlots * kKVBytes + 2 * kPBytes + 1024 + 1024;
   static constexpr int kSCol = 0;                         // S^T buffers at 0 and N
   static constexpr int kOCol = 2 * N;
   static constexpr int kTmemCols = N == 16 ? 64 : 128;
@@ -675,7 +677,7 @@ __device__ __forceinline__ float warp_max_f32(float v) {
 }
 
 template <int N, bool BF16>
-__global__ void __launch_bounds__(kDecThreads, 1)
+__global__ void __launch_bounds__(kDecThreads, 2)
 attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p, const int splits) {
   using Cfg = DecCfg<N>;
@@ -686,18 +688,17 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   // the same offset in every CTA of the cluster, so peers can be addressed by mapping
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sKV = sQ + Cfg::kQBytes;                       // [stage][K | V]
-  uint8_t* sP = sKV + kDecStages * 2 * Cfg::kKVBytes;     // [2]
+  uint8_t* sKV = sQ + Cfg::kQBytes;                       // [slot]: tile t (K_i: t = 2i, V_i: t = 2i+1) in slot t % 3
+  uint8_t* sP = sKV + kDecSlots * Cfg::kKVBytes;          // [2]
   uint8_t* tail = sP + 2 * Cfg::kPBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;             // [3]
-  uint64_t* v_full = bars + 4;             // [3]
-  uint64_t* kv_empty = bars + 7;           // [3]
-  uint64_t* s_full = bars + 10;            // [2]
-  uint64_t* p_full = bars + 12;            // [2]
-  uint64_t* pv_done = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* slot_full = bars + 1;          // [3]
+  uint64_t* slot_empty = bars + 4;         // [3]
+  uint64_t* s_full = bars + 7;             // [2]
+  uint64_t* p_full = bars + 9;             // [2]
+  uint64_t* pv_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red = reinterpret_cast<float*>(tail + 128);      // [2][4][N] warp maxima; later [4][N] warp sums
   float* comb_ml = red + 2 * 4 * N;                       // [2][N]: m, l of this CTA
@@ -717,10 +718,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   for (int i = threadIdx.x; i < Cfg::kQBytes / 16; i += kDecThreads) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < kDecStages; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < kDecSlots; ++i) {
+      mbar_init(&slot_full[i], 1);
+      mbar_init(&slot_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
@@ -750,18 +750,15 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(2 * 128 * R));
 #pragma unroll
       for (int h = 0; h < 2; ++h) tma_load_4d(sQ + h * (N * 128), &tmap_q, q_full, h * 64, 0, hq0, b);
-      for (int i = 0; i < n_my; ++i) {
-        const int st = i % kDecStages, use = i / kDecStages;
-        if (!mbar_wait(&kv_empty[st], (use & 1u) ^ 1u, abort_flag)) break;
-        uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
-        uint8_t* sV = sK + Cfg::kKVBytes;
-        const int key0 = (t_begin + i) * BKV;
-        mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
+      for (int t = 0; t < 2 * n_my; ++t) {
+        const int slot = t % kDecSlots, use = t / kDecSlots;
+        if (!mbar_wait(&slot_empty[slot], (use & 1u) ^ 1u, abort_flag)) break;
+        uint8_t* dst = sKV + slot * Cfg::kKVBytes;
+        const int key0 = (t_begin + (t >> 1)) * BKV;
+        const CUtensorMap* tm = (t & 1) ? &tmap_v : &tmap_k;
+        mbar_arrive_expect_tx(&slot_full[slot], Cfg::kKVBytes);
 #pragma unroll
-        for (int h = 0; h < 2; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, key0, hkv, b);
-        mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, key0, hkv, b);
+        for (int h = 0; h < 2; ++h) tma_load_4d(dst + h * (BKV * 128), tm, &slot_full[slot], h * 64, key0, hkv, b);
       }
     }
   } else if (warp == 1) {
@@ -772,11 +769,11 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
       const uint32_t q_addr = smem_u32(sQ);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       auto issue_pv = [&](int i) -> bool {
-        const int st = i % kDecStages, use = i / kDecStages, buf = i & 1;
+        const int t = 2 * i + 1, slot = t % kDecSlots, use = t / kDecSlots, buf = i & 1;
         if (!mbar_wait(&p_full[buf], (i >> 1) & 1u, abort_flag)) return false;
-        if (!mbar_wait(&v_full[st], use & 1u, abort_flag)) return false;
+        if (!mbar_wait(&slot_full[slot], use & 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
+        const uint32_t v_addr = smem_u32(sKV + slot * Cfg::kKVBytes);
         const uint32_t p_addr = smem_u32(sP + buf * Cfg::kPBytes);
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
@@ -786,16 +783,16 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           const uint64_t db = smem_desc_sw128(p_addr + (kk / 4) * (N * 128) + (kk % 4) * 32, 16u, 1024u);
           umma_f16(tmem_base + Cfg::kOCol, da, db, idesc_o, (i | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(&kv_empty[st]);
+        umma_commit(&slot_empty[slot]);
         umma_commit(pv_done);
         return true;
       };
       for (int i = 0; i < n_my && ok; ++i) {
-        const int st = i % kDecStages, use = i / kDecStages, buf = i & 1;
-        if (!mbar_wait(&k_full[st], use & 1u, abort_flag)) { ok = false; break; }
+        const int t = 2 * i, slot = t % kDecSlots, use = t / kDecSlots, buf = i & 1;
+        if (!mbar_wait(&slot_full[slot], use & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
         // S^T buffer `buf` was read by the softmax of tile i-2, whose P this thread has already waited for
-        const uint32_t k_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes);
+        const uint32_t k_addr = smem_u32(sKV + slot * Cfg::kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t koff = (kk / 4) * (BKV * 128) + (kk % 4) * 32;
@@ -803,6 +800,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
           umma_f16(tmem_base + Cfg::kSCol + buf * N, smem_desc_sw128(k_addr + koff, 16u, 1024u),
                    smem_desc_sw128(q_addr + qoff, 16u, 1024u), idesc_s, kk != 0 ? 1u : 0u);
         }
+        umma_commit(&slot_empty[slot]);   // K_i is free once S^T_i has been computed
         umma_commit(&s_full[buf]);
         if (i > 0) ok = issue_pv(i - 1);
       }
@@ -1012,7 +1010,7 @@ b200Status launch_decode(const b200Tensor* q, const b200Tensor* k, const b200Ten
   const int n_tiles = (p.Sk + BKV - 1) / BKV;
   const int ctas = p.B * p.Hkv;
   int splits = 1;
-  while (splits < 8 && ctas * splits < 4 * 148 && n_tiles >= splits * 4) splits *= 2;
+  while (splits < 8 && ctas * splits < 4 * 148 && n_tiles >= splits * 2 * 8) splits *= 2;   // >= 8 tiles per CTA
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, p.Hkv, p.B);
   cfg.blockDim = dim3(kDecThreads);
