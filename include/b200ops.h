@@ -278,6 +278,49 @@ b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200
 b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up,
                           b200Stream stream);
 
+/* ---- comparison, selection, clamping, extremes, generators ------------------
+ * The operators model code needs around the hot path (masks, sampling, position
+ * ids); they take the place of the vendor calls behind the reference's generated
+ * aotops::eq_out … ge_out, where, masked_fill_, maximum_out, clamp_out, argmax_out,
+ * max.dim, arange_out, triu_out / tril_out (rows of codegen/gcu_native_functions.yaml).
+ * Semantics are CPU ATen's: comparisons with NaN are false (NE true); maximum,
+ * minimum and clamp propagate NaN; extremes return the first occurrence, and the
+ * first NaN if there is one.                                                      */
+enum b200CompareOp {
+  B200_CMP_EQ = 0, B200_CMP_NE, B200_CMP_LT, B200_CMP_LE, B200_CMP_GT, B200_CMP_GE,
+  B200_CMP_AND, B200_CMP_OR, B200_CMP_XOR   /* logical, operands tested against zero */
+};
+/* out (bool) = a <op> b; a and b of one dtype (any arithmetic dtype or bool),
+ * expanded to out's shape.                                                        */
+b200Status b200_compare(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, int32_t op,
+                        b200Stream stream);
+/* out (bool) = a <op> scalar, the scalar rounded to a's dtype first.               */
+b200Status b200_compare_scalar(const b200Tensor* out, const b200Tensor* a, double b, int32_t op,
+                               b200Stream stream);
+/* out = cond ? a : b (cond bool; a, b, out one dtype; all expanded to out's shape). */
+b200Status b200_where(const b200Tensor* out, const b200Tensor* cond, const b200Tensor* a,
+                      const b200Tensor* b, b200Stream stream);
+/* out = mask ? value : self. In place allowed.                                     */
+b200Status b200_masked_fill(const b200Tensor* out, const b200Tensor* self, const b200Tensor* mask,
+                            double value, b200Stream stream);
+/* out = max(a, b) (is_max) or min(a, b), elementwise.                              */
+b200Status b200_minmax(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, int32_t is_max,
+                       b200Stream stream);
+/* out = clamp(a, min, max) with either bound optional (has_min / has_max).         */
+b200Status b200_clamp(const b200Tensor* out, const b200Tensor* a, int32_t has_min, double min_value,
+                      int32_t has_max, double max_value, b200Stream stream);
+/* Maximum (is_max) or minimum of a contiguous tensor along `dim`: values (input's
+ * dtype) and / or indices (int64), each contiguous with the reduced dim removed;
+ * either may be NULL.                                                              */
+b200Status b200_extreme_dim(const b200Tensor* values, const b200Tensor* indices, const b200Tensor* in,
+                            int64_t dim, int32_t is_max, b200Stream stream);
+/* out[i] = start + i * step (1-D contiguous; integer outputs computed in int64).   */
+b200Status b200_arange(const b200Tensor* out, double start, double step, b200Stream stream);
+/* Upper (upper != 0) or lower triangle of the last two dims of a contiguous tensor,
+ * zeros elsewhere; `diagonal` as in torch.triu / torch.tril. In place allowed.      */
+b200Status b200_tri(const b200Tensor* out, const b200Tensor* in, int64_t diagonal, int32_t upper,
+                    b200Stream stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -114,7 +114,12 @@ def gen_structured(f, g, row, ns):
     decl_args = ", ".join("%s %s" % (a.type, a.name) for a in args)
     in_args = [a for a in args if a.name not in out_names]
     # meta() takes the functional arguments in schema order (as the structured C++ API spells them)
-    meta_call = ", ".join(a.name for a in in_args)
+    def meta_arg(a):
+        # the structured API spells optional scalars as a non-owning reference
+        if "optional<at::Scalar>" in str(a.type):
+            return "(%s.has_value() ? at::OptionalScalarRef(&(%s.value())) : at::OptionalScalarRef())" % (a.name, a.name)
+        return a.name
+    meta_call = ", ".join(meta_arg(a) for a in in_args)
     inherits_iter = g.out.structured_inherits is not None
     precomputed = g.out.precomputed is not None
     cls = "structured_%s_gcu" % name

@@ -186,6 +186,9 @@ void reduce_impl(const at::Tensor& self, at::OptionalIntArrayRef dim, const at::
   }
   at::Tensor in = self;
   if (mean && in.scalar_type() != out.scalar_type()) in = in.to(out.scalar_type());
+  // integer and bool inputs are summed in the output's type (int64 by default), as ATen promotes them
+  if (!mean && at::isIntegralType(in.scalar_type(), /*includeBool=*/true) && in.scalar_type() != out.scalar_type())
+    in = in.to(out.scalar_type());
   // the kernel wants the reduced dimensions adjacent: permute them to the end otherwise
   bool adjacent = true;
   for (size_t i = 1; i < dims.size(); ++i) adjacent = adjacent && dims[i] == dims[i - 1] + 1;
