@@ -321,6 +321,25 @@ b200Status b200_arange(const b200Tensor* out, double start, double step, b200Str
 b200Status b200_tri(const b200Tensor* out, const b200Tensor* in, int64_t diagonal, int32_t upper,
                     b200Stream stream);
 
+/* ---- backward of the layer's pointwise and row operators ---------------------
+ * (reference yaml rows silu_backward.grad_input, _softmax_backward_data.out,
+ * native_layer_norm_backward; fp32 math, one rounding per output, reductions in a
+ * fixed order.)                                                                    */
+/* grad_in = grad_out * s * (1 + x * (1 - s)), s = sigmoid(x).                      */
+b200Status b200_silu_backward(const b200Tensor* grad_in, const b200Tensor* grad_out, const b200Tensor* x,
+                              b200Stream stream);
+/* grad_in = output * (grad_out - sum_dim(grad_out * output)); contiguous operands.  */
+b200Status b200_softmax_backward(const b200Tensor* grad_in, const b200Tensor* grad_out,
+                                 const b200Tensor* output, int64_t dim, b200Stream stream);
+/* Layer-norm backward over an (M, N) view: dx, dweight, dbias (each optional) from
+ * grad_out, x, the saved f32 mean / rstd (M each) and the optional weight. dweight
+ * and dbias need a workspace of b200_layer_norm_backward_workspace_size bytes.      */
+size_t b200_layer_norm_backward_workspace_size(int64_t M, int64_t N);
+b200Status b200_layer_norm_backward(const b200Tensor* dx, const b200Tensor* dweight, const b200Tensor* dbias,
+                                    const b200Tensor* grad_out, const b200Tensor* x, const b200Tensor* mean,
+                                    const b200Tensor* rstd, const b200Tensor* weight, int64_t M, int64_t N,
+                                    void* workspace, size_t workspace_bytes, b200Stream stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif
