@@ -168,8 +168,10 @@ def run_gpu(args):
     # ---- prefill (headline) ---------------------------------------------------
     for _ in range(warmup):
         stack.prefill(x, group)
+    launches_before = b200ops.launch_count()
     with ClockSampler(local) as clocks:
         prefill_ms = timed(lambda: stack.prefill(x, group), steps)
+    gpu_launches = b200ops.launch_count() - launches_before   # this library's kernels inside the timed region
 
     # ---- end to end: host buffers in, host buffer out, every step -------------------
     # The step's input goes up from pinned memory on a copy stream while the previous step
@@ -262,7 +264,7 @@ def run_gpu(args):
             "clocks": clocks.summary(),
             "e2e": {"value": round(tokens / e2e_ms * 1e3, 1), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": x_host.numel() * 2},
-            "gpu_launches": steps * N_LAYERS * 11,
+            "gpu_launches": gpu_launches,
             "prefill": {"tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1),
                         "frac_of_bf16_sustained": round(flops_rank / prefill_ms / 1e9 / tf_sust, 3)},
             "decode": {"tokens_per_s": round(DECODE_B / decode_ms * 1e3, 1), "ms_per_step": round(decode_ms, 4),

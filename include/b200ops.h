@@ -87,6 +87,10 @@ size_t b200_dtype_size(int32_t dtype);  /* bytes per element, 0 if unknown    */
  * kernels launch on (SM count - n) SMs; process-wide, default 0. No reference
  * counterpart (the vendor library schedules its own kernels).                  */
 void b200_set_reserved_sms(int n);
+/* Kernel launches this library has issued in this process so far (a counter for
+ * benchmarks and tests: the difference around a region is the number of this
+ * library's kernels launched inside it).                                        */
+unsigned long long b200_launch_count(void);
 int b200_get_reserved_sms(void);
 /* Index kernels never trap on an out-of-range index: they substitute index 0
  * (or drop the element) and set bit 0 of a device-side error word. This call

@@ -316,6 +316,12 @@ def sdpa_flash_fwd(out, lse, q, k, v, is_causal, scale=None, stream=None):
                                     ctypes.c_int32(1 if is_causal else 0), ctypes.c_double(scale), _stream(stream)))
 
 
+def launch_count():
+    """Kernel launches the library has issued in this process so far."""
+    lib().b200_launch_count.restype = ctypes.c_ulonglong
+    return int(lib().b200_launch_count())
+
+
 def device_error_fetch():
     flags = ctypes.c_uint32(0)
     check(lib().b200_device_error_fetch(ctypes.byref(flags)))

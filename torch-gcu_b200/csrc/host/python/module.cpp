@@ -167,6 +167,7 @@ PYBIND11_MODULE(_C, m) {
       .def("captured", &GCUGraph::captured)
       .def("num_nodes", &GCUGraph::num_nodes);
   m.def("_gcu_isCurrentStreamCapturing", &current_stream_is_capturing);
+  m.def("_kernel_launch_count", [] { return static_cast<uint64_t>(b200_launch_count()); });
   m.def("_set_reserved_sms", [](int n) { b200_set_reserved_sms(n); });
   m.def("_get_reserved_sms", [] { return b200_get_reserved_sms(); });
 

@@ -235,6 +235,7 @@ b200Status b200_layer_norm_backward(const b200Tensor* dx, const b200Tensor* dwei
           pw, pb, static_cast<const T*>(grad_out->data), static_cast<const T*>(x->data), pm, pr, M, N);
       layer_norm_dwdb_final_kernel<T><<<static_cast<unsigned>((N + kThreads - 1) / kThreads), kThreads, 0, s>>>(
           dweight ? static_cast<T*>(dweight->data) : nullptr, dbias ? static_cast<T*>(dbias->data) : nullptr, pw, pb, chunks, N);
+      note_launches(dx ? 2 : 1);
     }
   });
   return check_launch("b200_layer_norm_backward");

@@ -32,7 +32,12 @@ inline b200Status fail(b200Status st, const char* fmt, ...) {
     if (!(cond)) return ::b200::fail((status), __VA_ARGS__); \
   } while (0)
 
+// Kernel launches issued by this library in this process (b200_launch_count): one per checked
+// launch; entry points that launch several kernels before one check add the rest themselves.
+void note_launches(int n);
+
 inline b200Status check_launch(const char* what) {
+  note_launches(1);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(B200_LAUNCH_FAILED, "%s: %s", what, cudaGetErrorString(e));

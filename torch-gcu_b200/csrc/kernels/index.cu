@@ -603,6 +603,7 @@ b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint3
   }
   *sorted_keys = kin;
   *sorted_vals = vin;
+  note_launches(3 * p.passes - 1);
   return check_launch("radix sort");
 }
 
@@ -692,6 +693,7 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
   if (st != B200_OK) return st;
   segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
+  note_launches(2);   // key generation and this one; the sort and the segment walk count themselves
   if (mode == 1) return launch_segment_rows<T, 1, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   if (mode == 2 && sizeof(T) == 2) return launch_segment_rows<T, 0, true>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   return launch_segment_rows<T, 0, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
@@ -971,6 +973,7 @@ b200Status b200_scatter_add(const b200Tensor* out, const b200Tensor* self, int64
     element_keys_kernel<int64_t><<<kgrid, kThreads, 0, s>>>((const int64_t*)index->data, n, ix, dim_stride, dim_size, out_numel, keys_a);
   else
     element_keys_kernel<int32_t><<<kgrid, kThreads, 0, s>>>((const int32_t*)index->data, n, ix, dim_stride, dim_size, out_numel, keys_a);
+  note_launches(1);   // the key kernel above
   uint32_t *sk, *sv;
   b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
   if (st != B200_OK) return st;

@@ -11,6 +11,9 @@ char* error_buffer() {
   return buf;
 }
 
+static std::atomic<unsigned long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+
 int sm_count_current_device();
 // SMs the persistent GEMM kernels leave free (for a collective running beside them).
 static std::atomic<int> g_reserved_sms{0};
@@ -41,6 +44,7 @@ const char* b200_last_error(void) { return b200::error_buffer(); }
 
 const char* b200_version(void) { return "b200ops 0.1 (sm_100a)"; }
 
+unsigned long long b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
 void b200_set_reserved_sms(int n) { b200::g_reserved_sms.store(n < 0 ? 0 : n, std::memory_order_relaxed); }
 int b200_get_reserved_sms(void) { return b200::g_reserved_sms.load(std::memory_order_relaxed); }
 

@@ -218,32 +218,31 @@ class DecoderStack:
             torch.gcu.set_reserved_sms(before)
 
     def _two_microbatches(self, x, group, caches):
+        import os
         import torch.distributed as dist
-        half = x.shape[0] // 2
-        xs = [x[:half], x[half:]]
+        n_mb = int(os.environ.get("TP_DECODER_MICROBATCHES", "2"))
+        if x.shape[0] % n_mb != 0:
+            n_mb = 2
+        part = x.shape[0] // n_mb
+        xs = [x[m * part:(m + 1) * part] for m in range(n_mb)]
         B, S, H = xs[0].shape
-        pending = [None, None]   # all-reduce of the previous layer's MLP output, per half
-        carry = [None, None]     # (down, r) that the pending all-reduce completes
+        pending = [None] * n_mb   # all-reduce of the previous layer's MLP output, per part
+        carry = [None] * n_mb     # (down, r) that the pending all-reduce completes
         for i, layer in enumerate(self.layers):
-            o, wo = [None, None], [None, None]
-            for m in (0, 1):
+            o, wo = [None] * n_mb, [None] * n_mb
+            for m in range(n_mb):
                 if pending[m] is not None:
                     pending[m].wait()
                     xs[m] = torch.add(carry[m][0].view(B, S, H), carry[m][1])
-                kv = None if caches is None else tuple(c[m * half:(m + 1) * half] for c in caches[i])
+                kv = None if caches is None else tuple(c[m * part:(m + 1) * part] for c in caches[i])
                 o[m] = layer.attn_part(xs[m], kv)
                 wo[m] = dist.all_reduce(o[m], group=group, async_op=True)
-            for m in (0, 1):
+            for m in range(n_mb):
                 wo[m].wait()
                 carry[m] = layer.mlp_part(o[m], xs[m])
                 pending[m] = dist.all_reduce(carry[m][0], group=group, async_op=True)
         out = []
-        for m in (0, 1):
+        for m in range(n_mb):
             pending[m].wait()
             out.append(torch.add(carry[m][0].view(B, S, H), carry[m][1]))
         return torch.cat(out, 0)
-
-    def decode(self, x, caches, pos, group=None):
-        for layer, kv in zip(self.layers, caches):
-            x = layer.forward_decode(x, kv, pos, group)
-        return x
