@@ -246,3 +246,8 @@ class DecoderStack:
             pending[m].wait()
             out.append(torch.add(carry[m][0].view(B, S, H), carry[m][1]))
         return torch.cat(out, 0)
+
+    def decode(self, x, caches, pos, group=None):
+        for layer, kv in zip(self.layers, caches):
+            x = layer.forward_decode(x, kv, pos, group)
+        return x
