@@ -344,6 +344,20 @@ b200Status b200_layer_norm_backward(const b200Tensor* dx, const b200Tensor* dwei
                                     const b200Tensor* rstd, const b200Tensor* weight, int64_t M, int64_t N,
                                     void* workspace, size_t workspace_bytes, b200Stream stream);
 
+/* Flash-attention backward (reference: aot_ops/gcu_attention.cpp:135-203
+ * topsatenScaledDotProductFlashAttentionBackward). dq (B,Hq,Sq,D), dk / dv
+ * (B,Hkv,Sk,D) from dout, q, k, v, the forward's out and logsumexp; D = 128,
+ * bf16 / f16, last dim contiguous, other strides free, causal needs Sq == Sk.
+ * The probabilities are recomputed from q, k and lse; no atomics are used, so
+ * the gradients are reproducible. Needs b200_sdpa_flash_bwd_workspace_size(q)
+ * bytes of workspace (the per-row sum of dout * out).                            */
+size_t b200_sdpa_flash_bwd_workspace_size(const b200Tensor* q);
+b200Status b200_sdpa_flash_bwd(const b200Tensor* dq, const b200Tensor* dk, const b200Tensor* dv,
+                               const b200Tensor* dout, const b200Tensor* q, const b200Tensor* k,
+                               const b200Tensor* v, const b200Tensor* out, const b200Tensor* lse,
+                               int32_t is_causal, double scale, void* workspace, size_t workspace_bytes,
+                               b200Stream stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -121,3 +121,46 @@ def test_sdpa_growing_maximum(ops, dtype, Sq, Sk, causal):
     assert (s.max(-1).values - s[..., :128].max(-1).values).max() > 20   # the maximum really moves
     close(out, (torch.softmax(s, -1) @ vf).to(dtype), 1.6e-2, 1e-2)
     close(lse, torch.logsumexp(s, -1), 1e-3, 2e-3)
+
+
+def _cpu_attention_grads(q, k, v, go, causal):
+    """fp32 autograd on the CPU over the same 16-bit operands."""
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    G = q.shape[1] // k.shape[1]
+    ke, ve = kf.repeat_interleave(G, 1), vf.repeat_interleave(G, 1)
+    s = (qf @ ke.transpose(-1, -2)) * q.shape[-1] ** -0.5
+    if causal:
+        S = q.shape[2]
+        s = s.masked_fill(torch.ones(S, S, dtype=torch.bool).triu(1), float("-inf"))
+    o = torch.softmax(s, -1) @ ve
+    o.backward(go.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Sq,Sk,causal", [(1, 2, 2, 128, 128, True), (2, 4, 2, 256, 256, True), (1, 4, 1, 200, 200, True),
+                                                   (1, 2, 1, 128, 384, False), (2, 8, 2, 77, 300, False), (1, 4, 4, 640, 640, True)])
+@pytest.mark.parametrize("dtype", [BF, torch.float16])
+def test_sdpa_backward(ops, B, Hq, Hkv, Sq, Sk, causal, dtype):
+    """dq, dk, dv of the flash kernel against fp32 CPU autograd on the same operands."""
+    g = torch.Generator().manual_seed(55)
+    D = 128
+    q = torch.randn(B, Hq, Sq, D, generator=g).to(dtype)
+    k = torch.randn(B, Hkv, Sk, D, generator=g).to(dtype)
+    v = torch.randn(B, Hkv, Sk, D, generator=g).to(dtype)
+    go = torch.randn(B, Hq, Sq, D, generator=g).to(dtype)
+    qd, kd, vd, god = dev(q), dev(k), dev(v), dev(go)
+    out = torch.empty(B, Sq, Hq, D, dtype=dtype, device=DEV).transpose(1, 2)
+    lse = torch.empty(B, Hq, Sq, device=DEV)
+    ops.sdpa_flash_fwd(out, lse, qd, kd, vd, causal)
+    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    ops.sdpa_flash_bwd(dq, dk, dv, god, qd, kd, vd, out, lse, causal)
+    assert ops.device_error_fetch() == 0
+    rq, rk, rv = _cpu_attention_grads(q, k, v, go, causal)
+    for got, ref, name in ((dq, rq, "dq"), (dk, rk, "dk"), (dv, rv, "dv")):
+        err = (got.float().cpu() - ref).norm() / ref.norm()
+        assert err < 2e-2, (name, err.item())
+        close(got, ref.to(dtype), 5e-2, 5e-2 * ref.abs().max().item())
+    # reproducible: no atomics anywhere in the backward
+    dq2, dk2, dv2 = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
+    ops.sdpa_flash_bwd(dq2, dk2, dv2, god, qd, kd, vd, out, lse, causal)
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)

@@ -119,3 +119,24 @@ def test_decoder_layer_training_step(dev):
     for k in params:
         rel = (g_d[k] - g_c[k]).norm() / g_c[k].norm()
         assert rel < 1e-3, (k, rel)
+
+
+def test_sdpa_trains_through_the_flash_kernels(dev):
+    """F.scaled_dot_product_attention with head dim 128 takes the flash forward and, under
+    autograd, the flash backward; gradients against CPU autograd in fp32."""
+    g = torch.Generator().manual_seed(25)
+    bf = torch.bfloat16
+    q = torch.randn(2, 4, 256, 128, generator=g).to(bf)
+    k = torch.randn(2, 2, 256, 128, generator=g).to(bf)
+    v = torch.randn(2, 2, 256, 128, generator=g).to(bf)
+    go = torch.randn(2, 4, 256, 128, generator=g).to(bf)
+    qd, kd, vd = (t.to(dev).requires_grad_() for t in (q, k, v))
+    out = F.scaled_dot_product_attention(qd, kd, vd, is_causal=True, enable_gqa=True)
+    out.backward(go.to(dev))
+    qc, kc, vc = (t.float().requires_grad_() for t in (q, k, v))
+    ref = F.scaled_dot_product_attention(qc, kc.repeat_interleave(2, 1), vc.repeat_interleave(2, 1), is_causal=True)
+    ref.backward(go.float())
+    assert torch.allclose(out.detach().cpu().float(), ref.detach(), rtol=2e-2, atol=2e-2)
+    for got, want in ((qd.grad, qc.grad), (kd.grad, kc.grad), (vd.grad, vc.grad)):
+        rel = (got.cpu().float() - want).norm() / want.norm()
+        assert rel < 2e-2, rel

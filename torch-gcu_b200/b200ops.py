@@ -316,6 +316,20 @@ def sdpa_flash_fwd(out, lse, q, k, v, is_causal, scale=None, stream=None):
                                     ctypes.c_int32(1 if is_causal else 0), ctypes.c_double(scale), _stream(stream)))
 
 
+def sdpa_flash_bwd(dq, dk, dv, dout, q, k, v, out, lse, is_causal, scale=None, workspace=None, stream=None):
+    """Flash-attention backward: dq, dk, dv from dout and the forward's q, k, v, out, lse."""
+    import torch
+    sc = float(scale) if scale is not None else float(q.shape[-1]) ** -0.5
+    lib().b200_sdpa_flash_bwd_workspace_size.restype = ctypes.c_size_t
+    need = lib().b200_sdpa_flash_bwd_workspace_size(_ref(view(q)))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=q.device)
+    check(lib().b200_sdpa_flash_bwd(_ref(view(dq)), _ref(view(dk)), _ref(view(dv)), _ref(view(dout)), _ref(view(q)),
+                                    _ref(view(k)), _ref(view(v)), _ref(view(out)), _ref(view(lse)),
+                                    ctypes.c_int32(1 if is_causal else 0), ctypes.c_double(sc), *ws_args(workspace),
+                                    _stream(stream)))
+
+
 def launch_count():
     """Kernel launches the library has issued in this process so far."""
     lib().b200_launch_count.restype = ctypes.c_ulonglong

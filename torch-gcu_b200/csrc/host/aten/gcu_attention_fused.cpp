@@ -54,6 +54,51 @@ _scaled_dot_product_fused_attention_overrideable(const at::Tensor& query, const 
   return aotops::_scaled_dot_product_flash_attention(query, key, value, dropout_p, is_causal, return_debug_mask, scale);
 }
 
+// Backward of the flash kernel: dq, dk, dv (reference: aot_ops/gcu_attention.cpp:135-203).
+static std::tuple<at::Tensor, at::Tensor, at::Tensor> sdpa_flash_backward(const at::Tensor& grad_out, const at::Tensor& q,
+                                                                          const at::Tensor& k, const at::Tensor& v,
+                                                                          const at::Tensor& out, const at::Tensor& lse, bool is_causal,
+                                                                          std::optional<double> scale) {
+  TORCH_CHECK(q.dim() == 4 && q.size(3) == 128, "flash attention backward on the gcu backend supports head dim 128");
+  auto last_contig = [](const at::Tensor& t) { return t.stride(-1) == 1 ? t : t.contiguous(); };
+  at::Tensor go = last_contig(grad_out), qc = last_contig(q), kc = last_contig(k), vc = last_contig(v), oc = last_contig(out);
+  at::Tensor l = lse.contiguous();
+  // gradients in the layout the forward uses for its output: (B,S,H,D) storage viewed (B,H,S,D)
+  at::Tensor dq = at::empty({q.size(0), q.size(2), q.size(1), q.size(3)}, q.options()).transpose(1, 2);
+  at::Tensor dk = at::empty({k.size(0), k.size(2), k.size(1), k.size(3)}, k.options()).transpose(1, 2);
+  at::Tensor dv = at::empty({v.size(0), v.size(2), v.size(1), v.size(3)}, v.options()).transpose(1, 2);
+  if (q.numel() == 0 || k.numel() == 0) return std::make_tuple(dq.zero_(), dk.zero_(), dv.zero_());
+  b200Tensor vdq = to_b200(dq), vdk = to_b200(dk), vdv = to_b200(dv), vgo = to_b200(go), vq = to_b200(qc), vk = to_b200(kc),
+             vv = to_b200(vc), vo = to_b200(oc), vl = to_b200(l);
+  const size_t ws_bytes = b200_sdpa_flash_bwd_workspace_size(&vq);
+  at::Tensor ws = at::empty({static_cast<int64_t>(ws_bytes)}, q.options().dtype(at::kByte));
+  const double sc = scale.has_value() ? *scale : 1.0 / std::sqrt(static_cast<double>(q.size(3)));
+  const c10::OptionalDeviceGuard guard(q.device());
+  cudaStream_t stream = current_stream(q);
+  GCU_KERNEL_CALL(b200_sdpa_flash_bwd, stream, &vdq, &vdk, &vdv, &vgo, &vq, &vk, &vv, &vo, &vl, is_causal ? 1 : 0, sc, ws.data_ptr(),
+                  ws_bytes);
+  return std::make_tuple(dq, dk, dv);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> _scaled_dot_product_flash_attention_backward(
+    const at::Tensor& grad_out, const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, const at::Tensor& out,
+    const at::Tensor& logsumexp, const at::Tensor&, const at::Tensor&, int64_t, int64_t, double dropout_p, bool is_causal,
+    const at::Tensor&, const at::Tensor&, std::optional<double> scale) {
+  TORCH_CHECK(dropout_p == 0.0, "flash attention on the gcu backend does not implement dropout");
+  return sdpa_flash_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale);
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> _scaled_dot_product_fused_attention_overrideable_backward(
+    const at::Tensor& grad_out, const at::Tensor& query, const at::Tensor& key, const at::Tensor& value, const at::Tensor& attn_bias,
+    std::array<bool, 4> grad_input_mask, const at::Tensor& out, const at::Tensor& logsumexp, const at::Tensor&, const at::Tensor&, int64_t,
+    int64_t, double dropout_p, bool is_causal, const at::Tensor&, const at::Tensor&, std::optional<double> scale) {
+  TORCH_CHECK(dropout_p == 0.0, "flash attention on the gcu backend does not implement dropout");
+  TORCH_CHECK(!attn_bias.defined() || attn_bias.numel() == 0, "flash attention on the gcu backend takes no attention bias");
+  (void)grad_input_mask;
+  auto [dq, dk, dv] = sdpa_flash_backward(grad_out, query, key, value, out, logsumexp, is_causal, scale);
+  return std::make_tuple(dq, dk, dv, at::Tensor());
+}
+
 // --------------------------------------------------------------- fused ops --
 std::tuple<at::Tensor, at::Tensor> rms_norm_residual(const at::Tensor& x, const std::optional<at::Tensor>& residual,
                                                      const at::Tensor& weight, double eps) {
@@ -163,7 +208,9 @@ int64_t fused_sdp_choice(const at::Tensor& query, const at::Tensor& key, const a
                         (dt == at::kBFloat16 || dt == at::kHalf) && key.scalar_type() == dt && value.scalar_type() == dt &&
                         (query.size(-1) == 64 || query.size(-1) == 128) && key.size(-1) == query.size(-1) &&
                         value.size(-1) == query.size(-1) && key.size(1) > 0 && query.size(1) % key.size(1) == 0 &&
-                        (!is_causal || query.size(2) == key.size(2)) && !query.requires_grad() && key.size(2) > 0;
+                        (!is_causal || query.size(2) == key.size(2)) && key.size(2) > 0 &&
+                        // the backward kernel exists for head dim 128; other sizes train through the math path
+                        (query.size(-1) == 128 || !(query.requires_grad() || key.requires_grad() || value.requires_grad()));
   return static_cast<int64_t>(flash_ok ? sdp::SDPBackend::overrideable : sdp::SDPBackend::math);
 }
 
