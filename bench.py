@@ -311,13 +311,15 @@ def gemm_roofline(dev, tf_peak, peak_kind, world):
     w = (torch.randn(n, k) * 0.02).bfloat16().to(dev)
     ms = _time_gcu(lambda: efficient.linear_swiglu(a, w))
     tf = 2 * m * n * k / ms / 1e9
-    # DRAM traffic: the profiler capture of the plain two-operand kernel on 8192x4096x4096 (profiles/) moved
-    # 164.8 MB for 167.8 MB of operands and output; traffic grows with those bytes, so that ratio is applied
-    # to this launch's operands and its (M, N/2) output.
-    operand_bytes = 2 * (m * k + n * k + m * n // 2)
+    # DRAM traffic per launch, scaled from a smaller capture of the same kernel (profiles/): the tile walk keeps a
+    # band of 20 row-tiles of A in L2 and streams the weight once per band, so traffic = A + W x bands + out; the
+    # capture at 8192 x (2 x 4096) x 4096 (2 bands) moved 305.3 MB against 268.4 MB by that count (x 1.14, L2 misses
+    # inside a band), and the same factor is applied to this launch's counts.
+    bands = -(-(m // 256) // 20)
+    traffic = int(1.14 * 2 * (m * k + n * k * bands + m * n // 2))
     return {"bound": "tensor", "kernel": "gemm_tc2_kernel<swiglu> (gate/up projection %dx%dx%d, SwiGLU in the epilogue)" % (m, n, k),
             "achieved": round(tf, 1), "peak": tf_peak, "unit": "TFLOP/s", "frac": round(tf / tf_peak, 3),
-            "traffic": int(operand_bytes * 164.8 / 167.8), "traffic_unit": "bytes per launch, scaled from a smaller capture",
+            "traffic": traffic, "traffic_unit": "bytes per launch, scaled from a smaller capture",
             "peak_kind": peak_kind + " bf16 burst"}
 
 
@@ -422,6 +424,26 @@ def run_micro(name):
         w = (torch.randn(n, k, device=dev) * 0.02).to(bf)
         out = torch.empty(m, n, dtype=bf, device=dev)
         fn, work = ops.bind("mm", out, a, w.t()), {"flops": 2 * m * n * k}
+    elif name == "gemm_swiglu":
+        m, f, k = 8192, 4096, 4096
+        a = torch.randn(m, k, device=dev).to(bf)
+        w = (torch.randn(2 * f, k, device=dev) * 0.02).to(bf)
+        out = torch.empty(m, f, dtype=bf, device=dev)
+        fn, work = ops.bind("mm_swiglu", out, a, w), {"flops": 2 * m * 2 * f * k}
+    elif name == "sdpa_bwd":
+        B, Hq, Hkv, S, D = 2, 32, 8, 2048, 128
+        q = torch.randn(B, Hq, S, D, device=dev).to(bf)
+        k_ = torch.randn(B, Hkv, S, D, device=dev).to(bf)
+        v_ = torch.randn(B, Hkv, S, D, device=dev).to(bf)
+        go = torch.randn(B, Hq, S, D, device=dev).to(bf)
+        out = torch.empty(B, S, Hq, D, dtype=bf, device=dev).transpose(1, 2)
+        lse = torch.empty(B, Hq, S, device=dev)
+        ops.sdpa_flash_fwd(out, lse, q, k_, v_, True)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k_), torch.empty_like(v_)
+        ws = torch.empty(B * Hq * S * 4 + 256, dtype=torch.uint8, device=dev)
+        fn = ops.bind("sdpa_flash_bwd", dq, dk, dv, go, q, k_, v_, out, lse, ctypes.c_int32(1), ctypes.c_double(D ** -0.5),
+                      *ops.ws_args(ws), keep=(ws,))
+        work = {"flops": 10 * B * Hq * S * S * D // 2}
     elif name == "sdpa":
         B, Hq, Hkv, S, D = 2, 32, 8, 2048, 128
         q = torch.randn(B, Hq, S, D, device=dev).to(bf)
@@ -474,7 +496,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
-    ap.add_argument("--micro", default="", help="gemm | sdpa | decode | swiglu | scatter: a 3-launch case for profiler captures")
+    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | sdpa | sdpa_bwd | decode | swiglu | scatter: a 3-launch case for profiler captures")
     args = ap.parse_args()
     if args.micro:
         run_micro(args.micro)

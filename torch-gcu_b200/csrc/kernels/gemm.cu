@@ -69,7 +69,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;           // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
-constexpr int GROUP_M = 8;
+constexpr int kBandBytes = 40 << 20;   // rows of A kept hot in L2 while one band of row-tiles sweeps all of B
 
 struct GemmParams {
   int M, N, K, batch;
@@ -82,6 +82,7 @@ struct GemmParams {
   int64_t c_sb, c_sm, c_sn;
   unsigned int* error_word;
   int up_offset;                 // fused SwiGLU: row of B where the "up" half starts (= output columns F)
+  int group_m;                   // row-tiles per band of the tile walk
 };
 
 template <int BN> struct GemmCfg {
@@ -93,7 +94,15 @@ template <int BN> struct GemmCfg {
   static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {64,128,256}
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& tm, int& tn) {
+// Row-tiles per band: as many as keep the band's rows of A (tile_rows x K each) within kBandBytes,
+// so that B is streamed from DRAM once per band and A once in total.
+inline int band_rows(int tile_rows, int64_t K) {
+  const int64_t per_tile = static_cast<int64_t>(tile_rows) * K * 2;
+  int64_t g = per_tile > 0 ? kBandBytes / per_tile : 8;
+  return static_cast<int>(g < 8 ? 8 : (g > 64 ? 64 : g));   // never narrower than 8: a long K needs B reuse more
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int GROUP_M, int& b, int& tm, int& tn) {
   const int per_batch = tiles_m * tiles_n;
   b = tile / per_batch;
   int t = tile - b * per_batch;
@@ -156,7 +165,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int b, tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+        tile_coords(tile, tiles_m, tiles_n, p.group_m, b, tm, tn);
         for (int k = 0; k < n_k; ++k) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStage;
@@ -225,7 +234,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       int b, tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, p.group_m, b, tm, tn);
       if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * BM + quarter * 32 + lane;
@@ -330,6 +339,7 @@ b200Status launch_tc(const Operand& oa, const Operand& ob, GemmParams p, cudaStr
     last_dev = dev;
   }
   B200_REQUIRE(attr_err == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(attr_err));
+  p.group_m = band_rows(BM, p.K);
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
   const int sms = gemm_sm_budget();
   const int grid = tiles < sms ? tiles : sms;
@@ -458,7 +468,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         int b, tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+        tile_coords(tile, tiles_m, tiles_n, p.group_m, b, tm, tn);
         const int row0 = tm * BM2 + static_cast<int>(rank) * BM;          // this CTA's rows of A
         const int col0 = SWIGLU ? tn * BNO + static_cast<int>(rank) * p.up_offset   // gate rows / up rows of B
                                 : tn * BN2 + static_cast<int>(rank) * (BN2 / 2);    // this CTA's columns of B
@@ -526,7 +536,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const int ab = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1u;
       int b, tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, b, tm, tn);
+      tile_coords(tile, tiles_m, tiles_n, p.group_m, b, tm, tn);
       if (!mbar_wait(&acc_full[ab], acc_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * BM2 + static_cast<int>(rank) * BM + quarter * 32 + lane;
@@ -627,6 +637,7 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
     last_dev = dev;
   }
   constexpr int bno = SWIGLU ? BN2 / 2 : BN2;
+  p.group_m = band_rows(BM2, p.K);
   const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + bno - 1) / bno) * p.batch;
   const int pairs = gemm_sm_budget() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
@@ -668,7 +679,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   const int rank = static_cast<int>(cluster.block_rank());
   const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BNS - 1) / BNS;
   int b, tm, tn;
-  tile_coords(static_cast<int>(blockIdx.x) / splits, tiles_m, tiles_n, b, tm, tn);
+  tile_coords(static_cast<int>(blockIdx.x) / splits, tiles_m, tiles_n, p.group_m, b, tm, tn);
   const int n_k = (p.K + BK - 1) / BK;
   const int per = (n_k + splits - 1) / splits;
   const int k_begin = min(rank * per, n_k), k_end = min(k_begin + per, n_k);
@@ -808,6 +819,7 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
+  p.group_m = 8;
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BNS - 1) / BNS) * p.batch;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * splits);
