@@ -166,23 +166,51 @@ def run_gpu(args):
         return t.item()
 
     # ---- prefill (headline) ---------------------------------------------------
+    # The 8-layer pass is recorded once into a graph (kernels, and with more than one rank the
+    # all-reduces on the process group's stream) and replayed: no host work per operator inside the
+    # timed region. TP_DECODER_GRAPH=0 times the eager loop instead.
+    use_graph = os.environ.get("TP_DECODER_GRAPH", "1") != "0"
     for _ in range(warmup):
         stack.prefill(x, group)
+
+    def capture(inp):
+        g = torch.gcu.GCUGraph()
+        before = b200ops.launch_count()
+        with torch.gcu.graph(g):
+            out = stack.prefill(inp, group)
+        return g, out, b200ops.launch_count() - before
+
+    graph_error = None
+    if use_graph:
+        try:
+            graph_x, y_x, launches_per_step = capture(x)
+        except RuntimeError as e:   # fall back to the eager loop rather than lose the measurement
+            use_graph, graph_error = False, str(e).splitlines()[0][:200]
+            torch.gcu.synchronize()
+    if use_graph:
+        step = graph_x.replay
+        for _ in range(warmup):
+            step()
+    else:
+        step = lambda: stack.prefill(x, group)  # noqa: E731
     launches_before = b200ops.launch_count()
     with ClockSampler(local) as clocks:
-        prefill_ms = timed(lambda: stack.prefill(x, group), steps)
-    gpu_launches = b200ops.launch_count() - launches_before   # this library's kernels inside the timed region
+        prefill_ms = timed(step, steps)
+    # this library's kernels inside the timed region (graph nodes when replaying)
+    gpu_launches = launches_per_step * steps if use_graph else b200ops.launch_count() - launches_before
 
     # ---- end to end: host buffers in, host buffer out, every step -------------------
     # The step's input goes up from pinned memory on a copy stream while the previous step
     # computes, and its result comes down on a second copy stream while the next step
-    # computes: what a serving loop built on torch.gcu streams and events does. All K
+    # computes: what a serving loop built on torch.gcu streams, events and graphs does. All K
     # uploads and K downloads lie inside the timed region.
     out_host = torch.empty_like(x_host).pin_memory()
     s_in, s_out = torch.gcu.Stream(), torch.gcu.Stream()
     x_dev = [torch.empty_like(x), torch.empty_like(x)]
-    uploaded = [None, None]   # event: x_dev[i] holds the step's input
-    consumed = [None, None]   # event: the pass reading x_dev[i] has been enqueued and finished
+    slot_graph = [capture(x_dev[i])[:2] for i in range(2)] if use_graph else None
+    uploaded = [None, None]     # event: x_dev[i] holds the step's input
+    consumed = [None, None]     # event: the pass reading x_dev[i] has finished
+    downloaded = [None, None]   # event: the result of the pass of slot i has reached the host
 
     def upload(slot):
         with torch.gcu.stream(s_in):
@@ -199,12 +227,19 @@ def run_gpu(args):
             if i + 1 < n:
                 upload(slot ^ 1)
             cur.wait_event(uploaded[slot])
-            y = stack.prefill(x_dev[slot], group)
+            if use_graph:
+                if downloaded[slot] is not None:
+                    cur.wait_event(downloaded[slot])   # the replay overwrites the slot's output buffer
+                slot_graph[slot][0].replay()
+                y = slot_graph[slot][1]
+            else:
+                y = stack.prefill(x_dev[slot], group)
+                y.record_stream(s_out)
             consumed[slot] = cur.record_event()
-            y.record_stream(s_out)
             with torch.gcu.stream(s_out):
                 s_out.wait_event(consumed[slot])
                 out_host.copy_(y, non_blocking=True)
+                downloaded[slot] = s_out.record_event()
         cur.wait_stream(s_out)
 
     e2e_loop(2)
@@ -220,6 +255,11 @@ def run_gpu(args):
         dist.all_reduce(td, op=dist.ReduceOp.MAX)
         t = td.cpu()
     e2e_ms = t.item()
+    if use_graph:
+        for g_, _ in slot_graph:
+            g_.reset()
+        graph_x.reset()
+    del slot_graph
 
     # ---- decode ------------------------------------------------------------------
     hk = CFG["kv_heads"] // world
@@ -264,7 +304,7 @@ def run_gpu(args):
             "clocks": clocks.summary(),
             "e2e": {"value": round(tokens / e2e_ms * 1e3, 1), "unit": UNIT,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": x_host.numel() * 2},
-            "gpu_launches": gpu_launches,
+            "gpu_launches": gpu_launches, "graph_replay": use_graph if graph_error is None else "failed: " + graph_error,
             "prefill": {"tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1),
                         "frac_of_bf16_sustained": round(flops_rank / prefill_ms / 1e9 / tf_sust, 3)},
             "decode": {"tokens_per_s": round(DECODE_B / decode_ms * 1e3, 1), "ms_per_step": round(decode_ms, 4),

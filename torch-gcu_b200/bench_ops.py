@@ -206,6 +206,13 @@ def measure_ops(dev, steps, warmup, only=""):
         one_pass(events)
     torch.cuda.synchronize(dev)
     op_ms = [sum(s.elapsed_time(e) for s, e in ev) / steps / NSETS for ev in events]
+    # kernels per call, counted by the library rather than assumed
+    import b200ops
+    for op in ops:
+        before = b200ops.launch_count()
+        op.gpu_run()
+        op.launches = b200ops.launch_count() - before
+    torch.cuda.synchronize(dev)
     return ops, op_ms
 
 

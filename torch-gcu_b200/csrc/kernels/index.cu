@@ -14,6 +14,8 @@
 // floating-point atomics anywhere, so results are run-to-run identical.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 #include <mutex>
 
 namespace b200 {
@@ -245,18 +247,15 @@ constexpr int kSortThreads = 256;
 constexpr int kItemsPerThread = 4;
 constexpr int kTile = kSortThreads * kItemsPerThread;  // 1024
 constexpr int kWarps = kSortThreads / 32;
-constexpr int kMaxPasses = 4;
 
 // hist[digit * nblocks + block]: digit counts of every tile, for one pass. The
 // histogram is taken again before each pass because the previous pass has
 // permuted which keys sit in which tile.
-__global__ void __launch_bounds__(kSortThreads)
-radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int pass, int nblocks,
-                  uint32_t* __restrict__ hist) {
-  __shared__ uint32_t sh[256];
+__device__ __forceinline__ void hist_tile(const uint32_t* __restrict__ keys, int64_t n, int pass, int nblocks, int tile,
+                                          uint32_t* __restrict__ hist, uint32_t* sh /* [256] */) {
   sh[threadIdx.x] = 0;
   __syncthreads();
-  const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
+  const int64_t base = static_cast<int64_t>(tile) * kTile;
   const int shift = 8 * pass;
 #pragma unroll 4
   for (int r = 0; r < kItemsPerThread; ++r) {
@@ -264,7 +263,15 @@ radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int pass, int nb
     if (i < n) atomicAdd(&sh[(keys[i] >> shift) & 255u], 1u);
   }
   __syncthreads();
-  hist[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x] = sh[threadIdx.x];
+  hist[static_cast<int64_t>(threadIdx.x) * nblocks + tile] = sh[threadIdx.x];
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+radix_hist_kernel(const uint32_t* __restrict__ keys, int64_t n, int pass, int nblocks,
+                  uint32_t* __restrict__ hist) {
+  __shared__ uint32_t sh[256];
+  hist_tile(keys, n, pass, nblocks, blockIdx.x, hist, sh);
 }
 
 // Exclusive scan over the 256 threads of a block; *total gets the sum. `sh` holds
@@ -294,10 +301,9 @@ __device__ __forceinline__ uint32_t block_scan_256(uint32_t v, uint32_t* sh, uin
 // Block d scans, in place, the row of tile counts of digit d (exclusive) and
 // leaves the digit's total in totals[d]; the scatter kernel adds the scan over
 // the 256 totals itself.
-__global__ void __launch_bounds__(kSortThreads)
-radix_scan_rows_kernel(uint32_t* __restrict__ hist, int nblocks, uint32_t* __restrict__ totals) {
-  __shared__ uint32_t sh[kWarps];
-  uint32_t* row = hist + static_cast<int64_t>(blockIdx.x) * nblocks;
+__device__ __forceinline__ void scan_row(uint32_t* __restrict__ hist, int nblocks, int digit, uint32_t* __restrict__ totals,
+                                         uint32_t* sh /* [kWarps] */) {
+  uint32_t* row = hist + static_cast<int64_t>(digit) * nblocks;
   uint32_t carry = 0;
   for (int base = 0; base < nblocks; base += kSortThreads) {
     const int i = base + threadIdx.x;
@@ -307,28 +313,40 @@ radix_scan_rows_kernel(uint32_t* __restrict__ hist, int nblocks, uint32_t* __res
     if (i < nblocks) row[i] = carry + ex;
     carry += total;
   }
-  if (threadIdx.x == 0) totals[blockIdx.x] = carry;
+  if (threadIdx.x == 0) totals[digit] = carry;
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+radix_scan_rows_kernel(uint32_t* __restrict__ hist, int nblocks, uint32_t* __restrict__ totals) {
+  __shared__ uint32_t sh[kWarps];
+  scan_row(hist, nblocks, blockIdx.x, totals, sh);
 }
 
 // vals_in == nullptr: the value of item i is i (first pass).
-__global__ void __launch_bounds__(kSortThreads)
-radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
-                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
-                     int pass, int nblocks, const uint32_t* __restrict__ hist_scanned,
-                     const uint32_t* __restrict__ totals) {
-  __shared__ uint32_t warp_count[kWarps][256];  // sweep 1: counts; then exclusive base per warp
-  __shared__ uint32_t digit_base[256];
-  __shared__ uint32_t scan_sh[kWarps];
+struct ScatterSmem {
+  uint32_t warp_count[kWarps][256];  // sweep 1: counts; then exclusive base per warp
+  uint32_t digit_base[256];
+  uint32_t scan_sh[kWarps];
+};
+
+__device__ __forceinline__ void scatter_tile(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                                             uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
+                                             int pass, int nblocks, int tile, const uint32_t* __restrict__ hist_scanned,
+                                             const uint32_t* __restrict__ totals, ScatterSmem& sm) {
+  auto& warp_count = sm.warp_count;
+  auto& digit_base = sm.digit_base;
+  uint32_t* scan_sh = sm.scan_sh;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kWarps * 256; i += kSortThreads) (&warp_count[0][0])[i] = 0;
   {
     uint32_t all;
     const uint32_t first = block_scan_256(totals[threadIdx.x], scan_sh, &all);   // where digit threadIdx.x starts
-    digit_base[threadIdx.x] = first + hist_scanned[static_cast<int64_t>(threadIdx.x) * nblocks + blockIdx.x];
+    digit_base[threadIdx.x] = first + hist_scanned[static_cast<int64_t>(threadIdx.x) * nblocks + tile];
   }
   __syncthreads();
 
-  const int64_t wbase = static_cast<int64_t>(blockIdx.x) * kTile + warp * (kItemsPerThread * 32);
+  const int64_t wbase = static_cast<int64_t>(tile) * kTile + warp * (kItemsPerThread * 32);
   uint32_t key[kItemsPerThread];
   const int shift = 8 * pass;
 #pragma unroll
@@ -379,6 +397,41 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
       // (the digits never reach it) and turns the value into an invalid id
       vals_out[pos] = (key[r] >> 31) ? 0xffffffffu : (vals_in ? vals_in[i] : static_cast<uint32_t>(i));
     }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                     uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
+                     int pass, int nblocks, const uint32_t* __restrict__ hist_scanned,
+                     const uint32_t* __restrict__ totals) {
+  __shared__ ScatterSmem sm;
+  scatter_tile(keys_in, vals_in, keys_out, vals_out, n, pass, nblocks, blockIdx.x, hist_scanned, totals, sm);
+}
+
+// All passes in one cooperative launch: histogram, row scans and scatter of a pass are
+// separated by grid-wide barriers instead of kernel boundaries (three launches per pass
+// otherwise, each a few microseconds of ramp for a few hundred kilobytes of keys).
+__global__ void __launch_bounds__(kSortThreads)
+radix_sort_fused_kernel(uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, int64_t n, int passes,
+                        int nblocks, uint32_t* hist, uint32_t* totals) {
+  namespace cg = cooperative_groups;
+  cg::grid_group grid = cg::this_grid();
+  __shared__ ScatterSmem sm;
+  uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
+  for (int pass = 0; pass < passes; ++pass) {
+    for (int tile = blockIdx.x; tile < nblocks; tile += gridDim.x) hist_tile(kin, n, pass, nblocks, tile, hist, sm.digit_base);
+    grid.sync();
+    for (int d = blockIdx.x; d < 256; d += gridDim.x) scan_row(hist, nblocks, d, totals, sm.scan_sh);
+    grid.sync();
+    for (int tile = blockIdx.x; tile < nblocks; tile += gridDim.x)
+      scatter_tile(kin, vin, kout, vout, n, pass, nblocks, tile, hist, totals, sm);
+    grid.sync();
+    uint32_t* t = kin; kin = kout; kout = t;
+    vin = vout;
+    vout = vother;
+    vother = vin;
   }
 }
 
@@ -591,11 +644,38 @@ b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint3
                     uint32_t* vals_b, uint32_t* hist, cudaStream_t s, uint32_t** sorted_keys,
                     uint32_t** sorted_vals) {
   uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
+  uint32_t* totals = hist + static_cast<size_t>(256) * p.nblocks;
+  // one cooperative launch when the device can hold the grid, else three launches per pass
+  static thread_local int coop_dev = -1, coop_blocks = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != coop_dev) {
+    int supported = 0, per_sm = 0;
+    cudaDeviceGetAttribute(&supported, cudaDevAttrCooperativeLaunch, dev);
+    if (supported && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, radix_sort_fused_kernel, kSortThreads, 0) == cudaSuccess)
+      coop_blocks = per_sm * sm_count_current_device();
+    else
+      coop_blocks = 0;
+    cudaGetLastError();
+    coop_dev = dev;
+  }
+  bool fused = false;
+  if (coop_blocks > 0) {
+    int grid = p.nblocks > 256 ? p.nblocks : 256;
+    if (grid > coop_blocks) grid = coop_blocks;
+    int64_t n = p.n;
+    int passes = p.passes, nblocks = p.nblocks;
+    void* args[] = {&keys_a, &keys_b, &vals_a, &vals_b, &n, &passes, &nblocks, &hist, &totals};
+    fused = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(radix_sort_fused_kernel), dim3(grid), dim3(kSortThreads), args, 0, s) ==
+            cudaSuccess;
+    if (!fused) cudaGetLastError();
+  }
   for (int pass = 0; pass < p.passes; ++pass) {
-    radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, p.n, pass, p.nblocks, hist);
-    uint32_t* totals = hist + static_cast<size_t>(256) * p.nblocks;
-    radix_scan_rows_kernel<<<256, kSortThreads, 0, s>>>(hist, p.nblocks, totals);
-    radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist, totals);
+    if (!fused) {
+      radix_hist_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, p.n, pass, p.nblocks, hist);
+      radix_scan_rows_kernel<<<256, kSortThreads, 0, s>>>(hist, p.nblocks, totals);
+      radix_scatter_kernel<<<p.nblocks, kSortThreads, 0, s>>>(kin, vin, kout, vout, p.n, pass, p.nblocks, hist, totals);
+    }
     uint32_t* t = kin; kin = kout; kout = t;
     vin = vout;
     vout = vother;
@@ -603,7 +683,7 @@ b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint3
   }
   *sorted_keys = kin;
   *sorted_vals = vin;
-  note_launches(3 * p.passes - 1);
+  if (!fused) note_launches(3 * p.passes - 1);
   return check_launch("radix sort");
 }
 
