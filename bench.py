@@ -136,6 +136,10 @@ def run_gpu(args):
         # keep stdout to the one JSON line: at the VERSION and WARN levels NCCL prints its banner there
         if os.environ.get("NCCL_DEBUG", "VERSION").upper() in ("VERSION", "WARN"):
             os.environ["NCCL_DEBUG"] = "NONE"
+        if world == 2:
+            # two ranks: keep the all-reduce to 8 CTAs so that it runs beside the GEMMs (8 SMs are
+            # reserved for it) instead of taking a fifth of the SMs from them
+            os.environ.setdefault("NCCL_MAX_NCHANNELS", "8")
         dist.init_process_group("eccl", rank=rank, world_size=world)
         group = dist.group.WORLD
     bf = torch.bfloat16

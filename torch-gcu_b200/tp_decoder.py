@@ -192,10 +192,11 @@ class DecoderStack:
 
     def prefill(self, x, group=None, caches=None, overlap=None):
         if overlap is None:
-            # measured on B200: at tp 2 the all-reduce is a small share and the plain schedule wins
-            # (561 k vs 549 k tokens/s); at tp 8 the two-microbatch schedule gives 1.40 M vs 1.14 M
+            # measured on B200: tp 8 1.40 M tokens/s against 1.14 M for the plain schedule, tp 4 900 k against
+            # 835 k; at tp 2 it only pays when the collective is kept to a few SMs (8 channels, 8 reserved
+            # SMs: 583 k against 565 k), because its CTAs otherwise take as much from the GEMMs as they hide
             import os
-            overlap = os.environ.get("TP_DECODER_OVERLAP", "1" if self.tp >= 4 else "0") != "0"
+            overlap = os.environ.get("TP_DECODER_OVERLAP", "1") != "0"
         if self.tp > 1 and overlap and self.layers[0].backend == "gcu" and x.shape[0] % 2 == 0:
             return self._prefill_two_microbatches(x, group, caches)
         for i, layer in enumerate(self.layers):
@@ -209,7 +210,7 @@ class DecoderStack:
         import os
         import torch.distributed as dist
         # the collective's CTAs need SMs of their own next to the persistent GEMM kernels
-        reserve = int(os.environ.get("TP_DECODER_COMM_SMS", "32"))
+        reserve = int(os.environ.get("TP_DECODER_COMM_SMS", "8" if self.tp == 2 else "32"))
         before = torch.gcu.get_reserved_sms()
         torch.gcu.set_reserved_sms(reserve)
         try:
