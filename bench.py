@@ -217,6 +217,10 @@ def run_gpu(args):
     downloaded = [None, None]   # event: the result of the pass of slot i has reached the host
 
     def upload(slot):
+        # rank 0 reads the host buffer (on the copy stream, under the previous step); the other ranks
+        # get the input over NVLink, see the broadcast in the loop
+        if rank != 0:
+            return
         with torch.gcu.stream(s_in):
             if consumed[slot] is not None:
                 s_in.wait_event(consumed[slot])
@@ -230,7 +234,12 @@ def run_gpu(args):
             slot = i & 1
             if i + 1 < n:
                 upload(slot ^ 1)
-            cur.wait_event(uploaded[slot])
+            if rank == 0:
+                cur.wait_event(uploaded[slot])
+            if world > 1:
+                # one broadcast instead of every rank pulling the same bytes through the host's memory; it is
+                # issued on the compute stream, so it never runs beside the step's own collectives
+                dist.broadcast(x_dev[slot], src=0)
             if use_graph:
                 if downloaded[slot] is not None:
                     cur.wait_event(downloaded[slot])   # the replay overwrites the slot's output buffer
@@ -242,7 +251,8 @@ def run_gpu(args):
             consumed[slot] = cur.record_event()
             with torch.gcu.stream(s_out):
                 s_out.wait_event(consumed[slot])
-                out_host.copy_(y, non_blocking=True)
+                if rank == 0:   # the result is replicated: the job reads it once
+                    out_host.copy_(y, non_blocking=True)
                 downloaded[slot] = s_out.record_event()
         cur.wait_stream(s_out)
 
