@@ -344,6 +344,21 @@ b200Status b200_layer_norm_backward(const b200Tensor* dx, const b200Tensor* dwei
                                     const b200Tensor* rstd, const b200Tensor* weight, int64_t M, int64_t N,
                                     void* workspace, size_t workspace_bytes, b200Stream stream);
 
+/* Log-softmax along `dim` and its backward (grad_in = grad_out - exp(output) * sum(grad_out));
+ * negative log-likelihood over (N, C) log-probabilities with int64 targets, optional
+ * class weights, ignore_index, reduction 0 none / 1 mean / 2 sum, and its backward
+ * (reference yaml rows _log_softmax.out, _log_softmax_backward_data.out,
+ * nll_loss_forward.output, nll_loss_backward.grad_input). Contiguous operands.        */
+b200Status b200_log_softmax(const b200Tensor* out, const b200Tensor* in, int64_t dim, b200Stream stream);
+b200Status b200_log_softmax_backward(const b200Tensor* grad_in, const b200Tensor* grad_out,
+                                     const b200Tensor* output, int64_t dim, b200Stream stream);
+b200Status b200_nll_loss(const b200Tensor* out, const b200Tensor* total_weight, const b200Tensor* logp,
+                         const b200Tensor* target, const b200Tensor* weight, int32_t reduction,
+                         int64_t ignore_index, b200Stream stream);
+b200Status b200_nll_loss_backward(const b200Tensor* grad_in, const b200Tensor* grad_out,
+                                  const b200Tensor* target, const b200Tensor* weight,
+                                  const b200Tensor* total_weight, int32_t reduction, int64_t ignore_index,
+                                  b200Stream stream);
 /* Flash-attention backward (reference: aot_ops/gcu_attention.cpp:135-203
  * topsatenScaledDotProductFlashAttentionBackward). dq (B,Hq,Sq,D), dk / dv
  * (B,Hkv,Sk,D) from dout, q, k, v, the forward's out and logsumexp; D = 128,

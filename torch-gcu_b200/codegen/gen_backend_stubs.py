@@ -118,6 +118,8 @@ def gen_structured(f, g, row, ns):
         # the structured API spells optional scalars as a non-owning reference
         if "optional<at::Scalar>" in str(a.type):
             return "(%s.has_value() ? at::OptionalScalarRef(&(%s.value())) : at::OptionalScalarRef())" % (a.name, a.name)
+        if "optional<at::Tensor>" in str(a.type) and "List" not in str(a.type):
+            return "((%s.has_value() && %s->defined()) ? at::OptionalTensorRef(*%s) : at::OptionalTensorRef())" % (a.name, a.name, a.name)
         return a.name
     meta_call = ", ".join(meta_arg(a) for a in in_args)
     inherits_iter = g.out.structured_inherits is not None

@@ -106,3 +106,73 @@ at::Tensor embedding_dense_backward(const at::Tensor& grad_output, const at::Ten
 
 }  // namespace aotops
 }  // namespace torch_gcu
+
+// ------------------------------------------------- log-softmax and NLL loss --
+namespace torch_gcu {
+namespace aotops {
+
+void _log_softmax_out(const at::Tensor& self, int64_t dim, bool half_to_float, const at::Tensor& out) {
+  if (out.numel() == 0) return;
+  at::Tensor in = (half_to_float ? self.to(at::kFloat) : self).contiguous();
+  at::Tensor work = (out.is_contiguous() && out.scalar_type() == in.scalar_type()) ? out : at::empty(out.sizes(), in.options());
+  b200Tensor vo = to_b200(work), vi = to_b200(in);
+  cudaStream_t stream = current_stream(out);
+  GCU_KERNEL_CALL(b200_log_softmax, stream, &vo, &vi, at::maybe_wrap_dim(dim, self.dim()));
+  if (!work.is_same(out)) out.copy_(work);
+}
+
+void _log_softmax_backward_data_out(const at::Tensor& grad_output, const at::Tensor& output, int64_t dim, at::ScalarType,
+                                    const at::Tensor& out) {
+  if (out.numel() == 0) return;
+  const at::ScalarType math = grad_output.scalar_type();
+  at::Tensor g = grad_output.contiguous();
+  at::Tensor y = (output.scalar_type() == math ? output : output.to(math)).contiguous();
+  at::Tensor work = (out.is_contiguous() && out.scalar_type() == math) ? out : at::empty(out.sizes(), g.options());
+  b200Tensor vo = to_b200(work), vg = to_b200(g), vy = to_b200(y);
+  cudaStream_t stream = current_stream(out);
+  GCU_KERNEL_CALL(b200_log_softmax_backward, stream, &vo, &vg, &vy, at::maybe_wrap_dim(dim, grad_output.dim()));
+  if (!work.is_same(out)) out.copy_(work);
+}
+
+void nll_loss_forward_output(const at::Tensor& self, const at::Tensor& target, const std::optional<at::Tensor>& weight_opt,
+                             int64_t reduction, int64_t ignore_index, const at::Tensor& output, const at::Tensor& total_weight) {
+  // ATen's reduction codes: 0 none, 1 mean, 2 sum
+  at::Tensor x = (self.dim() == 1 ? self.unsqueeze(0) : self).contiguous();
+  at::Tensor t = (target.dim() == 0 ? target.unsqueeze(0) : target).to(at::kLong).contiguous();
+  at::Tensor w;
+  if (weight_opt.has_value() && weight_opt->defined()) w = weight_opt->to(x.scalar_type()).contiguous();
+  if (x.size(0) == 0) {
+    if (reduction != 0) output.fill_(reduction == 1 ? std::numeric_limits<double>::quiet_NaN() : 0.0);
+    total_weight.zero_();
+    return;
+  }
+  at::Tensor out_work = output.is_contiguous() ? output : at::empty(output.sizes(), output.options());
+  b200Tensor vo = to_b200(out_work), vt = to_b200(total_weight), vx = to_b200(x), vtg = to_b200(t), vw;
+  if (w.defined()) vw = to_b200(w);
+  cudaStream_t stream = current_stream(self);
+  GCU_KERNEL_CALL(b200_nll_loss, stream, &vo, &vt, &vx, &vtg, w.defined() ? &vw : static_cast<const b200Tensor*>(nullptr),
+                  static_cast<int32_t>(reduction), ignore_index);
+  if (!out_work.is_same(output)) output.copy_(out_work);
+}
+
+void nll_loss_backward_grad_input(const at::Tensor& grad_output, const at::Tensor& self, const at::Tensor& target,
+                                  const std::optional<at::Tensor>& weight_opt, int64_t reduction, int64_t ignore_index,
+                                  const at::Tensor& total_weight, const at::Tensor& grad_input) {
+  if (grad_input.numel() == 0) return;
+  at::Tensor gi = grad_input.is_contiguous() ? grad_input : at::empty(grad_input.sizes(), grad_input.options());
+  at::Tensor gi2 = gi.dim() == 1 ? gi.unsqueeze(0) : gi;
+  at::Tensor t = (target.dim() == 0 ? target.unsqueeze(0) : target).to(at::kLong).contiguous();
+  at::Tensor go = grad_output.to(gi.scalar_type()).contiguous();
+  at::Tensor tw = total_weight.to(gi.scalar_type()).contiguous();
+  at::Tensor w;
+  if (weight_opt.has_value() && weight_opt->defined()) w = weight_opt->to(gi.scalar_type()).contiguous();
+  b200Tensor vgi = to_b200(gi2), vgo = to_b200(go), vtg = to_b200(t), vtw = to_b200(tw), vw;
+  if (w.defined()) vw = to_b200(w);
+  cudaStream_t stream = current_stream(self);
+  GCU_KERNEL_CALL(b200_nll_loss_backward, stream, &vgi, &vgo, &vtg, w.defined() ? &vw : static_cast<const b200Tensor*>(nullptr), &vtw,
+                  static_cast<int32_t>(reduction), ignore_index);
+  if (!gi.is_same(grad_input)) grad_input.copy_(gi);
+}
+
+}  // namespace aotops
+}  // namespace torch_gcu
