@@ -96,8 +96,7 @@ class DecoderLayer:
         h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
         qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
-        eff.rope(q, cos, sin, None, True)
-        eff.rope(k, cos, sin, None, True)
+        eff.rope(qkv[:, :, :hq + hk], cos, sin, None, True)   # q and k heads are neighbours in the fused projection: one launch
         if kv_out is not None:
             kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
             kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
@@ -158,8 +157,7 @@ class DecoderLayer:
         qkv = torch.mm(h.view(B, H), w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
         positions = self._positions(B, pos)
-        eff.rope(q, cos, sin, positions, True)
-        eff.rope(k, cos, sin, positions, True)
+        eff.rope(qkv[:, :, :hq + hk], cos, sin, positions, True)
         kv[0][:, :, pos:pos + 1].copy_(k.transpose(1, 2))   # strided device copy into the cache slice
         kv[1][:, :, pos:pos + 1].copy_(v.transpose(1, 2))
         att, _ = eff.sdpa_flash(q.transpose(1, 2), kv[0][:, :, :pos + 1], kv[1][:, :, :pos + 1], False)
