@@ -392,16 +392,24 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         tmem_ld_32x32(tmem_base + lane_sel + kS + c, s);
         tmem_ld_32x32(tmem_base + lane_sel + kDP + c, dp);
         tmem_wait_ld();
+        // the 32 queries' statistics of this chunk: 16-byte shared-memory loads (all threads read the same words)
+        float ls[32], dl[32];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(stat + c + i);
+          const float4 d4 = *reinterpret_cast<const float4*>(stat + BT + c + i);
+          ls[i] = a.x; ls[i + 1] = a.y; ls[i + 2] = a.z; ls[i + 3] = a.w;
+          dl[i] = d4.x; dl[i + 1] = d4.y; dl[i + 2] = d4.z; dl[i + 3] = d4.w;
+        }
         uint32_t pt[16], ds[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), p.scale_log2, -stat[c + i]));
-          float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -stat[c + i + 1]));
+          float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), p.scale_log2, -ls[i]));
+          float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -ls[i + 1]));
           if (c + i < first_vis) p0 = 0.f;
           if (c + i + 1 < first_vis) p1 = 0.f;
           pt[i / 2] = pack2<BF16>(p0, p1);
-          ds[i / 2] = pack2<BF16>(p0 * (__uint_as_float(dp[i]) - stat[BT + c + i]) * p.scale,
-                                  p1 * (__uint_as_float(dp[i + 1]) - stat[BT + c + i + 1]) * p.scale);
+          ds[i / 2] = pack2<BF16>(p0 * (__uint_as_float(dp[i]) - dl[i]) * p.scale, p1 * (__uint_as_float(dp[i + 1]) - dl[i + 1]) * p.scale);
         }
         tmem_st_32x16(tmem_base + lane_sel + kS + c / 2, pt);
         tmem_st_32x16(tmem_base + lane_sel + kDP + c / 2, ds);
