@@ -254,10 +254,12 @@ attention_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 }
 
 // ------------------------------------------------------------------ dK, dV ----
+// 10 warps: TMA, MMA, and two groups of four pointwise warps that split the 64 query columns of a half tile
+constexpr int kThreadsDkv = 320;
 constexpr int kSmemDkv = 2 * kTileBytes + 2 * 2 * kTileBytes + 2 * 2 * BT * 4 + 1024 + 256;   // K, V, 2 x (Q, dO), 2 x (lse, delta)
 
 template <bool BF16>
-__global__ void __launch_bounds__(kThreadsBwd, 1)
+__global__ void __launch_bounds__(kThreadsDkv, 1)
 attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                          const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                          const BwdParams p) {
@@ -271,10 +273,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint64_t* kv_full = bars;
   uint64_t* qdo_full = bars + 1;      // [2]
   uint64_t* qdo_empty = bars + 3;     // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_full = bars + 5;      // [2]: S^T / dP^T of a half tile are in tensor-memory buffer i
+  uint64_t* pds_full = bars + 7;      // [2]: P^T / dS^T written back into buffer i (4 warps)
+  uint64_t* acc_done = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -288,8 +290,7 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&qdo_full[i], 1); mbar_init(&qdo_empty[i], 1); }
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    for (int i = 0; i < 2; ++i) { mbar_init(&sdp_full[i], 1); mbar_init(&pds_full[i], 8); }
     mbar_init(acc_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -299,7 +300,10 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kS = 0, kDP = 128, kDV = 256, kDK = 384;
+  // a query tile is worked in two halves of 64 queries; half-iteration h uses buffer h & 1:
+  // S^T at kBuf*(h&1), dP^T 64 columns further; P^T / dS^T packed over their first 32 columns
+  constexpr uint32_t kBuf = 128, kDPoff = 64, kDV = 256, kDK = 384;
+  constexpr int HQ = BT / 2;                      // queries per half iteration
 
   if (warp == 0) {
     if (lane == 0 && n_it > 0) {
@@ -326,79 +330,107 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     }
   } else if (warp == 1) {
     if (lane == 0 && n_it > 0) {
-      const uint32_t idesc_kk = make_idesc(BT, BT, BF16, false, false);
+      const uint32_t idesc_kk = make_idesc(BT, HQ, BF16, false, false);   // 128 keys x 64 queries
       const uint32_t idesc_acc = make_idesc(BT, D, BF16, false, true);    // A from tensor memory, B MN-major
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      const int n_half = 2 * n_it;
       bool ok = mbar_wait(kv_full, 0, abort_flag);
-      for (int it = 0; it < n_it && ok; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&qdo_full[st], (it >> 1) & 1u, abort_flag)) { ok = false; break; }
+      // S^T = K Q_half^T and dP^T = V dO_half^T of half-iteration h into buffer h & 1
+      auto issue_sdp = [&](int h) -> bool {
+        const int it = h >> 1, st = it & 1, half = h & 1;
+        if (half == 0 && !mbar_wait(&qdo_full[st], (it >> 1) & 1u, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(sQdO + st * 2 * kTileBytes), do_addr = q_addr + kTileBytes;
+        const uint32_t q_addr = smem_u32(sQdO + st * 2 * kTileBytes) + half * (HQ * 128), do_addr = q_addr + kTileBytes;
+        const uint32_t buf = tmem_base + kBuf * (h & 1);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {   // S^T = K Q^T
+        for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * (BT * 128) + (kk % 4) * 32;
-          umma_f16(tmem_base + kS, smem_desc_sw128(k_addr + off, 16u, 1024u), smem_desc_sw128(q_addr + off, 16u, 1024u),
-                   idesc_kk, kk != 0 ? 1u : 0u);
+          umma_f16(buf, smem_desc_sw128(k_addr + off, 16u, 1024u), smem_desc_sw128(q_addr + off, 16u, 1024u), idesc_kk,
+                   kk != 0 ? 1u : 0u);
         }
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {   // dP^T = V dO^T
+        for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * (BT * 128) + (kk % 4) * 32;
-          umma_f16(tmem_base + kDP, smem_desc_sw128(v_addr + off, 16u, 1024u), smem_desc_sw128(do_addr + off, 16u, 1024u),
-                   idesc_kk, kk != 0 ? 1u : 0u);
+          umma_f16(buf + kDPoff, smem_desc_sw128(v_addr + off, 16u, 1024u), smem_desc_sw128(do_addr + off, 16u, 1024u), idesc_kk,
+                   kk != 0 ? 1u : 0u);
         }
-        umma_commit(sdp_full);
-        if (!mbar_wait(pds_full, it & 1u, abort_flag)) { ok = false; break; }
+        umma_commit(&sdp_full[h & 1]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int h = 0; h < n_half && ok; ++h) {
+        // the next half's products run while the pointwise stage works on this one; its buffer was
+        // read by the accumulating MMAs of half h-1, which were issued before (in-order execution)
+        if (h + 1 < n_half && !issue_sdp(h + 1)) { ok = false; break; }
+        if (!mbar_wait(&pds_full[h & 1], (h >> 1) & 1u, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        const int it = h >> 1, st = it & 1, half = h & 1;
+        const uint32_t q_addr = smem_u32(sQdO + st * 2 * kTileBytes) + half * (HQ * 128), do_addr = q_addr + kTileBytes;
+        const uint32_t buf = tmem_base + kBuf * (h & 1);
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (queries are the K dimension)
-          umma_f16_ts(tmem_base + kDV, tmem_base + kS + kk * 8, smem_desc_sw128(do_addr + kk * 2048, BT * 128, 1024u), idesc_acc,
-                      (it | kk) != 0 ? 1u : 0u);
-          umma_f16_ts(tmem_base + kDK, tmem_base + kDP + kk * 8, smem_desc_sw128(q_addr + kk * 2048, BT * 128, 1024u), idesc_acc,
-                      (it | kk) != 0 ? 1u : 0u);
+        for (int kk = 0; kk < HQ / 16; ++kk) {  // dV += P^T dO ; dK += dS^T Q   (the 64 queries are the K dimension)
+          umma_f16_ts(tmem_base + kDV, buf + kk * 8, smem_desc_sw128(do_addr + kk * 2048, BT * 128, 1024u), idesc_acc,
+                      (h | kk) != 0 ? 1u : 0u);
+          umma_f16_ts(tmem_base + kDK, buf + kDPoff + kk * 8, smem_desc_sw128(q_addr + kk * 2048, BT * 128, 1024u), idesc_acc,
+                      (h | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[st]);
+        if (half == 1) umma_commit(&qdo_empty[st]);
       }
       if (ok) umma_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3;
+    const int colgroup = (warp - 2) >> 2;            // which 32 query columns of a half tile this warp takes
     const int tid = quarter * 32 + lane;             // key row of the tile
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const int key = k0 + tid;
     const bool key_valid = key < p.Sk;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int st = it & 1;
+    float next_lse = CUDART_INF_F, next_delta = 0.f;
+    auto load_stats = [&](int it_) {
+      const int g_ = it_ / n_q, qi = (q_first + (it_ - g_ * n_q)) * BT + tid;
+      const bool qv = qi < p.Sq;
+      const int64_t off = (static_cast<int64_t>(b) * p.Hq + hkv * G + g_) * p.Sq + qi;
+      next_lse = qv ? p.lse[off] * kLog2e : CUDART_INF_F;
+      next_delta = qv ? p.delta[off] : 0.f;
+    };
+    if (colgroup == 0 && n_it > 0) load_stats(0);
+    for (int h = 0; h < 2 * n_it && ok; ++h) {
+      const int it = h >> 1, st = it & 1, half = h & 1;
       const int g = it / n_q, qt = q_first + (it - g * n_q);
       const int q0 = qt * BT;
-      // statistics of this query tile, one per thread, shared through smem
       float* stat = sStat + st * 2 * BT;
-      {
-        const int qi = q0 + tid;
-        const bool qv = qi < p.Sq;
-        const int64_t off = (static_cast<int64_t>(b) * p.Hq + hkv * G + g) * p.Sq + qi;
-        stat[tid] = qv ? p.lse[off] * kLog2e : CUDART_INF_F;
-        stat[BT + tid] = qv ? p.delta[off] : 0.f;
+      if (half == 0) {
+        // statistics of this query tile (fetched one tile ahead into registers), one per row thread of
+        // group 0, shared through smem
+        if (colgroup == 0) {
+          stat[tid] = next_lse;
+          stat[BT + tid] = next_delta;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      } else if (colgroup == 0 && it + 1 < n_it) {
+        load_stats(it + 1);   // in flight while this half and the next tile's first products run
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (!mbar_wait(sdp_full, it & 1u, abort_flag)) { ok = false; break; }
+      if (!mbar_wait(&sdp_full[h & 1], (h >> 1) & 1u, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      // query column q is visible to this key when q0 + q >= key (causal) and the key exists
+      const uint32_t buf = tmem_base + lane_sel + kBuf * (h & 1);
+      const int qbase = half * HQ;                       // first query of this half inside the tile
+      // query column q (of the tile) is visible to this key when q0 + q >= key (causal) and the key exists
       const int first_vis = !key_valid ? BT : (p.causal ? max(0, key - q0) : 0);
-#pragma unroll 1
-      for (int c = 0; c < BT; c += 32) {
+      {
+        const int c = colgroup * 32;
         uint32_t s[32], dp[32];
-        tmem_ld_32x32(tmem_base + lane_sel + kS + c, s);
-        tmem_ld_32x32(tmem_base + lane_sel + kDP + c, dp);
+        tmem_ld_32x32(buf + c, s);
+        tmem_ld_32x32(buf + kDPoff + c, dp);
         tmem_wait_ld();
-        // the 32 queries' statistics of this chunk: 16-byte shared-memory loads (all threads read the same words)
+        // the packed results of one group land on columns the other group reads: everyone has loaded first
+        asm volatile("bar.sync 2, 256;" ::: "memory");
         float ls[32], dl[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 4) {
-          const float4 a = *reinterpret_cast<const float4*>(stat + c + i);
-          const float4 d4 = *reinterpret_cast<const float4*>(stat + BT + c + i);
-          ls[i] = a.x; ls[i + 1] = a.y; ls[i + 2] = a.z; ls[i + 3] = a.w;
+          const float4 a4 = *reinterpret_cast<const float4*>(stat + qbase + c + i);
+          const float4 d4 = *reinterpret_cast<const float4*>(stat + BT + qbase + c + i);
+          ls[i] = a4.x; ls[i + 1] = a4.y; ls[i + 2] = a4.z; ls[i + 3] = a4.w;
           dl[i] = d4.x; dl[i + 1] = d4.y; dl[i + 2] = d4.z; dl[i + 3] = d4.w;
         }
         uint32_t pt[16], ds[16];
@@ -406,28 +438,29 @@ attention_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         for (int i = 0; i < 32; i += 2) {
           float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), p.scale_log2, -ls[i]));
           float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, -ls[i + 1]));
-          if (c + i < first_vis) p0 = 0.f;
-          if (c + i + 1 < first_vis) p1 = 0.f;
+          if (qbase + c + i < first_vis) p0 = 0.f;
+          if (qbase + c + i + 1 < first_vis) p1 = 0.f;
           pt[i / 2] = pack2<BF16>(p0, p1);
           ds[i / 2] = pack2<BF16>(p0 * (__uint_as_float(dp[i]) - dl[i]) * p.scale, p1 * (__uint_as_float(dp[i + 1]) - dl[i + 1]) * p.scale);
         }
-        tmem_st_32x16(tmem_base + lane_sel + kS + c / 2, pt);
-        tmem_st_32x16(tmem_base + lane_sel + kDP + c / 2, ds);
+        // packed results over the first half of each region: columns c/2 .. c/2+15, always behind the reads
+        tmem_st_32x16(buf + c / 2, pt);
+        tmem_st_32x16(buf + kDPoff + c / 2, ds);
       }
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
+      if (lane == 0) mbar_arrive(&pds_full[h & 1]);
     }
     if (ok && n_it > 0) ok = mbar_wait(acc_done, 0, abort_flag);
     if (n_it == 0 || ok) {
       tc_fence_after();
       uint16_t* dkr = static_cast<uint16_t*>(p.dk) + b * p.dk_sb + static_cast<int64_t>(hkv) * p.dk_sh + static_cast<int64_t>(key) * p.dk_ss;
       uint16_t* dvr = static_cast<uint16_t*>(p.dv) + b * p.dv_sb + static_cast<int64_t>(hkv) * p.dv_sh + static_cast<int64_t>(key) * p.dv_ss;
-      if (n_it > 0) {
-        store_acc_row<BF16>(tmem_base + lane_sel + kDV, dvr, key_valid);
-        store_acc_row<BF16>(tmem_base + lane_sel + kDK, dkr, key_valid);
-      } else if (key_valid) {   // no query sees these keys: zero gradient
+      if (n_it > 0) {   // one group stores dV, the other dK
+        if (colgroup == 0) store_acc_row<BF16>(tmem_base + lane_sel + kDV, dvr, key_valid);
+        else store_acc_row<BF16>(tmem_base + lane_sel + kDK, dkr, key_valid);
+      } else if (key_valid && colgroup == 0) {   // no query sees these keys: zero gradient
         for (int c = 0; c < D; ++c) { dkr[c] = 0; dvr[c] = 0; }
       }
     }
@@ -533,10 +566,10 @@ b200Status b200_sdpa_flash_bwd(const b200Tensor* dq, const b200Tensor* dk, const
   const dim3 gq((p.Sq + BT - 1) / BT, p.Hq, p.B), gk((p.Sk + BT - 1) / BT, p.Hkv, p.B);
   if (bf) {
     attention_bwd_dq_kernel<true><<<gq, kThreadsBwd, kSmemDq, s>>>(tq, tdo, tk, tv, p);
-    attention_bwd_dkv_kernel<true><<<gk, kThreadsBwd, kSmemDkv, s>>>(tq, tdo, tk, tv, p);
+    attention_bwd_dkv_kernel<true><<<gk, kThreadsDkv, kSmemDkv, s>>>(tq, tdo, tk, tv, p);
   } else {
     attention_bwd_dq_kernel<false><<<gq, kThreadsBwd, kSmemDq, s>>>(tq, tdo, tk, tv, p);
-    attention_bwd_dkv_kernel<false><<<gk, kThreadsBwd, kSmemDkv, s>>>(tq, tdo, tk, tv, p);
+    attention_bwd_dkv_kernel<false><<<gk, kThreadsDkv, kSmemDkv, s>>>(tq, tdo, tk, tv, p);
   }
   note_launches(2);
   return check_launch(name);
