@@ -281,6 +281,14 @@ b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200
  * No reference counterpart: the reference runs mm followed by pointwise ops.     */
 b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up,
                           b200Stream stream);
+/* Fused qkv projection with the rotary embedding in the GEMM epilogue:
+ *   out (M,N) = a @ w^T, then rotate-half RoPE (the convention of b200_rope) on the first
+ *   rope_cols columns, taken as heads of 128; row m has position m % seq_len.
+ * a (M,K), w (N,K) bf16 / f16 with K contiguous; cos / sin f32 (positions, 64). The rotation
+ * acts on the fp32 accumulators, one rounding. No reference counterpart.                 */
+b200Status b200_mm_rope(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w,
+                        const b200Tensor* cos_table, const b200Tensor* sin_table, int64_t seq_len,
+                        int64_t rope_cols, b200Stream stream);
 
 /* ---- comparison, selection, clamping, extremes, generators ------------------
  * The operators model code needs around the hot path (masks, sampling, position

@@ -174,6 +174,15 @@ def test_fused_efficient_ops(dev):
         gu = xin.float() @ wgu.float().t()
         ref = torch.nn.functional.silu(gu[..., :384]) * gu[..., 384:]
         assert ls.shape == ref.shape and torch.allclose(ls.cpu().float(), ref, rtol=3e-2, atol=3e-2)
+    xr = torch.randn(2, 300, 256, generator=g).to(torch.bfloat16)
+    wr = (torch.randn(5 * 128, 256, generator=g) * 0.06).to(torch.bfloat16)
+    cr, sr = efficient.rope_tables(300, 128, device="cpu")
+    for xin in (xr, xr[:, :7]):   # GEMM with the rotation in its epilogue (>= 512 rows), and mm followed by the rope kernel
+        lr = efficient.linear_rope(xin.to(dev), wr.to(dev), cr.to(dev), sr.to(dev), 4)
+        y = (xin.float() @ wr.float().t()).view(2, -1, 5, 128)
+        ref = y.clone()
+        ref[:, :, :4] = aten_cpu.rope(y[:, :, :4].contiguous(), cr, sr).float()
+        assert lr.shape == ref.shape and torch.allclose(lr.cpu().float(), ref, rtol=3e-2, atol=3e-2)
     s2 = efficient.swiglu_packed(torch.cat([gate, up], -1).to(dev))
     assert torch.equal(s2.cpu(), s.cpu())
 

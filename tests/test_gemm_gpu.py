@@ -229,3 +229,27 @@ def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):
     two = torch.empty_like(out)
     ops.swiglu(two, gu_dev[:, :F], gu_dev[:, F:])
     close(out, two.cpu(), 3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("B,S,K,heads,rope_heads,dtype", [(2, 512, 256, 6, 5, BF), (1, 600, 136, 3, 2, torch.float16),
+                                                          (4, 300, 512, 8, 8, BF), (2, 256, 128, 4, 0, BF)])
+def test_mm_rope_fused_epilogue(ops, B, S, K, heads, rope_heads, dtype):
+    """qkv projection with rotate-half RoPE applied to the first heads in the GEMM epilogue, against fp32
+    CPU arithmetic; heads past rope_heads (the v part) come out unrotated."""
+    g = torch.Generator().manual_seed(56)
+    N = heads * 128
+    a = torch.randn(B * S, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) * (1.0 / K ** 0.5)).to(dtype)
+    import workloads
+    cos, sin = workloads.rope_tables(S + 7, 128)
+    out = torch.empty(B * S, N, dtype=dtype, device=DEV)
+    ops.mm_rope(out, dev(a), dev(w), dev(cos), dev(sin), S, rope_heads * 128)
+    assert ops.device_error_fetch() == 0
+    y = (a.float() @ w.float().t()).view(B, S, heads, 128)
+    pos = torch.arange(S)
+    c = torch.cat((cos[pos], cos[pos]), -1)[None, :, None, :]
+    s_ = torch.cat((sin[pos], sin[pos]), -1)[None, :, None, :]
+    rot = torch.cat((-y[..., 64:], y[..., :64]), -1)
+    ref = y.clone()
+    ref[:, :, :rope_heads] = (y * c + rot * s_)[:, :, :rope_heads]
+    close(out.view(B, S, heads, 128), ref.to(dtype), 1.6e-2, 1e-2 * max(1.0, (K / 64) ** 0.5))

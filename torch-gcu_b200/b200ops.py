@@ -292,6 +292,12 @@ def mm_swiglu(out, a, w_gate_up, stream=None):
     check(lib().b200_mm_swiglu(_ref(view(out)), _ref(view(a)), _ref(view(w_gate_up)), _stream(stream)))
 
 
+def mm_rope(out, a, w, cos_table, sin_table, seq_len, rope_cols, stream=None):
+    """out (M,N) = a @ w.T with rotate-half RoPE on the first rope_cols columns (heads of 128), in the GEMM epilogue."""
+    check(lib().b200_mm_rope(_ref(view(out)), _ref(view(a)), _ref(view(w)), _ref(view(cos_table)), _ref(view(sin_table)),
+                             ctypes.c_int64(seq_len), ctypes.c_int64(rope_cols), _stream(stream)))
+
+
 def mm(out, a, b, stream=None):
     check(lib().b200_mm(_ref(view(out)), _ref(view(a)), _ref(view(b)), _stream(stream)))
 

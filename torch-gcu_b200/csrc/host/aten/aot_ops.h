@@ -17,6 +17,7 @@ at::Tensor rope(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& si
 at::Tensor swiglu(const at::Tensor& gate, const at::Tensor& up);
 at::Tensor swiglu_packed(const at::Tensor& gate_up);
 at::Tensor linear_swiglu(const at::Tensor& x, const at::Tensor& w_gate_up);
+at::Tensor linear_rope(const at::Tensor& x, const at::Tensor& w, const at::Tensor& cos, const at::Tensor& sin, int64_t rope_heads);
 at::Tensor int32_indices_index(const at::Tensor& self, const c10::List<std::optional<at::Tensor>>& indices);
 // (out, logsumexp) of the flash kernel for q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D)
 std::tuple<at::Tensor, at::Tensor> sdpa_flash(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,

@@ -194,6 +194,32 @@ at::Tensor linear_swiglu(const at::Tensor& x, const at::Tensor& w_gate_up) {
   return out.view(shape);
 }
 
+// x (B, S, K) times a fused qkv weight (N, K), RoPE (heads of 128, position = index along S) on the first
+// rope_heads heads: one GEMM whose epilogue rotates; small or odd problems run mm followed by the rope kernel.
+at::Tensor linear_rope(const at::Tensor& x, const at::Tensor& w, const at::Tensor& cos, const at::Tensor& sin, int64_t rope_heads) {
+  TORCH_CHECK(x.dim() == 3 && w.dim() == 2 && w.size(1) == x.size(2) && w.size(0) % 128 == 0,
+              "linear_rope: x (B, S, K) and w (heads * 128, K) expected");
+  TORCH_CHECK(x.scalar_type() == w.scalar_type(), "linear_rope: x and w must share a dtype");
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat && cos.dim() == 2 && cos.size(1) == 64 &&
+              cos.sizes() == sin.sizes() && cos.size(0) >= x.size(1), "linear_rope: cos / sin must be float32 (positions >= S, 64)");
+  const int64_t B = x.size(0), S = x.size(1), K = x.size(2), N = w.size(0), heads = N / 128;
+  TORCH_CHECK(rope_heads >= 0 && rope_heads <= heads, "linear_rope: rope_heads out of range");
+  at::Tensor x2 = x.contiguous().view({B * S, K});
+  const bool fused = B * S >= 512 && (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf) && K % 8 == 0;
+  if (!fused) {
+    at::Tensor out = at::mm(x2, w.t()).view({B, S, heads, 128});
+    if (rope_heads > 0) rope(out.narrow(2, 0, rope_heads), cos, sin, std::nullopt, true);
+    return out;
+  }
+  at::Tensor wc = w.contiguous(), c = cos.contiguous(), s = sin.contiguous();
+  at::Tensor out = at::empty({B * S, N}, x.options());
+  const c10::OptionalDeviceGuard guard(x.device());
+  cudaStream_t stream = current_stream(x);
+  b200Tensor vo = to_b200(out), va = to_b200(x2), vw = to_b200(wc), vc = to_b200(c), vs = to_b200(s);
+  GCU_KERNEL_CALL(b200_mm_rope, stream, &vo, &va, &vw, &vc, &vs, S, rope_heads * 128);
+  return out.view({B, S, heads, 128});
+}
+
 // ------------------------------------------------------ SDPA backend choice --
 // flash (reported as "overrideable", the slot PyTorch gives PrivateUse1 backends)
 // when the kernel can take the problem, otherwise the math composite

@@ -146,6 +146,7 @@ PYBIND11_MODULE(_C, m) {
   m.def("_swiglu", &aotops::swiglu);
   m.def("_swiglu_packed", &aotops::swiglu_packed);
   m.def("_linear_swiglu", &aotops::linear_swiglu);
+  m.def("_linear_rope", &aotops::linear_rope);
   m.def("_sdpa_flash", &aotops::sdpa_flash, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("is_causal"),
         py::arg("scale") = py::none());
 

@@ -83,6 +83,11 @@ struct GemmParams {
   unsigned int* error_word;
   int up_offset;                 // fused SwiGLU: row of B where the "up" half starts (= output columns F)
   int group_m;                   // row-tiles per band of the tile walk
+  // fused RoPE epilogue: rotate-half over 128-wide heads of the first rope_cols output columns;
+  // f32 (positions, 64) tables, position of row m = m % rope_seq
+  const float* rope_cos;
+  const float* rope_sin;
+  int rope_seq, rope_cols;
 };
 
 template <int BN> struct GemmCfg {
@@ -413,10 +418,14 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // hold gate and [128,256) up for the same 128 output columns, and the epilogue
 // stores silu(gate) * up (computed on the fp32 accumulators): the 2F-wide
 // intermediate never exists in memory. p.N is F here.
-template <bool SWIGLU>
+// EPI 2 (RoPE): output columns below p.rope_cols are heads of 128 (a 256-wide tile holds two) and get the
+// rotate-half rotary embedding applied to the fp32 accumulators before the one rounding; the rest are stored
+// as they are (the v part of a fused qkv projection).
+template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const GemmParams p) {
+  constexpr bool SWIGLU = EPI == 1, ROPE = EPI == 2;
   constexpr int BNO = SWIGLU ? BN2 / 2 : BN2;   // output columns per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -578,6 +587,57 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             }
           }
         }
+      } else if (ROPE && tn * BN2 < p.rope_cols) {
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(ab * BN2);
+        const int pos = row_ok ? row % p.rope_seq : 0;
+        const float* cs = p.rope_cos + static_cast<int64_t>(pos) * 64;
+        const float* sn = p.rope_sin + static_cast<int64_t>(pos) * 64;
+#pragma unroll 1
+        for (int hc = 0; hc < 128; hc += 32) {       // (head of the tile, 32-column chunk of its first half)
+          const int hd = hc >> 6, c = hc & 32;        // hc = 0, 32 -> head 0; 64, 96 -> head 1
+          uint32_t x1[32], x2[32];
+          tmem_ld_32x32(t_row + hd * 128 + c, x1);
+          tmem_ld_32x32(t_row + hd * 128 + c + 64, x2);
+          tmem_wait_ld();
+          const int col0 = tn * BN2 + hd * 128 + c;
+          if (row_ok && col0 < p.N) {
+            const bool rot = col0 < p.rope_cols;
+            uint32_t o1[16], o2[16];
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              float a0 = p.alpha * __uint_as_float(x1[j]), a1 = p.alpha * __uint_as_float(x1[j + 1]);
+              float b0 = p.alpha * __uint_as_float(x2[j]), b1 = p.alpha * __uint_as_float(x2[j + 1]);
+              if (rot) {
+                const float c0 = cs[c + j], c1 = cs[c + j + 1], s0 = sn[c + j], s1 = sn[c + j + 1];
+                const float r0 = a0 * c0 - b0 * s0, r1 = a1 * c1 - b1 * s1;
+                b0 = b0 * c0 + a0 * s0;
+                b1 = b1 * c1 + a1 * s1;
+                a0 = r0;
+                a1 = r1;
+              }
+              if (p.is_bf16) {
+                o1[j / 2] = f32x2_to_bf16x2_bits(a0, a1);
+                o2[j / 2] = f32x2_to_bf16x2_bits(b0, b1);
+              } else {
+                __half2 h1 = __floats2half2_rn(a0, a1), h2 = __floats2half2_rn(b0, b1);
+                o1[j / 2] = *reinterpret_cast<uint32_t*>(&h1);
+                o2[j / 2] = *reinterpret_cast<uint32_t*>(&h2);
+              }
+            }
+            if (vec_ok && col0 + 96 <= p.N) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                *reinterpret_cast<uint4*>(orow + col0 + q * 8) = make_uint4(o1[q * 4], o1[q * 4 + 1], o1[q * 4 + 2], o1[q * 4 + 3]);
+                *reinterpret_cast<uint4*>(orow + col0 + 64 + q * 8) = make_uint4(o2[q * 4], o2[q * 4 + 1], o2[q * 4 + 2], o2[q * 4 + 3]);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) orow[col0 + j] = static_cast<uint16_t>(j & 1 ? o1[j >> 1] >> 16 : o1[j >> 1] & 0xffffu);
+                if (col0 + 64 + j < p.N) orow[col0 + 64 + j] = static_cast<uint16_t>(j & 1 ? o2[j >> 1] >> 16 : o2[j >> 1] & 0xffffu);
+              }
+            }
+          }
+        }
       } else {
 #pragma unroll 1
       for (int c = 0; c < BN2; c += 32) {
@@ -622,7 +682,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
 }
 
-template <bool SWIGLU>
+template <int EPI>
 b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaStream_t s) {
   CUtensorMap ta, tb;
   const char* err = "";
@@ -632,16 +692,16 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev != last_dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
-  constexpr int bno = SWIGLU ? BN2 / 2 : BN2;
+  constexpr int bno = EPI == 1 ? BN2 / 2 : BN2;
   p.group_m = band_rows(BM2, p.K);
   const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + bno - 1) / bno) * p.batch;
   const int pairs = gemm_sm_budget() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tc2_kernel<SWIGLU><<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
+  gemm_tc2_kernel<EPI><<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
   return check_launch("matmul (tcgen05, two-CTA)");
 }
 
@@ -914,7 +974,7 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
       }
       p.error_word = device_error_word();
       B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
-      if (pair_kernel) return launch_tc2<false>(oa, ob, p, s);
+      if (pair_kernel) return launch_tc2<0>(oa, ob, p, s);
       if (skinny) return launch_splitk(oa, ob, p, splits, s);
       if (bn == 256) return launch_tc<256>(oa, ob, p, s);
       if (bn == 128) return launch_tc<128>(oa, ob, p, s);
@@ -958,7 +1018,43 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
   p.up_offset = (int)F;
   p.error_word = device_error_word();
   B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
-  return launch_tc2<true>(oa, ob, p, s);
+  return launch_tc2<1>(oa, ob, p, s);
+}
+
+// out (M, N) = a @ w^T with the rotate-half rotary embedding applied to the first rope_cols columns
+// (heads of 128), in the GEMM's epilogue. a (M,K), w (N,K) K-contiguous; cos / sin f32 (P, 64).
+b200Status mm_rope_impl(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w, const b200Tensor* cos_t,
+                        const b200Tensor* sin_t, int64_t seq_len, int64_t rope_cols, cudaStream_t s) {
+  const char* name = "b200_mm_rope";
+  B200_REQUIRE(valid(out) && valid(a) && valid(w) && valid(cos_t) && valid(sin_t), B200_BAD_PARAM, "%s: invalid tensor view", name);
+  B200_REQUIRE(out->ndim == 2 && a->ndim == 2 && w->ndim == 2, B200_BAD_PARAM, "%s: operands must be 2-D", name);
+  B200_REQUIRE((a->dtype == B200_BF16 || a->dtype == B200_F16) && w->dtype == a->dtype && out->dtype == a->dtype,
+               B200_NOT_SUPPORTED, "%s: bf16 or f16 operands of one dtype", name);
+  const int64_t M = a->sizes[0], K = a->sizes[1], N = w->sizes[0];
+  B200_REQUIRE(out->sizes[0] == M && out->sizes[1] == N && w->sizes[1] == K, B200_BAD_PARAM, "%s: expected a (M,K), w (N,K), out (M,N)", name);
+  B200_REQUIRE(rope_cols >= 0 && rope_cols <= N && rope_cols % 128 == 0 && seq_len > 0, B200_BAD_PARAM,
+               "%s: rope_cols must be a multiple of the head size 128 within N, seq_len positive", name);
+  B200_REQUIRE(cos_t->dtype == B200_F32 && sin_t->dtype == B200_F32 && cos_t->ndim == 2 && same_shape(cos_t, sin_t) &&
+               cos_t->sizes[1] == 64 && cos_t->sizes[0] >= seq_len && is_contiguous(cos_t) && is_contiguous(sin_t), B200_BAD_PARAM,
+               "%s: cos / sin must be contiguous f32 (positions >= seq_len, 64)", name);
+  if (M == 0 || N == 0) return B200_OK;
+  B200_REQUIRE(K > 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31) && (out->strides[1] == 1 || N == 1), B200_NOT_SUPPORTED,
+               "%s: sizes or output layout not supported", name);
+  Operand oa, ob;
+  const bool a_ok = describe_operand(a->data, M, K, 1, a->strides[0], a->strides[1], 0, BM, &oa) && !oa.mn_major;
+  const bool b_ok = describe_operand(w->data, N, K, 1, w->strides[0], w->strides[1], 0, BN2 / 2, &ob) && !ob.mn_major;
+  B200_REQUIRE(a_ok && b_ok, B200_NOT_SUPPORTED, "%s: operands must be K-contiguous, 16-byte aligned, leading dimension a multiple of 8", name);
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = 1;
+  p.is_bf16 = a->dtype == B200_BF16;
+  p.alpha = 1.f; p.beta = 0.f;
+  p.out = out->data; p.o_sm = out->strides[0];
+  p.rope_cos = static_cast<const float*>(cos_t->data);
+  p.rope_sin = static_cast<const float*>(sin_t->data);
+  p.rope_seq = (int)seq_len; p.rope_cols = (int)rope_cols;
+  p.error_word = device_error_word();
+  B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+  return launch_tc2<2>(oa, ob, p, s);
 }
 
 }  // namespace b200
@@ -966,6 +1062,11 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
 using namespace b200;
 
 extern "C" {
+
+b200Status b200_mm_rope(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w, const b200Tensor* cos_table,
+                        const b200Tensor* sin_table, int64_t seq_len, int64_t rope_cols, b200Stream stream) {
+  return mm_rope_impl(out, a, w, cos_table, sin_table, seq_len, rope_cols, static_cast<cudaStream_t>(stream));
+}
 
 b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up, b200Stream stream) {
   return mm_swiglu_impl(out, a, w_gate_up, static_cast<cudaStream_t>(stream));

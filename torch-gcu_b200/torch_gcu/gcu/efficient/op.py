@@ -59,6 +59,13 @@ def linear_swiglu(x: Tensor, w_gate_up: Tensor):
     return _C._linear_swiglu(x, w_gate_up)
 
 
+def linear_rope(x: Tensor, w: Tensor, cos: Tensor, sin: Tensor, rope_heads: int):
+    """Fused qkv projection of x (B, S, K) with weight (heads*128, K): returns (B, S, heads, 128) with the
+    rotate-half rotary embedding (tables as for `rope`, position = index along S) applied to the first
+    `rope_heads` heads in the GEMM's epilogue."""
+    return _C._linear_rope(x, w, cos, sin, rope_heads)
+
+
 def sdpa_flash(q: Tensor, k: Tensor, v: Tensor, is_causal: bool, scale: Optional[float] = None):
     """Flash attention forward for q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D); returns (out, logsumexp)."""
     return _C._sdpa_flash(q, k, v, is_causal, scale)

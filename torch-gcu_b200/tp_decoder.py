@@ -94,9 +94,12 @@ class DecoderLayer:
         hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
         cos, sin = self.tables(S)
         h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
-        qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
+        if d == 128:
+            qkv = eff.linear_rope(h, w["wqkv"], cos, sin, hq + hk)   # qkv GEMM with RoPE on q and k in its epilogue
+        else:
+            qkv = torch.mm(h.view(B * S, H), w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
+            eff.rope(qkv[:, :, :hq + hk], cos, sin, None, True)   # q and k heads are neighbours: one launch
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
-        eff.rope(qkv[:, :, :hq + hk], cos, sin, None, True)   # q and k heads are neighbours in the fused projection: one launch
         if kv_out is not None:
             kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
             kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
