@@ -9,9 +9,11 @@
 //      already laid out as the A operand of the accumulating products:
 //        S^T = K Q^T, dP^T = V dO^T -> P^T, dS^T
 //        dV += P^T dO,  dK += dS^T Q
-// Roles per CTA (192 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 the
-// pointwise stage (one thread per accumulator row). All barrier waits are bounded;
-// loads never use cluster multicast.
+// Roles per CTA: warp 0 TMA producer, warp 1 MMA issuer, then the pointwise warps (one thread
+// per accumulator row): four in the dQ kernel; eight in the dK/dV kernel, which works on
+// 64-query half tiles with two S^T / dP^T buffers in tensor memory so that the next half's
+// products run under the pointwise stage. All barrier waits are bounded; loads never use
+// cluster multicast.
 // (reference: aot_ops/gcu_attention.cpp:135-203 _scaled_dot_product_flash_attention_backward.)
 #include "common.cuh"
 #include "tc_common.cuh"
