@@ -40,6 +40,7 @@ constexpr int kKVStages = 2;
 struct AttnParams {
   int B, Hq, Hkv, Sq, Sk, D;
   int causal, packed, is_bf16;
+  int pair_heads;    // prefill kernel: the CTA's two Q tiles are two heads of one KV group (else two row tiles)
   float scale_log2;  // scale * log2(e)
   float scale;
   void* out;
@@ -395,13 +396,20 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
-  const int pair = gridDim.x - 1 - blockIdx.x;  // longest (last) causal pairs first
-  const int q0 = pair * 2 * BQ, hq = blockIdx.y, hkv = hq / G, b = blockIdx.z;
+  // The two Q tiles of a CTA: with an even group size, the same 128 query rows of two query heads that share
+  // the KV head (equal work and equal masks for both tiles, so the ping-pong never runs single-handed);
+  // otherwise two consecutive row tiles of one head.
+  const int first = gridDim.x - 1 - blockIdx.x;  // longest (last) causal tiles first
+  const int b = blockIdx.z;
+  const int q0 = p.pair_heads ? first * BQ : first * 2 * BQ;
+  const int hq = p.pair_heads ? blockIdx.y * 2 : blockIdx.y;
+  const int hkv = hq / G;
+  const int tile_rows = p.pair_heads ? 0 : BQ, tile_heads = p.pair_heads ? 1 : 0;   // step from tile 0 to tile 1
   const int n_all = (p.Sk + BKV - 1) / BKV;
   int n_t[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int q0t = q0 + t * BQ;
+    const int q0t = q0 + t * tile_rows;
     n_t[t] = q0t >= p.Sq ? 0 : (p.causal ? min(n_all, q0t / BKV + 1) : n_all);
   }
   const int n_max = max(n_t[0], n_t[1]);
@@ -439,7 +447,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       for (int t = 0; t < n_q; ++t)
 #pragma unroll
         for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_load_4d(sQ + t * Cfg::kQBytes + h * (BQ * 128), &tmap_q, q_full, h * 64, q0 + t * BQ, hq, b);
+          tma_load_4d(sQ + t * Cfg::kQBytes + h * (BQ * 128), &tmap_q, q_full, h * 64, q0 + t * tile_rows, hq + t * tile_heads, b);
       for (int j = 0; j < n_max; ++j) {
         const int st = j & 1;
         if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1u) ^ 1u, abort_flag)) break;
@@ -517,7 +525,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int quarter = warp & 3;                  // tensor-memory lanes this warp may touch
     const int r = quarter * 32 + lane;             // row of the tile this thread owns
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
-    const int q0t = q0 + t * BQ;
+    const int q0t = q0 + t * tile_rows;
+    const int head = hq + t * tile_heads;
     const int qi = q0t + r;
     const bool row_valid = qi < p.Sq;
     const int n_kv = n_t[t];
@@ -595,7 +604,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (ok && n_kv > 0) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(hq) * p.o_sh +
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(head) * p.o_sh +
                        static_cast<int64_t>(qi) * p.o_ss;
       const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
 #pragma unroll 1
@@ -623,7 +632,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       }
       if (row_valid && p.lse) {
         const float lse = l > 0.f ? m * p.scale + logf(l) : -CUDART_INF_F;
-        p.lse[(static_cast<int64_t>(b) * p.Hq + hq) * p.Sq + qi] = lse;
+        p.lse[(static_cast<int64_t>(b) * p.Hq + head) * p.Sq + qi] = lse;
       }
     }
   }
@@ -983,7 +992,8 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
   if (p.packed) {
     attention_fwd_kernel<D><<<dim3(1, p.Hkv, p.B), kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
   } else {
-    const dim3 grid((p.Sq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
+    p.pair_heads = (p.Hq / p.Hkv) % 2 == 0 ? 1 : 0;
+    const dim3 grid = p.pair_heads ? dim3((p.Sq + BQ - 1) / BQ, p.Hq / 2, p.B) : dim3((p.Sq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
     if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
     else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
   }
