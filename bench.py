@@ -366,10 +366,10 @@ def gemm_roofline(dev, tf_peak, peak_kind, world):
     ms = _time_gcu(lambda: efficient.linear_swiglu(a, w))
     tf = 2 * m * n * k / ms / 1e9
     # DRAM traffic per launch, scaled from a smaller capture of the same kernel (profiles/): the tile walk keeps a
-    # band of 20 row-tiles of A in L2 and streams the weight once per band, so traffic = A + W x bands + out; the
+    # band of 16 row-tiles of A in L2 and streams the weight once per band, so traffic = A + W x bands + out; the
     # capture at 8192 x (2 x 4096) x 4096 (2 bands) moved 305.3 MB against 268.4 MB by that count (x 1.14, L2 misses
     # inside a band), and the same factor is applied to this launch's counts.
-    bands = -(-(m // 256) // 20)
+    bands = -(-(m // 256) // 16)
     traffic = int(1.14 * 2 * (m * k + n * k * bands + m * n // 2))
     return {"bound": "tensor", "kernel": "gemm_tc2_kernel<swiglu> (gate/up projection %dx%dx%d, SwiGLU in the epilogue)" % (m, n, k),
             "achieved": round(tf, 1), "peak": tf_peak, "unit": "TFLOP/s", "frac": round(tf / tf_peak, 3),

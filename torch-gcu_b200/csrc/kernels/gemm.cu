@@ -69,7 +69,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;           // 64 x 16-bit = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;
-constexpr int kBandBytes = 40 << 20;   // rows of A kept hot in L2 while one band of row-tiles sweeps all of B
+constexpr int kBandBytes = 32 << 20;   // rows of A kept hot in L2 while one band of row-tiles sweeps all of B
 
 struct GemmParams {
   int M, N, K, batch;
@@ -102,6 +102,8 @@ template <int BN> struct GemmCfg {
 // Row-tiles per band: as many as keep the band's rows of A (tile_rows x K each) within kBandBytes,
 // so that B is streamed from DRAM once per band and A once in total.
 inline int band_rows(int tile_rows, int64_t K) {
+  static const int forced = [] { const char* e = getenv("B200_GEMM_BAND"); return e ? atoi(e) : 0; }();   // tuning aid
+  if (forced > 0) return forced;
   const int64_t per_tile = static_cast<int64_t>(tile_rows) * K * 2;
   int64_t g = per_tile > 0 ? kBandBytes / per_tile : 8;
   return static_cast<int>(g < 8 ? 8 : (g > 64 ? 64 : g));   // never narrower than 8: a long K needs B reuse more
