@@ -91,8 +91,18 @@ class DecoderLayer:
     def attn_part(self, x, kv_out=None):
         """RMSNorm -> qkv -> RoPE -> attention -> o_proj; returns this rank's partial (B*S, hidden)."""
         B, S, H = x.shape
-        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
         cos, sin = self.tables(S)
+        if self.backend != "gcu":   # plain torch, fp32 math on whatever dtype the weights have
+            h = _rms_cpu(x, w["norm1"], self.eps)
+            qkv = (h.float() @ w["wqkv"].float().t()).view(B, S, hq + 2 * hk, d)
+            q = _rope_cpu(qkv[:, :, :hq], cos, sin).transpose(1, 2)
+            k = _rope_cpu(qkv[:, :, hq:hq + hk], cos, sin).transpose(1, 2)
+            v = qkv[:, :, hq + hk:].transpose(1, 2)
+            g = hq // hk
+            att = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
+            return (att.transpose(1, 2).reshape(B, S, hq * d) @ w["wo"].float().t()).reshape(B * S, H)
+        eff = self.eff
         h, _ = eff.rms_norm_residual(x, None, w["norm1"], self.eps)
         if d == 128:
             qkv = eff.linear_rope(h, w["wqkv"], cos, sin, hq + hk)   # qkv GEMM with RoPE on q and k in its epilogue
@@ -110,7 +120,14 @@ class DecoderLayer:
         """o: the reduced attention output. Returns (down, r): this rank's partial MLP output
         (with the residual already added when tp == 1) and the residual stream."""
         B, S, H = x.shape
-        w, eff = self.w, self.eff
+        w = self.w
+        if self.backend != "gcu":
+            r = x.float() + o.view(B, S, H)
+            h2 = _rms_cpu(r, w["norm2"], self.eps)
+            gu = h2 @ w["wgu"].float().t()
+            down = ((F.silu(gu[..., :self.f]) * gu[..., self.f:]) @ w["wd"].float().t()).reshape(B * S, H)
+            return (down.view(B, S, H) + r, r) if self.tp == 1 else (down, r)
+        eff = self.eff
         h2, r = eff.rms_norm_residual(o.view(B, S, H), x, w["norm2"], self.eps)
         act = eff.linear_swiglu(h2.view(B * S, H), w["wgu"])   # gate/up GEMM with the SwiGLU in its epilogue
         if self.tp == 1:
@@ -119,32 +136,13 @@ class DecoderLayer:
 
     def forward_prefill(self, x, group=None, kv_out=None):
         B, S, H = x.shape
-        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
-        cos, sin = self.tables(S)
-        if self.backend == "gcu":
-            o = self.attn_part(x, kv_out)
-            self._allreduce(o, group)
-            down, r = self.mlp_part(o, x)
-            if self.tp == 1:
-                return down
-            self._allreduce(down, group)
-            return torch.add(down.view(B, S, H), r)
-        # plain torch (fp32 math on whatever dtype the weights have)
-        h = _rms_cpu(x, w["norm1"], self.eps)
-        qkv = (h.float() @ w["wqkv"].float().t()).view(B, S, hq + 2 * hk, d)
-        q = _rope_cpu(qkv[:, :, :hq], cos, sin).transpose(1, 2)
-        k = _rope_cpu(qkv[:, :, hq:hq + hk], cos, sin).transpose(1, 2)
-        v = qkv[:, :, hq + hk:].transpose(1, 2)
-        g = hq // hk
-        att = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
-        o = att.transpose(1, 2).reshape(B, S, hq * d) @ w["wo"].float().t()
+        o = self.attn_part(x, kv_out)
         self._allreduce(o, group)
-        r = x.float() + o
-        h2 = _rms_cpu(r, w["norm2"], self.eps)
-        gu = h2 @ w["wgu"].float().t()
-        down = (F.silu(gu[..., :self.f]) * gu[..., self.f:]) @ w["wd"].float().t()
+        down, r = self.mlp_part(o, x)
+        if self.tp == 1:
+            return down
         self._allreduce(down, group)
-        return r + down
+        return torch.add(down.view(B, S, H), r)
 
     # -------------------------------------------------------------- decode --
     def forward_decode(self, x, kv, pos, group=None):
@@ -198,7 +196,9 @@ class DecoderStack:
             # SMs: 583 k against 565 k), because its CTAs otherwise take as much from the GEMMs as they hide
             import os
             overlap = os.environ.get("TP_DECODER_OVERLAP", "1") != "0"
-        if self.tp > 1 and overlap and self.layers[0].backend == "gcu" and x.shape[0] % 2 == 0:
+        if self.tp > 1 and overlap and x.shape[0] % 2 == 0:
+            if self.layers[0].backend != "gcu":
+                return self._two_microbatches(x, group, caches)   # the schedule alone (host-side tests)
             return self._prefill_two_microbatches(x, group, caches)
         for i, layer in enumerate(self.layers):
             x = layer.forward_prefill(x, group, None if caches is None else caches[i])
