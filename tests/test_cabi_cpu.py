@@ -74,3 +74,59 @@ def test_wrapper_raises_on_error(ops):
     b = torch.zeros(4, 5)
     with pytest.raises(ops.B200Error):
         ops.add(a, a, b, stream=0)
+
+
+def test_newer_entry_points_reject_malformed_arguments(ops):
+    """Argument checks of the fused GEMMs, the comparison / selection family, the attention backward and
+    the loss entries run before any device call, so they can be exercised without a GPU."""
+    L = ops.lib()
+    null = ctypes.c_void_p(0)
+    ref = ctypes.byref
+    f32 = _fake(ops, (4, 8), ops.F32)
+    b16 = _fake(ops, (256, 64), ops.BF16)
+    w16 = _fake(ops, (512, 64), ops.BF16)
+    o16 = _fake(ops, (256, 256), ops.BF16)
+    # fused gate/up GEMM: fp32 operands, then a weight whose row count is not 2F
+    assert L.b200_mm_swiglu(ref(f32), ref(f32), ref(f32), null) == ops.NOT_SUPPORTED
+    bad_w = _fake(ops, (500, 64), ops.BF16)
+    assert L.b200_mm_swiglu(ref(o16), ref(b16), ref(bad_w), null) == ops.BAD_PARAM
+    # fused qkv GEMM: rope_cols not a multiple of the head size; tables of the wrong dtype
+    cos = _fake(ops, (300, 64), ops.F32)
+    out_qkv = _fake(ops, (256, 512), ops.BF16)
+    st = L.b200_mm_rope(ref(out_qkv), ref(b16), ref(w16), ref(cos), ref(cos), ctypes.c_int64(256), ctypes.c_int64(100), null)
+    assert st == ops.BAD_PARAM and b"128" in L.b200_last_error()
+    cos16 = _fake(ops, (300, 64), ops.BF16)
+    st = L.b200_mm_rope(ref(out_qkv), ref(b16), ref(w16), ref(cos16), ref(cos16), ctypes.c_int64(256), ctypes.c_int64(256), null)
+    assert st == ops.BAD_PARAM
+    # comparison: the output must be bool; unknown operator
+    bool_out = _fake(ops, (4, 8), ops.BOOL)
+    assert L.b200_compare(ref(f32), ref(f32), ref(f32), ctypes.c_int32(0), null) == ops.BAD_PARAM
+    assert L.b200_compare(ref(bool_out), ref(f32), ref(f32), ctypes.c_int32(42), null) == ops.BAD_PARAM
+    # where: the condition must be bool
+    assert L.b200_where(ref(f32), ref(f32), ref(f32), ref(f32), null) == ops.BAD_PARAM
+    # clamp without a bound; extreme over a dimension that does not exist
+    assert L.b200_clamp(ref(f32), ref(f32), ctypes.c_int32(0), ctypes.c_double(0), ctypes.c_int32(0), ctypes.c_double(0), null) == ops.BAD_PARAM
+    idx = _fake(ops, (4,), ops.I64)
+    assert L.b200_extreme_dim(None, ref(idx), ref(f32), ctypes.c_int64(3), ctypes.c_int32(1), null) == ops.BAD_PARAM
+    # attention backward: head dim other than 128; missing workspace
+    q64 = _fake(ops, (1, 2, 128, 64), ops.BF16)
+    lse = _fake(ops, (1, 2, 128), ops.F32)
+    args64 = [ref(q64)] * 8
+    st = L.b200_sdpa_flash_bwd(*args64, ref(lse), ctypes.c_int32(1), ctypes.c_double(0.125), None, ctypes.c_size_t(0), null)
+    assert st == ops.NOT_SUPPORTED
+    q128 = _fake(ops, (1, 2, 128, 128), ops.BF16)
+    args128 = [ref(q128)] * 8
+    st = L.b200_sdpa_flash_bwd(*args128, ref(lse), ctypes.c_int32(1), ctypes.c_double(0.09), None, ctypes.c_size_t(0), null)
+    assert st == ops.WORKSPACE_TOO_SMALL
+    # NLL loss: targets must be int64 of N elements
+    logp = _fake(ops, (6, 10), ops.F32)
+    one = _fake(ops, (1,), ops.F32)
+    tgt32 = _fake(ops, (6,), ops.I32)
+    st = L.b200_nll_loss(ref(one), ref(one), ref(logp), ref(tgt32), None, ctypes.c_int32(1), ctypes.c_int64(-100), null)
+    assert st == ops.BAD_PARAM
+    # layer-norm backward: the column sums need a workspace
+    g = _fake(ops, (6, 10), ops.F32)
+    stat = _fake(ops, (6,), ops.F32)
+    dw = _fake(ops, (10,), ops.F32)
+    L.b200_layer_norm_backward_workspace_size.restype = ctypes.c_size_t
+    assert L.b200_layer_norm_backward_workspace_size(ctypes.c_int64(6), ctypes.c_int64(10)) > 0
