@@ -107,7 +107,15 @@ cast_stream_kernel(D* __restrict__ dst, const S* __restrict__ src, int64_t n) {
 #pragma unroll
     for (int u = 0; u < U; ++u) store_stream_pack(out + i + u * stride, convert(p[u]));
   }
-  for (; i < nv; i += stride) out[i] = convert(in[i]);
+  if (i < nv) {  // last, partial batch: every slot predicated, loads still issued together
+    PackE<S, E> p[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i + u * stride < nv) p[u] = load_stream_pack(in + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i + u * stride < nv) store_stream_pack(out + i + u * stride, convert(p[u]));
+  }
   if (blockIdx.x == 0) {
     int64_t t = nv * E + threadIdx.x;
     if (t < n) dst[t] = store_from_math<D>(load_as_math(src[t]));
@@ -146,7 +154,8 @@ b200Status dispatch_dst(const b200Tensor* dst, const b200Tensor* src, cudaStream
 template <typename S, typename D>
 b200Status launch_stream_cast(const b200Tensor* dst, const b200Tensor* src, cudaStream_t s) {
   const int64_t n = numel(dst);
-  int grid = grid_for(n / 4 / 8 + 1, kThreads, 8);
+  constexpr int E = 16 / (sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D));
+  int grid = wave_grid<cast_stream_kernel<S, D>>((n / E + 8 * kThreads - 1) / (8 * kThreads), kThreads, kStreamWaves);
   cast_stream_kernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<D*>(dst->data),
                                                     static_cast<const S*>(src->data), n);
   return check_launch("b200_copy(cast)");

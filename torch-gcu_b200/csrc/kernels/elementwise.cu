@@ -122,17 +122,31 @@ ew_contig_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restri
       store_stream16(out + (i + u * stride) * V, r);
     }
   }
-  for (; i < nvec; i += stride) {
-    Vec16<T> va = load_stream16(a + i * V), vb, r;
-    if constexpr (NIN == 2) vb = load_stream16(b + i * V);
+  // last, partial batch: the same loads-then-stores shape with each slot predicated, so the
+  // remainder keeps kUnroll loads in flight per thread instead of one
+  if (i < nvec) {
+    Vec16<T> va[kUnroll], vb[kUnroll];
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      if constexpr (NIN == 2)
-        r.v[k] = store_from_math<T>(f(load_as_math(va.v[k]), load_as_math(vb.v[k])));
-      else
-        r.v[k] = store_from_math<T>(f(load_as_math(va.v[k])));
+    for (int u = 0; u < kUnroll; ++u) {
+      if (i + u * stride < nvec) {
+        va[u] = load_stream16(a + (i + u * stride) * V);
+        if constexpr (NIN == 2) vb[u] = load_stream16(b + (i + u * stride) * V);
+      }
     }
-    store_stream16(out + i * V, r);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (i + u * stride < nvec) {
+        Vec16<T> r;
+#pragma unroll
+        for (int k = 0; k < V; ++k) {
+          if constexpr (NIN == 2)
+            r.v[k] = store_from_math<T>(f(load_as_math(va[u].v[k]), load_as_math(vb[u].v[k])));
+          else
+            r.v[k] = store_from_math<T>(f(load_as_math(va[u].v[k])));
+        }
+        store_stream16(out + (i + u * stride) * V, r);
+      }
+    }
   }
   // ragged tail (fewer than one vector)
   if (blockIdx.x == 0) {
@@ -169,7 +183,7 @@ b200Status launch_binary(const b200Tensor* out, const b200Tensor* a, const b200T
   if (is_contiguous(out) && is_contiguous(a) && is_contiguous(b) && aligned16(po) &&
       aligned16(pa) && aligned16(pb)) {
     constexpr int V = 16 / sizeof(T);
-    int grid = grid_for((n + V - 1) / V / kUnroll + 1, kThreads, 8);
+    int grid = wave_grid<ew_contig_kernel<T, 2, F>>((n / V + kUnroll * kThreads - 1) / (kUnroll * kThreads), kThreads, kStreamWaves);
     ew_contig_kernel<T, 2, F><<<grid, kThreads, 0, s>>>(po, pa, pb, n, f);
   } else {
     const b200Tensor* ts[3] = {out, a, b};
@@ -189,7 +203,7 @@ b200Status launch_unary(const b200Tensor* out, const b200Tensor* a, F f, cudaStr
   const T* pa = static_cast<const T*>(a->data);
   if (is_contiguous(out) && is_contiguous(a) && aligned16(po) && aligned16(pa)) {
     constexpr int V = 16 / sizeof(T);
-    int grid = grid_for((n + V - 1) / V / kUnroll + 1, kThreads, 8);
+    int grid = wave_grid<ew_contig_kernel<T, 1, F>>((n / V + kUnroll * kThreads - 1) / (kUnroll * kThreads), kThreads, kStreamWaves);
     ew_contig_kernel<T, 1, F><<<grid, kThreads, 0, s>>>(po, pa, nullptr, n, f);
   } else {
     const b200Tensor* ts[2] = {out, a};

@@ -322,11 +322,12 @@ b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tenso
   a.sin_t = static_cast<const float*>(sin_table->data);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = a.B * a.S * a.H * (a.D / 2 / V);
-  const int grid = grid_for(total, 256, 8);
-  const bool small = total + static_cast<int64_t>(grid) * 256 < (int64_t(1) << 32);
+  const int64_t need = (total + 255) / 256;
+  // 32-bit item arithmetic needs total + one grid stride below 2^32; bound the stride by 64 waves of 8 blocks
+  const bool small = total + static_cast<int64_t>(sm_count_current_device()) * 8 * 64 * 256 < (int64_t(1) << 32);
   B200_DISPATCH_HALF_FLOAT(x->dtype, T, {
-    if (small) rope_kernel<T, uint32_t><<<grid, 256, 0, s>>>(a);
-    else rope_kernel<T, int64_t><<<grid, 256, 0, s>>>(a);
+    if (small) rope_kernel<T, uint32_t><<<wave_grid<rope_kernel<T, uint32_t>>(need, 256, 4), 256, 0, s>>>(a);
+    else rope_kernel<T, int64_t><<<wave_grid<rope_kernel<T, int64_t>>(need, 256, 4), 256, 0, s>>>(a);
   });
   return check_launch("b200_rope");
 }
@@ -353,7 +354,7 @@ b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200
       if (so == cols && sg == cols && su == cols) {  // flat
         vpr = rows * vpr; r = 1;
       }
-      const int grid = grid_for(r * vpr / 4 + 1, 256, 8);
+      const int grid = wave_grid<swiglu_kernel<T>>((r * vpr + 1023) / 1024, 256, kStreamWaves);
       swiglu_kernel<T><<<grid, 256, 0, s>>>((T*)out->data, (const T*)gate->data, (const T*)up->data, r, vpr, so, sg, su);
     } else {
       const int grid = grid_for(rows * cols, 256, 8);

@@ -128,13 +128,13 @@ b200Status launch_row_gather_i(RowGatherArgs a, int unit, cudaStream_t s) {
   if (items == 0) return B200_OK;
   const int64_t groups_per_block = kThreads >> g_log;
   int64_t need = (items + groups_per_block - 1) / groups_per_block;
-  const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 16;
-  const int grid = static_cast<int>(need < cap ? need : cap);
   const bool small = items < (int64_t(1) << 31) && a.n_rows < (int64_t(1) << 31);
-#define B200_RG(U)                                                                     \
-  do {                                                                                 \
-    if (small) row_gather_kernel<U, I, uint32_t><<<grid, kThreads, 0, s>>>(a);         \
-    else row_gather_kernel<U, I, int64_t><<<grid, kThreads, 0, s>>>(a);                \
+#define B200_RG(U)                                                                                                  \
+  do {                                                                                                              \
+    if (small)                                                                                                      \
+      row_gather_kernel<U, I, uint32_t><<<wave_grid<row_gather_kernel<U, I, uint32_t>>(need, kThreads, kStreamWaves), kThreads, 0, s>>>(a); \
+    else                                                                                                            \
+      row_gather_kernel<U, I, int64_t><<<wave_grid<row_gather_kernel<U, I, int64_t>>(need, kThreads, kStreamWaves), kThreads, 0, s>>>(a);   \
   } while (0)
   switch (unit) {
     case 16: B200_RG(int4); break;
