@@ -748,6 +748,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // set-up above runs under the predecessor's tail; Q, K and V are read from here on
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -769,6 +770,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 #pragma unroll
         for (int h = 0; h < 2; ++h) tma_load_4d(dst + h * (BKV * 128), tm, &slot_full[slot], h * 64, key0, hkv, b);
       }
+      pdl_launch_dependents();   // all loads issued
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer --
@@ -1026,13 +1028,15 @@ b200Status launch_decode(const b200Tensor* q, const b200Tensor* k, const b200Ten
   cfg.blockDim = dim3(kDecThreads);
   cfg.dynamicSmemBytes = Cfg::kSmem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = splits;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<16, BF16>, tq, tk, tv, p, splits);
   B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
   return check_launch("b200_sdpa_flash_fwd");

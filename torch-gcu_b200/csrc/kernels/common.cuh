@@ -305,6 +305,43 @@ inline int wave_grid(int64_t need_blocks, int threads, int waves = 1, size_t dyn
   return static_cast<int>(need_blocks < cap ? need_blocks : cap);
 }
 
+// ------------------------------------------------- programmatic dependent launch --
+// A kernel launched through launch_pdl may become resident while its predecessor on the stream
+// is still draining (its blocks are scheduled as soon as every block of the predecessor has
+// called pdl_launch_dependents() or exited), which hides the launch latency and the ramp of a
+// short kernel under the predecessor's tail. The contract of such a kernel: pdl_wait() before
+// its first access to global memory (the wait returns once the predecessor has completed and
+// its writes are visible; it is a no-op for a kernel launched without the attribute).
+// B200_PDL=0 launches everything fully serialised.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = std::getenv("B200_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

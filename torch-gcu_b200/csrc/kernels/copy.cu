@@ -43,6 +43,8 @@ template <> __device__ __forceinline__ bool_t narrow<bool_t, int64_t>(int64_t w)
 template <typename S, typename D>
 __global__ void __launch_bounds__(kThreads)
 cast_indexed_kernel(D* dst, const S* src, int64_t n, StridedIndexer<2> ix, bool contig) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
     int64_t off[2] = {i, i};
@@ -54,6 +56,8 @@ cast_indexed_kernel(D* dst, const S* src, int64_t n, StridedIndexer<2> ix, bool 
 template <typename U>
 __global__ void __launch_bounds__(kThreads)
 copy_indexed_kernel(U* dst, const U* src, int64_t n, StridedIndexer<2> ix) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
     int64_t off[2];
@@ -87,6 +91,8 @@ template <typename P> __device__ __forceinline__ void store_stream_pack(P* p, co
 template <typename S, typename D>
 __global__ void __launch_bounds__(kThreads)
 cast_stream_kernel(D* __restrict__ dst, const S* __restrict__ src, int64_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int E = 16 / (sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D));
   constexpr int U = 8;
   const int64_t nv = n / E;
@@ -129,8 +135,8 @@ b200Status launch_cast(const b200Tensor* dst, const b200Tensor* src, cudaStream_
   auto ix = make_indexer<2>(ts);
   bool contig = is_contiguous(dst) && is_contiguous(src);
   int grid = grid_for(n, kThreads, 8);
-  cast_indexed_kernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<D*>(dst->data),
-                                                     static_cast<const S*>(src->data), n, ix, contig);
+  launch_pdl(cast_indexed_kernel<S, D>, grid, kThreads, 0, s, static_cast<D*>(dst->data),
+             static_cast<const S*>(src->data), n, ix, contig);
   return check_launch("b200_copy(cast)");
 }
 
@@ -156,8 +162,8 @@ b200Status launch_stream_cast(const b200Tensor* dst, const b200Tensor* src, cuda
   const int64_t n = numel(dst);
   constexpr int E = 16 / (sizeof(S) > sizeof(D) ? sizeof(S) : sizeof(D));
   int grid = wave_grid<cast_stream_kernel<S, D>>((n / E + 8 * kThreads - 1) / (8 * kThreads), kThreads, kStreamWaves);
-  cast_stream_kernel<S, D><<<grid, kThreads, 0, s>>>(static_cast<D*>(dst->data),
-                                                    static_cast<const S*>(src->data), n);
+  launch_pdl(cast_stream_kernel<S, D>, grid, kThreads, 0, s, static_cast<D*>(dst->data),
+             static_cast<const S*>(src->data), n);
   return check_launch("b200_copy(cast)");
 }
 
@@ -188,11 +194,11 @@ b200Status strided_same_dtype(const b200Tensor* dst, const b200Tensor* src, cuda
   const int64_t n = numel(dst) / ratio;
   int grid = grid_for(n, kThreads, 8);
   switch (unit) {
-    case 16: copy_indexed_kernel<int4><<<grid, kThreads, 0, s>>>((int4*)dst->data, (const int4*)src->data, n, ix); break;
-    case 8: copy_indexed_kernel<uint64_t><<<grid, kThreads, 0, s>>>((uint64_t*)dst->data, (const uint64_t*)src->data, n, ix); break;
-    case 4: copy_indexed_kernel<uint32_t><<<grid, kThreads, 0, s>>>((uint32_t*)dst->data, (const uint32_t*)src->data, n, ix); break;
-    case 2: copy_indexed_kernel<uint16_t><<<grid, kThreads, 0, s>>>((uint16_t*)dst->data, (const uint16_t*)src->data, n, ix); break;
-    default: copy_indexed_kernel<uint8_t><<<grid, kThreads, 0, s>>>((uint8_t*)dst->data, (const uint8_t*)src->data, n, ix); break;
+    case 16: launch_pdl(copy_indexed_kernel<int4>, grid, kThreads, 0, s, (int4*)dst->data, (const int4*)src->data, n, ix); break;
+    case 8: launch_pdl(copy_indexed_kernel<uint64_t>, grid, kThreads, 0, s, (uint64_t*)dst->data, (const uint64_t*)src->data, n, ix); break;
+    case 4: launch_pdl(copy_indexed_kernel<uint32_t>, grid, kThreads, 0, s, (uint32_t*)dst->data, (const uint32_t*)src->data, n, ix); break;
+    case 2: launch_pdl(copy_indexed_kernel<uint16_t>, grid, kThreads, 0, s, (uint16_t*)dst->data, (const uint16_t*)src->data, n, ix); break;
+    default: launch_pdl(copy_indexed_kernel<uint8_t>, grid, kThreads, 0, s, (uint8_t*)dst->data, (const uint8_t*)src->data, n, ix); break;
   }
   return check_launch("b200_copy(strided)");
 }

@@ -98,6 +98,8 @@ template <typename T, int NIN, typename F>
 __global__ void __launch_bounds__(kThreads)
 ew_contig_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b,
                  int64_t n, F f) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   const int64_t nvec = n / V;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
@@ -184,7 +186,7 @@ b200Status launch_binary(const b200Tensor* out, const b200Tensor* a, const b200T
       aligned16(pa) && aligned16(pb)) {
     constexpr int V = 16 / sizeof(T);
     int grid = wave_grid<ew_contig_kernel<T, 2, F>>((n / V + kUnroll * kThreads - 1) / (kUnroll * kThreads), kThreads, kStreamWaves);
-    ew_contig_kernel<T, 2, F><<<grid, kThreads, 0, s>>>(po, pa, pb, n, f);
+    launch_pdl(ew_contig_kernel<T, 2, F>, grid, kThreads, 0, s, po, pa, pb, n, f);
   } else {
     const b200Tensor* ts[3] = {out, a, b};
     auto ix = make_indexer<3>(ts);
@@ -204,7 +206,7 @@ b200Status launch_unary(const b200Tensor* out, const b200Tensor* a, F f, cudaStr
   if (is_contiguous(out) && is_contiguous(a) && aligned16(po) && aligned16(pa)) {
     constexpr int V = 16 / sizeof(T);
     int grid = wave_grid<ew_contig_kernel<T, 1, F>>((n / V + kUnroll * kThreads - 1) / (kUnroll * kThreads), kThreads, kStreamWaves);
-    ew_contig_kernel<T, 1, F><<<grid, kThreads, 0, s>>>(po, pa, nullptr, n, f);
+    launch_pdl(ew_contig_kernel<T, 1, F>, grid, kThreads, 0, s, po, pa, static_cast<const T*>(nullptr), n, f);
   } else {
     const b200Tensor* ts[2] = {out, a};
     auto ix = make_indexer<2>(ts);

@@ -11,6 +11,8 @@ template <typename T, int BX, int VPT>
 __global__ void __launch_bounds__(BX)
 rms_norm_residual_kernel(T* __restrict__ y, T* res_out, const T* x, const T* res,
                          const T* __restrict__ w, int64_t N, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   __shared__ float smem[BX / 32];
   const int64_t row = blockIdx.x;
@@ -104,12 +106,12 @@ b200Status launch_rms(void* y, void* res_out, const void* x, const void* res, co
   const T* pr = static_cast<const T*>(res);
   const T* pw = static_cast<const T*>(w);
   const unsigned grid = static_cast<unsigned>(M);
-  if (al && nvec <= 128) rms_norm_residual_kernel<T, 128, 1><<<grid, 128, 0, s>>>(py, pro, px, pr, pw, N, eps);
-  else if (al && nvec <= 256) rms_norm_residual_kernel<T, 256, 1><<<grid, 256, 0, s>>>(py, pro, px, pr, pw, N, eps);
-  else if (al && nvec <= 512) rms_norm_residual_kernel<T, 256, 2><<<grid, 256, 0, s>>>(py, pro, px, pr, pw, N, eps);
-  else if (al && nvec <= 1024) rms_norm_residual_kernel<T, 256, 4><<<grid, 256, 0, s>>>(py, pro, px, pr, pw, N, eps);
-  else if (al && nvec <= 2048) rms_norm_residual_kernel<T, 512, 4><<<grid, 512, 0, s>>>(py, pro, px, pr, pw, N, eps);
-  else if (al && nvec <= 4096) rms_norm_residual_kernel<T, 1024, 4><<<grid, 1024, 0, s>>>(py, pro, px, pr, pw, N, eps);
+  if (al && nvec <= 128) launch_pdl(rms_norm_residual_kernel<T, 128, 1>, grid, 128, 0, s, py, pro, px, pr, pw, N, eps);
+  else if (al && nvec <= 256) launch_pdl(rms_norm_residual_kernel<T, 256, 1>, grid, 256, 0, s, py, pro, px, pr, pw, N, eps);
+  else if (al && nvec <= 512) launch_pdl(rms_norm_residual_kernel<T, 256, 2>, grid, 256, 0, s, py, pro, px, pr, pw, N, eps);
+  else if (al && nvec <= 1024) launch_pdl(rms_norm_residual_kernel<T, 256, 4>, grid, 256, 0, s, py, pro, px, pr, pw, N, eps);
+  else if (al && nvec <= 2048) launch_pdl(rms_norm_residual_kernel<T, 512, 4>, grid, 512, 0, s, py, pro, px, pr, pw, N, eps);
+  else if (al && nvec <= 4096) launch_pdl(rms_norm_residual_kernel<T, 1024, 4>, grid, 1024, 0, s, py, pro, px, pr, pw, N, eps);
   else rms_norm_residual_generic_kernel<T><<<grid, 256, 0, s>>>(py, pro, px, pr, pw, N, eps);
   return check_launch("b200_rms_norm_residual");
 }
@@ -131,6 +133,8 @@ struct RopeArgs {
 template <typename T, typename W>
 __global__ void __launch_bounds__(256)
 rope_kernel(RopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   const int64_t half = a.D / 2;
   const W vph = static_cast<W>(half / V);  // vectors per half row
@@ -198,6 +202,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate, const T* __restrict__ up, int64_t rows,
               int64_t vpr, int64_t so, int64_t sg, int64_t su) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   constexpr int U = 4;
   const int64_t total = rows * vpr;
@@ -326,8 +332,8 @@ b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tenso
   // 32-bit item arithmetic needs total + one grid stride below 2^32; bound the stride by 64 waves of 8 blocks
   const bool small = total + static_cast<int64_t>(sm_count_current_device()) * 8 * 64 * 256 < (int64_t(1) << 32);
   B200_DISPATCH_HALF_FLOAT(x->dtype, T, {
-    if (small) rope_kernel<T, uint32_t><<<wave_grid<rope_kernel<T, uint32_t>>(need, 256, 4), 256, 0, s>>>(a);
-    else rope_kernel<T, int64_t><<<wave_grid<rope_kernel<T, int64_t>>(need, 256, 4), 256, 0, s>>>(a);
+    if (small) launch_pdl(rope_kernel<T, uint32_t>, wave_grid<rope_kernel<T, uint32_t>>(need, 256, 4), 256, 0, s, a);
+    else launch_pdl(rope_kernel<T, int64_t>, wave_grid<rope_kernel<T, int64_t>>(need, 256, 4), 256, 0, s, a);
   });
   return check_launch("b200_rope");
 }
@@ -355,7 +361,7 @@ b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200
         vpr = rows * vpr; r = 1;
       }
       const int grid = wave_grid<swiglu_kernel<T>>((r * vpr + 1023) / 1024, 256, kStreamWaves);
-      swiglu_kernel<T><<<grid, 256, 0, s>>>((T*)out->data, (const T*)gate->data, (const T*)up->data, r, vpr, so, sg, su);
+      launch_pdl(swiglu_kernel<T>, grid, 256, 0, s, (T*)out->data, (const T*)gate->data, (const T*)up->data, r, vpr, so, sg, su);
     } else {
       const int grid = grid_for(rows * cols, 256, 8);
       swiglu_scalar_kernel<T><<<grid, 256, 0, s>>>((T*)out->data, (const T*)gate->data, (const T*)up->data, rows, cols, so, sg, su);

@@ -161,6 +161,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // barriers and tensor memory were set up under the predecessor's tail; operands are read from here on
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -195,6 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
       }
+      // every load of this CTA is issued: the successor may take SM resources as they come free
+      // (it is triggered late, so a waiting successor never sits on SMs for longer than one tile)
+      pdl_launch_dependents();
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer --
@@ -350,7 +354,8 @@ b200Status launch_tc(const Operand& oa, const Operand& ob, GemmParams p, cudaStr
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
   const int sms = gemm_sm_budget();
   const int grid = tiles < sms ? tiles : sms;
-  gemm_tc_kernel<BN><<<grid, kGemmThreads, Cfg::kSmem, s>>>(ta, tb, p);
+  cudaError_t le = launch_pdl(gemm_tc_kernel<BN>, grid, kGemmThreads, Cfg::kSmem, s, ta, tb, p);
+  B200_REQUIRE(le == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(le));
   return check_launch("matmul (tcgen05)");
 }
 
@@ -468,6 +473,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   cluster_sync_all();      // both CTAs' barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // set-up above runs under the predecessor's tail; operands are read from here on
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer --
@@ -504,6 +510,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           if (++stage == kStages2) { stage = 0; phase ^= 1u; }
         }
       }
+      pdl_launch_dependents();   // all loads issued: at most one tile of work is left
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer --
@@ -703,7 +710,8 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
   const int tiles = ((p.M + BM2 - 1) / BM2) * ((p.N + bno - 1) / bno) * p.batch;
   const int pairs = gemm_sm_budget() / 2;
   const int grid = 2 * (tiles < pairs ? tiles : pairs);
-  gemm_tc2_kernel<EPI><<<grid, kGemmThreads, kSmem2, s>>>(ta, tb, p);
+  cudaError_t le = launch_pdl(gemm_tc2_kernel<EPI>, grid, kGemmThreads, kSmem2, s, ta, tb, p);
+  B200_REQUIRE(le == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(le));
   return check_launch("matmul (tcgen05, two-CTA)");
 }
 
@@ -764,6 +772,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // set-up above runs under the predecessor's tail; operands are read from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -790,6 +799,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
           for (int j = 0; j < BNS / 64; ++j) tma_load_3d(sb + j * 8192, &tmap_b, &full[stage], tn * BNS + j * 64, k * BK, b);
         }
       }
+      pdl_launch_dependents();   // all loads issued
     }
   } else if (warp == 1) {
     if (lane == 0 && n_my > 0) {
@@ -888,13 +898,15 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = kSmemS;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = splits;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, ta, tb, p, splits);
   B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
   return check_launch("matmul (tcgen05, split-K)");

@@ -67,6 +67,8 @@ struct RowGatherArgs {
 template <typename U, typename I, typename W /* item arithmetic */>
 __global__ void __launch_bounds__(kThreads)
 row_gather_kernel(RowGatherArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int G = 1 << a.g_log;
   const W lane = threadIdx.x & (G - 1);
   const W groups_per_block = kThreads >> a.g_log;
@@ -132,9 +134,9 @@ b200Status launch_row_gather_i(RowGatherArgs a, int unit, cudaStream_t s) {
 #define B200_RG(U)                                                                                                  \
   do {                                                                                                              \
     if (small)                                                                                                      \
-      row_gather_kernel<U, I, uint32_t><<<wave_grid<row_gather_kernel<U, I, uint32_t>>(need, kThreads, kStreamWaves), kThreads, 0, s>>>(a); \
+      launch_pdl(row_gather_kernel<U, I, uint32_t>, wave_grid<row_gather_kernel<U, I, uint32_t>>(need, kThreads, kStreamWaves), kThreads, 0, s, a); \
     else                                                                                                            \
-      row_gather_kernel<U, I, int64_t><<<wave_grid<row_gather_kernel<U, I, int64_t>>(need, kThreads, kStreamWaves), kThreads, 0, s>>>(a);   \
+      launch_pdl(row_gather_kernel<U, I, int64_t>, wave_grid<row_gather_kernel<U, I, int64_t>>(need, kThreads, kStreamWaves), kThreads, 0, s, a); \
   } while (0)
   switch (unit) {
     case 16: B200_RG(int4); break;
@@ -160,6 +162,8 @@ template <typename U, typename I>
 __global__ void __launch_bounds__(kThreads)
 gather_lastdim_kernel(U* __restrict__ out, const U* __restrict__ self, const I* __restrict__ index,
                       int64_t n4, int64_t cols, int64_t self_cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t v = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; v < n4; v += stride) {
     const int64_t e = v * 4;
@@ -516,6 +520,7 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
                     const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
                     int64_t n_dst, int64_t n_src, int64_t inner /* elements per row */,
                     int64_t chunks_per_row) {
+  pdl_wait();
   struct alignas(sizeof(T) * V) VecT { T v[V]; };
   const int lane = threadIdx.x & 31;
   const int64_t warps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
@@ -727,11 +732,11 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
   const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 8;
   const int grid = static_cast<int>(need < cap ? need : cap);
   if (vec)
-    segment_rows_kernel<T, V, MODE, ACC32><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
-                                                             sorted_src, seg_start, n_dst, n_src, inner, cpr);
+    launch_pdl(segment_rows_kernel<T, V, MODE, ACC32>, grid, kThreads, 0, s, (T*)out, (const T*)self, (const T*)src,
+               sorted_src, seg_start, n_dst, n_src, inner, cpr);
   else
-    segment_rows_kernel<T, 1, MODE, ACC32><<<grid, kThreads, 0, s>>>((T*)out, (const T*)self, (const T*)src,
-                                                             sorted_src, seg_start, n_dst, n_src, inner, cpr);
+    launch_pdl(segment_rows_kernel<T, 1, MODE, ACC32>, grid, kThreads, 0, s, (T*)out, (const T*)self, (const T*)src,
+               sorted_src, seg_start, n_dst, n_src, inner, cpr);
   return check_launch("segment rows");
 }
 
@@ -867,11 +872,11 @@ b200Status b200_gather(const b200Tensor* out, const b200Tensor* self, int64_t di
 #define B200_GL(U)                                                                                     \
   do {                                                                                                 \
     if (index->dtype == B200_I64)                                                                      \
-      gather_lastdim_kernel<U, int64_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data, \
-                                                                  (const int64_t*)index->data, n4, cols, dim_size); \
+      launch_pdl(gather_lastdim_kernel<U, int64_t>, grid, kThreads, 0, s, (U*)out->data, (const U*)self->data, \
+                 (const int64_t*)index->data, n4, cols, dim_size);                                     \
     else                                                                                               \
-      gather_lastdim_kernel<U, int32_t><<<grid, kThreads, 0, s>>>((U*)out->data, (const U*)self->data, \
-                                                                  (const int32_t*)index->data, n4, cols, dim_size); \
+      launch_pdl(gather_lastdim_kernel<U, int32_t>, grid, kThreads, 0, s, (U*)out->data, (const U*)self->data, \
+                 (const int32_t*)index->data, n4, cols, dim_size);                                     \
   } while (0)
     if (es == 4) B200_GL(uint32_t); else if (es == 2) B200_GL(uint16_t); else B200_GL(uint64_t);
 #undef B200_GL

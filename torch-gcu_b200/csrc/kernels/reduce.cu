@@ -81,6 +81,8 @@ struct RowArgs {
 template <typename T, typename TO, int BX, int VPT, int OP>
 __global__ void __launch_bounds__(BX < 256 ? 256 : BX)
 row_kernel(RowArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = 16 / sizeof(T);
   constexpr int ROWS = BX < 256 ? 256 / BX : 1;
   __shared__ float smem[ROWS * (BX > 32 ? BX / 32 : 1)];
@@ -195,10 +197,10 @@ b200Status launch_row_vpt(const RowArgs& a, int vpt, cudaStream_t s) {
   const int64_t blocks = (a.rows + ROWS - 1) / ROWS;
   B200_REQUIRE(blocks <= 0x7fffffff, B200_NOT_SUPPORTED, "row kernel: too many rows");
   switch (vpt) {
-    case 1: row_kernel<T, TO, BX, 1, OP><<<(unsigned)blocks, threads, 0, s>>>(a); break;
-    case 2: row_kernel<T, TO, BX, 2, OP><<<(unsigned)blocks, threads, 0, s>>>(a); break;
-    case 4: row_kernel<T, TO, BX, 4, OP><<<(unsigned)blocks, threads, 0, s>>>(a); break;
-    default: row_kernel<T, TO, BX, 8, OP><<<(unsigned)blocks, threads, 0, s>>>(a); break;
+    case 1: launch_pdl(row_kernel<T, TO, BX, 1, OP>, (unsigned)blocks, threads, 0, s, a); break;
+    case 2: launch_pdl(row_kernel<T, TO, BX, 2, OP>, (unsigned)blocks, threads, 0, s, a); break;
+    case 4: launch_pdl(row_kernel<T, TO, BX, 4, OP>, (unsigned)blocks, threads, 0, s, a); break;
+    default: launch_pdl(row_kernel<T, TO, BX, 8, OP>, (unsigned)blocks, threads, 0, s, a); break;
   }
   return check_launch("row kernel");
 }
