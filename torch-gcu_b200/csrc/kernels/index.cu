@@ -599,6 +599,154 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
   }
 }
 
+// MODE 0 with the row reads staged through shared memory. The register-resident walk above keeps at
+// most 4 source rows (4 KB) per warp in flight and is bound by latency (49 % of DRAM throughput, 80 % of
+// stall cycles on the row loads): registers limit both the rows per warp and the warps per SM. Here every
+// warp owns a contiguous range of destination rows and a ring of kRingSlots 1 KB slots that it fills with
+// cp.async: the rows it needs, in the order it needs them (row of self, then its sources in sorted
+// order, then the next destination row ...), always kRingSlots rows ahead of the one it is adding. A lane
+// reads back exactly the 2 x 16 bytes it copied itself, so cp.async.wait_group is the only
+// synchronisation. Segment bounds and source ids of a window of rows are staged per warp (no block-wide
+// barrier anywhere). The order of additions is the one of the register walk.
+constexpr int kRingSlots = 8;
+constexpr int kWarpRows = 64;      // destination rows per staged window
+constexpr int kWarpIds = 447;      // source ids staged per window (a longer stretch is read from global)
+constexpr int kWarpSmem = kRingSlots * 1024 + (kWarpRows + 1 + kWarpIds) * 4;
+static_assert(kWarpSmem % 16 == 0, "every warp's ring starts 16-byte aligned");
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gmem_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int V, bool ACC32>
+__global__ void __launch_bounds__(kThreads, 2)
+segment_rows_ring_kernel(T* out, const T* self, const T* __restrict__ src,
+                         const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
+                         int64_t n_dst, int64_t n_src, int64_t inner /* elements per row */,
+                         int64_t chunks_per_row, int64_t rows_per_warp) {
+  pdl_wait();
+  static_assert(sizeof(T) * V == 16, "one 16-byte vector per copy");
+  struct alignas(16) VecT { T v[V]; };
+  using A = typename AccT<T, ACC32>::type;
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* ring = ring_smem + warp * kWarpSmem;
+  uint32_t* s_seg = reinterpret_cast<uint32_t*>(ring + kRingSlots * 1024);
+  uint32_t* s_ids = s_seg + kWarpRows + 1;
+  const int64_t vpr = inner / V;
+  const int64_t gw = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + warp;
+  const int64_t ra = gw * rows_per_warp, rb = min(n_dst, ra + rows_per_warp);
+
+  for (int64_t w0 = ra; w0 < rb; w0 += kWarpRows) {
+    const int rows = static_cast<int>(min(static_cast<int64_t>(kWarpRows), rb - w0));
+    __syncwarp();   // the previous window's readers are done with the staged words
+    for (int i = lane; i <= rows; i += 32) s_seg[i] = seg_start[w0 + i];
+    __syncwarp();
+    const uint32_t g_beg = s_seg[0], g_end = s_seg[rows];
+    const uint32_t staged = (g_beg <= g_end && g_end <= n_src) ? min(g_end - g_beg, static_cast<uint32_t>(kWarpIds)) : 0u;
+    for (uint32_t i = lane; i < staged; i += 32) s_ids[i] = sorted_src[g_beg + i];
+    __syncwarp();
+    auto id_at = [&](uint32_t p) -> uint32_t {
+      const uint32_t o = p - g_beg;
+      return o < staged ? s_ids[o] : sorted_src[p];
+    };
+    auto seg_of = [&](int lr, uint32_t& beg, uint32_t& end) {
+      beg = s_seg[lr];
+      end = s_seg[lr + 1];
+      if (end > n_src || beg > end) beg = end = 0;   // never walk outside the sorted list
+    };
+    for (int64_t chunk = 0; chunk < chunks_per_row; ++chunk) {
+      const int64_t c0 = chunk * 64 + lane, c1 = c0 + 32;
+      const bool h0 = c0 < vpr, h1 = c1 < vpr;
+      // the item sequence of a row: k = -1 is the row of self, k >= 0 the k-th source of its segment
+      int ir = 0, ik = -1;          // next item to copy
+      uint32_t ibeg, iend;
+      seg_of(0, ibeg, iend);
+      auto issue = [&](int slot) {
+        if (ir < rows) {
+          const T* rowp = nullptr;
+          if (ik < 0) {
+            rowp = self + (w0 + ir) * inner;
+          } else {
+            const uint32_t sid = id_at(ibeg + static_cast<uint32_t>(ik));
+            if (sid < n_src) rowp = src + static_cast<int64_t>(sid) * inner;   // an invalid id copies nothing
+          }
+          if (rowp) {
+            uint8_t* dst = ring + slot * 1024 + lane * 16;
+            if (h0) cp_async16(dst, rowp + c0 * V);
+            if (h1) cp_async16(dst + 512, rowp + c1 * V);
+          }
+          ++ik;
+          if (ibeg + static_cast<uint32_t>(ik) >= iend) {
+            ++ir;
+            ik = -1;
+            if (ir < rows) seg_of(ir, ibeg, iend);
+          }
+        }
+        cp_async_commit();   // one group per slot, also when nothing was copied
+      };
+#pragma unroll 1
+      for (int sl = 0; sl < kRingSlots; ++sl) issue(sl);
+
+      int cr = 0, ck = -1, slot = 0;   // item being added
+      uint32_t cbeg, cend;
+      seg_of(0, cbeg, cend);
+      A a0[V], a1[V];
+#pragma unroll 1
+      while (cr < rows) {
+        cp_async_wait<kRingSlots - 1>();   // the oldest group, the one of `slot`, has landed
+        const uint8_t* from = ring + slot * 1024 + lane * 16;
+        bool use = true;
+        if (ck >= 0) use = id_at(cbeg + static_cast<uint32_t>(ck)) < n_src;
+        if (use) {
+          VecT v0, v1;
+          if (h0) v0 = *reinterpret_cast<const VecT*>(from);
+          if (h1) v1 = *reinterpret_cast<const VecT*>(from + 512);
+          if (ck < 0) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              if (h0) a0[e] = to_accum<A>(v0.v[e]);
+              if (h1) a1[e] = to_accum<A>(v1.v[e]);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+              if (h0) a0[e] = seq_add(a0[e], to_accum<A>(v0.v[e]));
+              if (h1) a1[e] = seq_add(a1[e], to_accum<A>(v1.v[e]));
+            }
+          }
+        }
+        ++ck;
+        if (cbeg + static_cast<uint32_t>(ck) >= cend) {   // the row is complete
+          VecT* out_row = reinterpret_cast<VecT*>(out + (w0 + cr) * inner);
+          if (h0) {
+            VecT t;
+#pragma unroll
+            for (int e = 0; e < V; ++e) t.v[e] = from_accum<T>(a0[e]);
+            out_row[c0] = t;
+          }
+          if (h1) {
+            VecT t;
+#pragma unroll
+            for (int e = 0; e < V; ++e) t.v[e] = from_accum<T>(a1[e]);
+            out_row[c1] = t;
+          }
+          ++cr;
+          ck = -1;
+          if (cr < rows) seg_of(cr, cbeg, cend);
+        }
+        issue(slot);   // the slot just read takes the item kRingSlots ahead
+        slot = slot + 1 == kRingSlots ? 0 : slot + 1;
+      }
+      cp_async_wait<0>();
+    }
+  }
+}
+
 // Element form: the thread that holds the head of a segment walks it.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
@@ -728,6 +876,30 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
   const int64_t cpr = (vpr + 63) / 64;
   const int64_t items = n_dst * cpr;
   if (items == 0) return B200_OK;
+  if constexpr (MODE == 0) {
+    // B200_WALK_RING=0 keeps the register-resident walk (for A/B timing)
+    static const bool ring = [] { const char* e = getenv("B200_WALK_RING"); return !(e && e[0] == '0'); }();
+    if (ring && vec) {
+      auto kernel = segment_rows_ring_kernel<T, V, ACC32>;
+      constexpr size_t smem = static_cast<size_t>(kThreads / 32) * kWarpSmem;
+      static thread_local int last_dev = -1;
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev != last_dev) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "segment rows: %s", cudaGetErrorString(e));
+        last_dev = dev;
+      }
+      // one resident wave; every warp walks one contiguous range of destination rows
+      const int grid = wave_grid<segment_rows_ring_kernel<T, V, ACC32>>((n_dst + 7) / 8, kThreads, 1, smem);
+      const int64_t total_warps = static_cast<int64_t>(grid) * (kThreads / 32);
+      const int64_t rows_per_warp = (n_dst + total_warps - 1) / total_warps;
+      cudaError_t le = launch_pdl(kernel, grid, kThreads, smem, s, (T*)out, (const T*)self, (const T*)src, sorted_src,
+                                  seg_start, n_dst, n_src, inner, cpr, rows_per_warp);
+      B200_REQUIRE(le == cudaSuccess, B200_LAUNCH_FAILED, "segment rows: %s", cudaGetErrorString(le));
+      return check_launch("segment rows (ring)");
+    }
+  }
   int64_t need = (items + 7) / 8;
   const int64_t cap = static_cast<int64_t>(sm_count_current_device()) * 8;
   const int grid = static_cast<int>(need < cap ? need : cap);
