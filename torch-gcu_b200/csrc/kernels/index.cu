@@ -602,17 +602,16 @@ segment_rows_kernel(T* __restrict__ out, const T* __restrict__ self, const T* __
 // MODE 0 with the row reads staged through shared memory. The register-resident walk above keeps at
 // most 4 source rows (4 KB) per warp in flight and is bound by latency (49 % of DRAM throughput, 80 % of
 // stall cycles on the row loads): registers limit both the rows per warp and the warps per SM. Here every
-// warp owns a contiguous range of destination rows and a ring of kRingSlots 1 KB slots that it fills with
+// warp owns a contiguous range of destination rows and a ring of kRingSlots (4) 1 KB slots that it fills with
 // cp.async: the rows it needs, in the order it needs them (row of self, then its sources in sorted
 // order, then the next destination row ...), always kRingSlots rows ahead of the one it is adding. A lane
 // reads back exactly the 2 x 16 bytes it copied itself, so cp.async.wait_group is the only
 // synchronisation. Segment bounds and source ids of a window of rows are staged per warp (no block-wide
 // barrier anywhere). The order of additions is the one of the register walk.
-constexpr int kRingSlots = 8;
 constexpr int kWarpRows = 64;      // destination rows per staged window
 constexpr int kWarpIds = 447;      // source ids staged per window (a longer stretch is read from global)
-constexpr int kWarpSmem = kRingSlots * 1024 + (kWarpRows + 1 + kWarpIds) * 4;
-static_assert(kWarpSmem % 16 == 0, "every warp's ring starts 16-byte aligned");
+__host__ __device__ constexpr int warp_smem(int slots) { return slots * 1024 + (kWarpRows + 1 + kWarpIds) * 4; }
+static_assert(warp_smem(4) % 16 == 0 && warp_smem(1) % 16 == 0, "every warp's ring starts 16-byte aligned");
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
@@ -622,8 +621,8 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src)
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <typename T, int V, bool ACC32>
-__global__ void __launch_bounds__(kThreads, 2)
+template <typename T, int V, bool ACC32, int kRingSlots, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 segment_rows_ring_kernel(T* out, const T* self, const T* __restrict__ src,
                          const uint32_t* __restrict__ sorted_src, const uint32_t* __restrict__ seg_start,
                          int64_t n_dst, int64_t n_src, int64_t inner /* elements per row */,
@@ -634,6 +633,7 @@ segment_rows_ring_kernel(T* out, const T* self, const T* __restrict__ src,
   using A = typename AccT<T, ACC32>::type;
   extern __shared__ __align__(16) uint8_t ring_smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kWarpSmem = warp_smem(kRingSlots);
   uint8_t* ring = ring_smem + warp * kWarpSmem;
   uint32_t* s_seg = reinterpret_cast<uint32_t*>(ring + kRingSlots * 1024);
   uint32_t* s_ids = s_seg + kWarpRows + 1;
@@ -880,8 +880,11 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
     // B200_WALK_RING=0 keeps the register-resident walk (for A/B timing)
     static const bool ring = [] { const char* e = getenv("B200_WALK_RING"); return !(e && e[0] == '0'); }();
     if (ring && vec) {
-      auto kernel = segment_rows_ring_kernel<T, V, ACC32>;
-      constexpr size_t smem = static_cast<size_t>(kThreads / 32) * kWarpSmem;
+      // 4 slots and three blocks per SM: measured 114 us per scatter_add call against 117 (8 slots, two blocks),
+      // 119 (10, two) and 162 (16, one): past a few KB per warp, more warps are worth more than a deeper ring
+      constexpr int kSlots = 4, kBlocksPerSm = 3;
+      auto kernel = segment_rows_ring_kernel<T, V, ACC32, kSlots, kBlocksPerSm>;
+      constexpr size_t smem = static_cast<size_t>(kThreads / 32) * warp_smem(kSlots);
       static thread_local int last_dev = -1;
       int dev = 0;
       cudaGetDevice(&dev);
@@ -891,7 +894,7 @@ b200Status launch_segment_rows(void* out, const void* self, const void* src, con
         last_dev = dev;
       }
       // one resident wave; every warp walks one contiguous range of destination rows
-      const int grid = wave_grid<segment_rows_ring_kernel<T, V, ACC32>>((n_dst + 7) / 8, kThreads, 1, smem);
+      const int grid = wave_grid<segment_rows_ring_kernel<T, V, ACC32, kSlots, kBlocksPerSm>>((n_dst + 7) / 8, kThreads, 1, smem);
       const int64_t total_warps = static_cast<int64_t>(grid) * (kThreads / 32);
       const int64_t rows_per_warp = (n_dst + total_warps - 1) / total_warps;
       cudaError_t le = launch_pdl(kernel, grid, kThreads, smem, s, (T*)out, (const T*)self, (const T*)src, sorted_src,
