@@ -414,12 +414,23 @@ radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __res
   scatter_tile(keys_in, vals_in, keys_out, vals_out, n, pass, nblocks, blockIdx.x, hist_scanned, totals, sm);
 }
 
+// seg_start[d] = first sorted position whose key is >= d, for d in [0, n_dst]; positions first, first + stride, ...
+__device__ __forceinline__ void segment_bounds(const uint32_t* sorted_keys, int64_t n, int64_t n_dst, uint32_t* seg_start,
+                                               int64_t first, int64_t stride) {
+  for (int64_t p = first; p <= n; p += stride) {
+    const int64_t lo = p == 0 ? 0 : static_cast<int64_t>(sorted_keys[p - 1] & 0x7fffffffu) + 1;
+    int64_t hi = p == n ? n_dst : static_cast<int64_t>(sorted_keys[p] & 0x7fffffffu);
+    if (hi > n_dst) hi = n_dst;
+    for (int64_t d = lo; d <= hi; ++d) seg_start[d] = static_cast<uint32_t>(p);
+  }
+}
+
 // All passes in one cooperative launch: histogram, row scans and scatter of a pass are
 // separated by grid-wide barriers instead of kernel boundaries (three launches per pass
 // otherwise, each a few microseconds of ramp for a few hundred kilobytes of keys).
 __global__ void __launch_bounds__(kSortThreads)
 radix_sort_fused_kernel(uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a, uint32_t* vals_b, int64_t n, int passes,
-                        int nblocks, uint32_t* hist, uint32_t* totals) {
+                        int nblocks, uint32_t* hist, uint32_t* totals, uint32_t* seg_start, int64_t n_dst) {
   namespace cg = cooperative_groups;
   cg::grid_group grid = cg::this_grid();
   __shared__ ScatterSmem sm;
@@ -437,19 +448,17 @@ radix_sort_fused_kernel(uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a, ui
     vout = vother;
     vother = vin;
   }
+  // the segment bounds of the sorted keys, when the caller wants them (the last pass ended with a grid barrier)
+  if (seg_start)
+    segment_bounds(kin, n, n_dst, seg_start, static_cast<int64_t>(blockIdx.x) * kSortThreads + threadIdx.x,
+                   static_cast<int64_t>(gridDim.x) * kSortThreads);
 }
 
-// seg_start[d] = first sorted position whose key is >= d, for d in [0, n_dst].
 __global__ void __launch_bounds__(kThreads)
 segment_bounds_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n, int64_t n_dst,
                       uint32_t* __restrict__ seg_start) {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
-  for (int64_t p = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; p <= n; p += stride) {
-    const int64_t lo = p == 0 ? 0 : static_cast<int64_t>(sorted_keys[p - 1] & 0x7fffffffu) + 1;
-    int64_t hi = p == n ? n_dst : static_cast<int64_t>(sorted_keys[p] & 0x7fffffffu);
-    if (hi > n_dst) hi = n_dst;
-    for (int64_t d = lo; d <= hi; ++d) seg_start[d] = static_cast<uint32_t>(p);
-  }
+  segment_bounds(sorted_keys, n, n_dst, seg_start, static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x,
+                 static_cast<int64_t>(gridDim.x) * kThreads);
 }
 
 // keys for the row form: the destination row of every source row.
@@ -795,7 +804,9 @@ SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range) */, in
 // Runs the sort. On return *sorted_keys / *sorted_vals point into the workspace.
 b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a,
                     uint32_t* vals_b, uint32_t* hist, cudaStream_t s, uint32_t** sorted_keys,
-                    uint32_t** sorted_vals) {
+                    uint32_t** sorted_vals, uint32_t* seg_start = nullptr, int64_t n_dst = 0,
+                    bool* bounds_done = nullptr) {
+  if (bounds_done) *bounds_done = false;
   uint32_t *kin = keys_a, *kout = keys_b, *vin = nullptr, *vout = vals_a, *vother = vals_b;
   uint32_t* totals = hist + static_cast<size_t>(256) * p.nblocks;
   // one cooperative launch when the device can hold the grid, else three launches per pass
@@ -818,10 +829,11 @@ b200Status run_sort(const SortPlan& p, uint32_t* keys_a, uint32_t* keys_b, uint3
     if (grid > coop_blocks) grid = coop_blocks;
     int64_t n = p.n;
     int passes = p.passes, nblocks = p.nblocks;
-    void* args[] = {&keys_a, &keys_b, &vals_a, &vals_b, &n, &passes, &nblocks, &hist, &totals};
+    void* args[] = {&keys_a, &keys_b, &vals_a, &vals_b, &n, &passes, &nblocks, &hist, &totals, &seg_start, &n_dst};
     fused = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(radix_sort_fused_kernel), dim3(grid), dim3(kSortThreads), args, 0, s) ==
             cudaSuccess;
     if (!fused) cudaGetLastError();
+    else if (bounds_done && seg_start) *bounds_done = true;
   }
   for (int pass = 0; pass < p.passes; ++pass) {
     if (!fused) {
@@ -950,10 +962,11 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   else
     row_keys_kernel<int32_t><<<kgrid, kThreads, 0, s>>>((const int32_t*)index->data, index_stride, n_src, n_dst, wrap_negative, keys_a);
   uint32_t *sk, *sv;
-  b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv);
+  bool bounds_done = false;   // the one-launch sort also writes the segment bounds
+  b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv, seg, n_dst, &bounds_done);
   if (st != B200_OK) return st;
-  segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
-  note_launches(2);   // key generation and this one; the sort and the segment walk count themselves
+  if (!bounds_done) segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
+  note_launches(bounds_done ? 1 : 2);   // key generation (and the bounds); the sort and the segment walk count themselves
   if (mode == 1) return launch_segment_rows<T, 1, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   if (mode == 2 && sizeof(T) == 2) return launch_segment_rows<T, 0, true>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   return launch_segment_rows<T, 0, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
