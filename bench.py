@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Headline (BASELINE.json: "bf16 TP decoder tokens/s at 1/2/4/8 B200"): one step is
+Headline metric ("bf16 TP decoder tokens/s at 1/2/4/8 B200"): one step is
 one prefill pass (batch 8 x sequence 2048) of a stack of 8 Llama-style decoder
 layers (hidden 4096, 32 query / 8 KV heads, head_dim 128, FFN 14336, bf16
 weights, random init) run on the "gcu" PrivateUse1 device: every operator goes

@@ -1,4 +1,4 @@
-"""Full-size BASELINE configurations 1-3 through the C ABI: direct comparison
+"""Full-size workload configurations 1-3 of the benchmark through the C ABI: direct comparison
 with CPU ATen where the CPU finishes in seconds, plus size-independent
 properties (linearity of scatter_add, gather/scatter round trip, idempotence)."""
 import pytest

@@ -1,4 +1,4 @@
-"""Operator sweep of the benchmark: BASELINE configurations 1-3 (the fp32
+"""Operator sweep of the benchmark: workload configurations 1-3 (the fp32
 (4096,4096) op sweep, the index ops on the bf16 (128256,4096) table, the fused
 bf16 RMSNorm / RoPE / SwiGLU ops), every operator called through the C ABI of
 libb200ops.so with its full-size seeded inputs resident in HBM.
