@@ -13,8 +13,10 @@ is followed by an all-reduce through the registered "eccl" process group
 (NCCL / NVLink). N ranks = tensor parallel degree N: strong scaling.
 
   value     prefill tokens/s of the whole job, inputs resident in HBM
-  e2e       same with the input hidden states in pinned HOST memory: H2D copy,
-            the stack, D2H copy of the output, all inside the timed region
+  e2e       same with the input hidden states in pinned HOST memory: H2D copy (on
+            every rank), the stack, D2H copy of the output, all inside the timed region
+  parity    batch element 0 of the timed prefill output against the unsharded CPU
+            stack, at every N; the run fails when it does not hold
   decode    one-token step at batch 64 against a 4096-token bf16 KV cache
   roofline  the dominant kernel of the step (the gate/up GEMM), timed live
   ops       (N = 1) "op HBM GB/s": every bandwidth-bound operator of configs 1-3
@@ -66,6 +68,29 @@ def layer_flops(tokens_b, seq, tp=1):
     gemm = 2 * m * h * ((hq + 2 * hk) * d + hq * d + 2 * f + f) / tp
     attn = 4 * tokens_b * hq * seq * seq * d / 2 / tp
     return gemm + attn
+
+
+def prefill_parity(y_b0, x_b0):
+    """Batch element 0 of the stack's prefill output (any tensor-parallel degree) against the
+    unsharded 8-layer stack computed by PyTorch CPU ATen in fp32 on the same bf16 weights and
+    input. The device path rounds to bf16 between its launches and, with more than one rank,
+    sums the row-parallel partial products in another order, so the bound is a bf16 one:
+    relative error of the whole output in the 2-norm below 3e-2."""
+    import workloads
+    from tp_decoder import reference_layer_cpu
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    h = x_b0.float()
+    for i in range(N_LAYERS):
+        w = workloads.decoder_layer_weights(seed=i, dtype=torch.bfloat16, **CFG)
+        h = reference_layer_cpu(h, w, **CFG)
+        del w
+    y = y_b0.float()
+    rel = ((y - h).norm() / h.norm()).item()
+    finite = bool(torch.isfinite(y).all())
+    return {"rel": round(rel, 5), "tol": 3e-2, "ok": finite and rel < 3e-2, "max_abs": round((y - h).abs().max().item(), 4),
+            "checked": "batch element 0 (2048 tokens) of the timed prefill output vs the unsharded fp32 CPU ATen stack",
+            "cpu_s": round(time.perf_counter() - t0, 1)}
 
 
 # ------------------------------------------------------------------- clocks --
@@ -142,6 +167,9 @@ def run_gpu(args):
             os.environ.setdefault("NCCL_MAX_NCHANNELS", "8")
         dist.init_process_group("eccl", rank=rank, world_size=world)
         group = dist.group.WORLD
+        # every collective of the backend against its known answer on these N ranks (untimed)
+        import collective_check
+        collectives_checked = collective_check.run(dev, rank, world)
     bf = torch.bfloat16
     stack = DecoderStack(N_LAYERS, world, rank, "gcu", dev, bf, CFG)
     g = torch.Generator().manual_seed(1234)
@@ -197,6 +225,15 @@ def run_gpu(args):
             step()
     else:
         step = lambda: stack.prefill(x, group)  # noqa: E731
+    # correctness of what is about to be timed, on this N: the output of the timed path (the graph's
+    # output buffer when replaying) for batch element 0 against the CPU. Every rank holds the same
+    # output; rank 0 checks it while the others wait at the barrier that opens the timed region.
+    y_timed = y_x if use_graph else stack.prefill(x, group)
+    torch.gcu.synchronize()
+    parity = None
+    if rank == 0 and not args.no_parity:
+        parity = prefill_parity(y_timed[0:1].cpu(), x_host[0:1])
+    del y_timed
     launches_before = b200ops.launch_count()
     with ClockSampler(local) as clocks:
         prefill_ms = timed(step, steps)
@@ -217,10 +254,9 @@ def run_gpu(args):
     downloaded = [None, None]   # event: the result of the pass of slot i has reached the host
 
     def upload(slot):
-        # rank 0 reads the host buffer (on the copy stream, under the previous step); the other ranks
-        # get the input over NVLink, see the broadcast in the loop
-        if rank != 0:
-            return
+        # every rank reads its own pinned copy of the step's input over its own PCIe link, on its copy
+        # stream, under the previous step's compute (activations are replicated under tensor
+        # parallelism, so each rank needs all of it; no collective and no SM is spent on the input)
         with torch.gcu.stream(s_in):
             if consumed[slot] is not None:
                 s_in.wait_event(consumed[slot])
@@ -234,12 +270,7 @@ def run_gpu(args):
             slot = i & 1
             if i + 1 < n:
                 upload(slot ^ 1)
-            if rank == 0:
-                cur.wait_event(uploaded[slot])
-            if world > 1:
-                # one broadcast instead of every rank pulling the same bytes through the host's memory; it is
-                # issued on the compute stream, so it never runs beside the step's own collectives
-                dist.broadcast(x_dev[slot], src=0)
+            cur.wait_event(uploaded[slot])
             if use_graph:
                 if downloaded[slot] is not None:
                     cur.wait_event(downloaded[slot])   # the replay overwrites the slot's output buffer
@@ -317,7 +348,9 @@ def run_gpu(args):
                        "l2": "activations (134 MB) and per-layer weights (436 MB) exceed the 126 MB L2"},
             "clocks": clocks.summary(),
             "e2e": {"value": round(tokens / e2e_ms * 1e3, 1), "unit": UNIT,
-                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": x_host.numel() * 2},
+                    "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2,
+                    "copies": "every rank uploads the input from its own pinned buffer; rank 0 reads the result back"},
+            "parity": parity,
             "gpu_launches": gpu_launches, "graph_replay": use_graph if graph_error is None else "failed: " + graph_error,
             "prefill": {"tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1),
                         "frac_of_bf16_sustained": round(flops_rank / prefill_ms / 1e9 / tf_sust, 3)},
@@ -337,10 +370,14 @@ def run_gpu(args):
             ops_section(result, args, hbm_peak, peak_kind)
             if not args.no_cpu:
                 result["cpu_baseline"] = cpu_baseline()
+        if world > 1:
+            result["collectives"] = {"ok": True, "ranks": world, "checked": collectives_checked}
         print(json.dumps(result), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if rank == 0 and parity is not None and not parity["ok"]:
+        raise SystemExit("bench.py: the prefill output does not match the CPU reference: %s" % json.dumps(parity))
 
 
 def _time_gcu(fn, reps=10):
@@ -365,7 +402,7 @@ def gemm_roofline(dev, tf_peak, peak_kind, world):
     w = (torch.randn(n, k) * 0.02).bfloat16().to(dev)
     ms = _time_gcu(lambda: efficient.linear_swiglu(a, w))
     tf = 2 * m * n * k / ms / 1e9
-    # DRAM traffic per launch, scaled from a smaller capture of the same kernel (profiles/): the tile walk keeps a
+    # DRAM traffic per launch, scaled from a smaller profiler capture of the same kernel: the tile walk keeps a
     # band of 16 row-tiles of A in L2 and streams the weight once per band, so traffic = A + W x bands + out; the
     # capture at 8192 x (2 x 4096) x 4096 (2 bands) moved 305.3 MB against 268.4 MB by that count (x 1.14, L2 misses
     # inside a band), and the same factor is applied to this launch's counts.
@@ -402,12 +439,17 @@ def ops_section(result, args, hbm_peak, peak_kind):
     import bench_ops
     cdev = torch.device("cuda", 0)
     ops, op_ms = bench_ops.measure_ops(cdev, max(3, min(args.steps, 5)), args.warmup, args.only)
+    cpu_rows = {} if args.no_cpu else {n: (s, b) for n, s, b in bench_ops.cpu_op_times(1.0, 2)}
     table = []
     for op, ms in zip(ops, op_ms):
         gbs = op.bytes / ms / 1e6
-        table.append({"op": op.name, "ms": round(ms, 4), "bytes": op.bytes, "gbs": round(gbs, 1),
-                      "frac_of_measured": round(gbs / hbm_peak, 3), "frac_of_8tbs": round(gbs / NOMINAL_HBM_GBS, 3),
-                      "launches": op.launches})
+        row = {"op": op.name, "ms": round(ms, 4), "bytes": op.bytes, "gbs": round(gbs, 1),
+               "frac_of_measured": round(gbs / hbm_peak, 3), "frac_of_8tbs": round(gbs / NOMINAL_HBM_GBS, 3),
+               "launches": op.launches}
+        if op.name in cpu_rows:   # PyTorch CPU ATen on the same tensors, all host threads
+            s, b = cpu_rows[op.name]
+            row["cpu_ms"], row["cpu_gbs"] = round(s * 1e3, 3), round(b / s / 1e9, 2)
+        table.append(row)
     pass_ms, pass_bytes = sum(op_ms), sum(op.bytes for op in ops)
     e2e_ms, h2d, d2h = bench_ops.e2e_pass_ms(cdev, ops, 2)
     result["ops"] = table
@@ -415,6 +457,12 @@ def ops_section(result, args, hbm_peak, peak_kind):
                           "frac_of_measured": round(pass_bytes / pass_ms / 1e6 / hbm_peak, 3), "peak": hbm_peak,
                           "peak_kind": peak_kind, "timing": "%d rotating buffer sets per operator" % bench_ops.NSETS,
                           "e2e_gbs": round(pass_bytes / e2e_ms / 1e6, 2), "h2d_bytes": h2d, "d2h_bytes": d2h}
+    if cpu_rows:
+        cpu_s = sum(s for s, _ in cpu_rows.values())
+        result["op_sweep"]["cpu"] = {"gbs": round(pass_bytes / cpu_s / 1e9, 2), "pass_ms": round(cpu_s * 1e3, 1),
+                                     "cores": torch.get_num_threads(), "kind": "port",
+                                     "sample": "PyTorch CPU ATen, the same 16 operators on the same full-size tensors, best of 2; "
+                                               "index_put under deterministic algorithms"}
 
 
 # ------------------------------------------------------------------ CPU arm --
@@ -466,8 +514,8 @@ def run_reference(args):
 
 
 def run_micro(name):
-    """One operator, a few launches, a case a little larger than L2: the command the
-    `ncu --set full` captures under profiles/ are taken from."""
+    """One operator, a few launches, a case a little larger than L2: the command for
+    single-kernel profiler captures."""
     import b200ops as ops
     import ctypes
     dev = torch.device("cuda", 0)
@@ -549,6 +597,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-parity", action="store_true", help="skip the CPU check of the prefill output (profiling aid)")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
     ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | sdpa | sdpa_bwd | decode | swiglu | scatter: a 3-launch case for profiler captures")
     args = ap.parse_args()

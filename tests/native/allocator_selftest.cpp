@@ -1,7 +1,8 @@
 // Exercises the stream-ordered caching policy against a fake device backend
 // (host malloc, manually completed events), so the allocator logic is testable
 // on a machine without a GPU. Returns the observations as a dict; the Python
-// test asserts on them.
+// test asserts on them. Built into the test-only module (selftest_module.cpp),
+// never into the product extension.
 #include <torch/csrc/utils/pybind.h>
 
 #include <algorithm>
@@ -150,6 +151,30 @@ py::dict allocator_selftest() {
     r["plain_frees_after_release"] = fb->plain_frees; // 1: the cached block; `out` is still alive
     a.free(out);
     r["plain_frees_after_output_died"] = fb->plain_frees;  // 2
+  }
+
+  // 4c. a block that another stream used, freed while a capture is open: no event may be recorded
+  // then (it could land inside the capture and never become queryable), so the block is parked and
+  // gets its events when the capture has closed
+  {
+    void* shared = a.malloc(0, 3000, s1);
+    a.record_stream(shared, s2);
+    const size_t events_before = fb->events.size();
+    const uint64_t pool = a.begin_capture(0, s1);
+    a.free(shared);
+    r["no_event_recorded_during_capture"] = fb->events.size() == events_before;
+    a.end_capture(0, s1);
+    r["event_recorded_after_capture"] = fb->events.size() == events_before + 1;
+    void* other = a.malloc(0, 3000, s1);     // the event has not completed: the block stays away
+    r["parked_block_not_reused_early"] = (other != shared);
+    for (FakeEvent* e : fb->events) e->done = true;
+    a.free(other);
+    void* again1 = a.malloc(0, 3000, s1);
+    void* again2 = a.malloc(0, 3000, s1);
+    r["parked_block_reused_after_event"] = (again1 == shared || again2 == shared);
+    a.free(again1);
+    a.free(again2);
+    a.release_pool(pool);
   }
 
   // 5. stats and empty_cache

@@ -130,6 +130,23 @@ def test_config_ops_through_dispatcher(dev):
         torch.use_deterministic_algorithms(False)
     got = base.to(dev).index_put_((rows.to(dev),), vals.to(dev), accumulate=True)
     assert torch.equal(got.cpu(), ref)
+    # two index tensors: linearised on the host, every dimension range-checked as ATen does
+    base2 = torch.zeros(6, 5, 4)
+    i0, i1 = torch.tensor([0, 5, -1, 2, 5]), torch.tensor([4, 0, -5, 3, 0])
+    v2 = torch.randn(5, 4, generator=g)
+    torch.use_deterministic_algorithms(True)
+    try:
+        ref2 = base2.clone().index_put_((i0, i1), v2, accumulate=True)
+    finally:
+        torch.use_deterministic_algorithms(False)
+    got2 = base2.to(dev).index_put_((i0.to(dev), i1.to(dev)), v2.to(dev), accumulate=True)
+    assert torch.equal(got2.cpu(), ref2)
+    for bad0, bad1 in ((torch.tensor([0]), torch.tensor([5])), (torch.tensor([0]), torch.tensor([-6])),
+                       (torch.tensor([6]), torch.tensor([0]))):
+        with pytest.raises(IndexError):   # not folded into a neighbouring row
+            base2.to(dev).index_put_((bad0.to(dev), bad1.to(dev)), v2[:1].to(dev), accumulate=True)
+        with pytest.raises(IndexError):
+            base2.clone().index_put_((bad0, bad1), v2[:1], accumulate=True)
     run_op_test(lambda t, i: t[i], dev, src, rows[:7] % 50, exact=True)
     run_op_test(lambda t: torch.cat([t, t * 2], dim=-1), dev, src, exact=True)
     run_op_test(lambda t: t.pow(2).mean(-1, keepdim=True).add(1e-6).rsqrt(), dev, src, rtol=1e-5, atol=1e-6)

@@ -47,8 +47,26 @@ def test_autocast_state_accessors(torch_gcu):
     assert isinstance(torch.gcu.amp.autocast(), torch.amp.autocast_mode.autocast)
 
 
-def test_caching_allocator_policy(torch_gcu):
-    r = torch_gcu._C._allocator_selftest()
+@pytest.fixture(scope="module")
+def selftest():
+    """The test-only native module (tests/native): the product's allocator and watchdog sources
+    compiled together with fakes of the device and of the communicator."""
+    import importlib.util
+    import torch  # noqa: F401  (its libraries must be loaded first)
+    path = os.path.join(ROOT, "tests", "native", "_gcu_selftest.so")
+    assert os.path.exists(path), "tests/native/_gcu_selftest.so is built by __graft_entry__.build()"
+    spec = importlib.util.spec_from_file_location("_gcu_selftest", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_product_extension_carries_no_test_harness(torch_gcu):
+    assert not hasattr(torch_gcu._C, "_allocator_selftest")
+
+
+def test_caching_allocator_policy(selftest):
+    r = selftest.allocator_selftest()
     assert r["round_small"] == 1024 and r["round_large"] == 2 << 20
     assert r["same_stream_reuse"] and r["backend_allocs_after_reuse"] == 1
     assert r["cross_stream_no_reuse"]
@@ -58,7 +76,9 @@ def test_caching_allocator_policy(torch_gcu):
     assert r["capture_ignores_general_cache"] and r["capture_reuses_own_block"]
     assert r["eager_does_not_get_pool_block"] and r["eager_gets_general_block"]
     assert r["plain_allocs_in_capture"] == 2 and r["plain_frees_after_release"] == 1
-    assert r["plain_frees_after_output_died"] == 2
+    assert r["plain_frees_after_output_died"] == 2   # the last live block of a released pool (pool erased after it)
+    assert r["no_event_recorded_during_capture"] and r["event_recorded_after_capture"]
+    assert r["parked_block_not_reused_early"] and r["parked_block_reused_after_event"]
     assert r["allocated_after_all_freed"] == 0 and r["reserved_after_empty_cache"] == 0
     assert r["backend_outstanding"] == 0 and r["cache_hits"] >= 3
 
@@ -105,6 +125,76 @@ def test_process_group_argument_checks(torch_gcu):
     with pytest.raises(RuntimeError):  # host tensors are rejected before anything is launched
         pg.allreduce([torch.zeros(4)])
     pg.shutdown()
+
+
+def _wait_until(cond, seconds=5.0):
+    import time
+    end = time.monotonic() + seconds
+    while time.monotonic() < end:
+        if cond():
+            return True
+        time.sleep(0.01)
+    return cond()
+
+
+def test_watchdog_times_out_a_work_that_never_completes(selftest):
+    """Failure made on the host: a collective whose completion query never turns true. After its
+    100 ms timeout the watchdog sets the work's exception, aborts the communicator exactly once,
+    fails what else was outstanding, and refuses later works (reference: checkTimeout /
+    watchdogHandler, torch_gcu/csrc/distributed/ProcessGroupECCL.cpp:533-556, :1485-1616)."""
+    aborts = []
+    wd = selftest.Watchdog(lambda: "", lambda: aborts.append(1), 10)
+    try:
+        done = selftest.FakeWork(lambda: True, 100, 1)
+        stuck = selftest.FakeWork(lambda: False, 100, 2)
+        bystander = selftest.FakeWork(lambda: False, 60_000, 3)   # far from its own timeout
+        for w in (done, stuck, bystander):
+            wd.watch(w)
+        assert _wait_until(lambda: done.finished)
+        assert not done.failed and done.exception_text == ""
+        assert _wait_until(lambda: wd.has_failed and wd.abort_calls == 1 and wd.outstanding() == 0)
+        assert "DistBackendError" in stuck.exception_text
+        assert "collective (seq 2) did not complete within 100 ms" in stuck.exception_text
+        assert not stuck.finished
+        assert "seq 3" in bystander.exception_text and "communicator was aborted" in bystander.exception_text
+        assert "seq 2" in bystander.exception_text      # carries the cause
+        assert "seq 2" in wd.failure()
+        late = selftest.FakeWork(lambda: True, 100, 4)
+        with pytest.raises(RuntimeError, match="aborted after an earlier failure"):
+            wd.watch(late)
+        assert late.failed and wd.outstanding() == 0
+        import time
+        time.sleep(0.1)
+        assert aborts == [1] and wd.abort_calls == 1     # the abort hook ran once, not once per sweep
+    finally:
+        wd.stop()
+
+
+def test_watchdog_turns_an_async_communicator_error_into_the_works_exception(selftest):
+    """The communicator's asynchronous-error poll (ncclCommGetAsyncError in the product) answers
+    with an error while two works are out: both fail with that text, one abort (reference:
+    checkForECCLErrors, ProcessGroupECCL.cpp:1682-1700)."""
+    state = {"err": ""}
+    aborts = []
+    wd = selftest.Watchdog(lambda: state["err"], lambda: aborts.append(1), 10)
+    try:
+        a = selftest.FakeWork(lambda: False, 60_000, 7)
+        b = selftest.FakeWork(lambda: False, 60_000, 8)
+        wd.watch(a)
+        wd.watch(b)
+        import time
+        time.sleep(0.1)
+        assert not wd.has_failed and wd.outstanding() == 2 and not a.failed
+        state["err"] = "unhandled system error (fake: peer closed the connection)"
+        assert _wait_until(lambda: wd.has_failed and wd.abort_calls == 1)
+        for w, seq in ((a, 7), (b, 8)):
+            assert "asynchronous error" in w.exception_text and "peer closed the connection" in w.exception_text
+            assert "seq %d" % seq in w.exception_text
+        assert aborts == [1]
+        with pytest.raises(RuntimeError, match="peer closed the connection"):
+            wd.watch(selftest.FakeWork(lambda: True, 100, 9))
+    finally:
+        wd.stop()
 
 
 def test_tensor_parallel_sharding_gloo_world2():

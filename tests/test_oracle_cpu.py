@@ -89,3 +89,25 @@ def test_bf16_rounding_rule():
     # and vectorised CPU casts disagree on it).
     n = seq_ref.f32_to_bf16_bits(np.array([np.nan], dtype=np.float32))
     assert np.isnan(seq_ref.bf16_bits_to_f32(n))[0]
+
+
+def test_sdpa_formula_oracle_is_pinned_to_aten_cpu_kernel():
+    """The fp32 formula used as the attention oracle against ATen's own CPU kernel -- the one the
+    reference backend's op check compares a device result with
+    (torch_gcu/csrc/aten/GCUNativeFunctions.cpp:49-102): causal, grouped-query, fp32 and bf16."""
+    g = torch.Generator().manual_seed(11)
+    for (B, Hq, Hkv, S, D) in [(2, 8, 2, 160, 128), (1, 4, 4, 77, 64), (1, 6, 1, 300, 128)]:
+        q, k, v = (torch.randn(B, h, S, D, generator=g) for h in (Hq, Hkv, Hkv))
+        out, lse = aten_cpu.sdpa_causal(q, k, v)
+        aten = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        assert torch.allclose(out, aten, rtol=1e-5, atol=1e-5)
+        # the op the reference registers, with its logsumexp output
+        G = Hq // Hkv
+        res = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(
+            q, k.repeat_interleave(G, 1), v.repeat_interleave(G, 1), 0.0, True)
+        assert torch.allclose(out, res[0], rtol=1e-5, atol=1e-5)
+        assert torch.allclose(lse, res[1], rtol=1e-5, atol=1e-5)
+        qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
+        ob, _ = aten_cpu.sdpa_causal(qb, kb, vb)
+        atb = torch.nn.functional.scaled_dot_product_attention(qb, kb, vb, is_causal=True, enable_gqa=True)
+        assert torch.allclose(ob.float(), atb.float(), rtol=1.6e-2, atol=1e-2)

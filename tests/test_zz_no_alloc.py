@@ -2,7 +2,8 @@
 callers that cannot call cudaMalloc while they run -- a serving loop that must
 not serialise the device, a plugin that is handed nothing but input and output
 buffers. Called through the C ABI twice in a row and compared bit for bit with
-the workspace-taking entry point; it must also refuse a problem whose scratch
+the workspace-taking entry point and with the CPU oracle (torch.scatter_add on
+the same values); it must also refuse a problem whose scratch
 does not fit the built-in array. This file sorts last so that a run that stops
 at the first failure has already run everything else."""
 import pytest
@@ -31,6 +32,9 @@ def test_static_scratch_scatter_add_matches_twice(ops):
         ops.scatter_add_static(got, base, 0, rows[:, None].expand(-1, inner), src)
         torch.cuda.synchronize()
         assert torch.equal(got, want), "call %d differs" % call  # integer-ordered fp32 adds: bit exact
+        from oracle import aten_cpu
+        cpu = aten_cpu.scatter_add(base.cpu(), 0, rows.cpu()[:, None].expand(-1, inner), src.cpu())
+        assert torch.equal(got.cpu(), cpu), "call %d differs from the CPU oracle" % call
     assert ops.device_error_fetch() == 0
 
 

@@ -38,6 +38,7 @@ def build(verbose=False, force=False):
         os.environ["CC"] = "/usr/bin/gcc"
     from torch.utils import cpp_extension
     sources = sorted(glob.glob(os.path.join(HOST, "**", "*.cpp"), recursive=True))
+    build_selftest(verbose, force)
     nccl_inc, nccl_lib = _nccl_paths()
     build_dir = os.path.join(HERE, "build", "host")
     os.makedirs(build_dir, exist_ok=True)
@@ -69,6 +70,43 @@ def build(verbose=False, force=False):
     built = os.path.join(build_dir, "_C.so")
     target = os.path.join(PKG, "_C.so")
     shutil.copy2(built, target)
+    return target
+
+
+def build_selftest(verbose=False, force=False):
+    """tests/native/_gcu_selftest.so: the host-side policies (caching allocator, collective
+    watchdog) compiled together with fakes of the device and of the communicator, for the CPU
+    test-suite. Test infrastructure: the product never loads it."""
+    if os.path.exists("/usr/bin/g++"):
+        os.environ["CXX"] = "/usr/bin/g++"
+        os.environ["CC"] = "/usr/bin/gcc"
+    from torch.utils import cpp_extension
+    native = os.path.join(ROOT, "tests", "native")
+    sources = sorted(glob.glob(os.path.join(native, "*.cpp"))) + [
+        os.path.join(HOST, "runtime", "gcu_allocator.cpp"), os.path.join(HOST, "runtime", "gcu_runtime.cpp"),
+        os.path.join(HOST, "distributed", "work_watchdog.cpp")]
+    target = os.path.join(native, "_gcu_selftest.so")
+    deps = sources + glob.glob(os.path.join(HOST, "runtime", "*.h")) + glob.glob(os.path.join(HOST, "distributed", "*.h"))
+    if os.path.exists(target) and not force and os.path.getmtime(target) > max(os.path.getmtime(p) for p in deps):
+        return target
+    build_dir = os.path.join(HERE, "build", "selftest")
+    os.makedirs(build_dir, exist_ok=True)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    cpp_extension._write_ninja_file_and_build_library(
+        name="_gcu_selftest",
+        sources=sources,
+        extra_cflags=["-O1", "-std=c++17", "-fvisibility=hidden", "-Wno-deprecated-declarations"],
+        extra_cuda_cflags=[],
+        extra_sycl_cflags=[],
+        extra_ldflags=["-L" + os.path.join(cuda_home, "lib64"), "-lcudart_static", "-lrt", "-ldl", "-lpthread"],
+        extra_include_paths=[HOST, os.path.join(ROOT, "include"), os.path.join(cuda_home, "include")],
+        build_directory=build_dir,
+        verbose=verbose,
+        with_cuda=False,
+        with_sycl=False,
+        is_standalone=False,
+    )
+    shutil.copy2(os.path.join(build_dir, "_gcu_selftest.so"), target)
     return target
 
 

@@ -191,13 +191,23 @@ at::Tensor& _index_put_impl_(at::Tensor& self, const c10::List<std::optional<at:
   if (k == 1) {
     lin = index_on_device(idx[0], self);
   } else {
-    // several index tensors: wrap and linearise on the host (small), one upload
+    // several index tensors: wrap, range-check and linearise on the host (small), one upload. The
+    // copies of the indices to the host synchronise with the device, so this form cannot be recorded
+    // into a graph; the one-index form stays on the device.
     std::vector<at::Tensor> host;
     for (auto& t : idx) host.push_back(t.to(at::kCPU, at::kLong));
     host = at::expand_outplace(host);
     at::Tensor acc = at::zeros_like(host[0]);
     for (int64_t d = 0; d < k; ++d) {
       at::Tensor w = at::where(host[d] < 0, host[d] + self.size(d), host[d]);
+      // checked per dimension, as ATen does: once linearised, an index one past the end of a
+      // trailing dimension would name a valid element of the next row
+      if (w.numel() > 0) {
+        const int64_t lo = w.min().item<int64_t>(), hi = w.max().item<int64_t>();
+        const int64_t bad = lo < 0 ? lo - self.size(d) : hi;
+        TORCH_CHECK_INDEX(lo >= 0 && hi < self.size(d), "index ", bad, " is out of bounds for dimension ", d, " with size ",
+                          self.size(d));
+      }
       acc = acc * self.size(d) + w;
     }
     lin = acc.to(self.device());

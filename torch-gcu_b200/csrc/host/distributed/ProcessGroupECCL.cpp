@@ -131,6 +131,11 @@ bool ProcessGroupECCL::WorkECCL::wait(std::chrono::milliseconds) {
   return true;
 }
 
+void ProcessGroupECCL::WorkECCL::markFinished() {
+  future_->markCompleted(c10::IValue(outputs_));
+  stashed_.clear();
+}
+
 void ProcessGroupECCL::WorkECCL::abort() {
   setException(std::make_exception_ptr(
       c10::DistBackendError(c10::SourceLocation{__func__, __FILE__, static_cast<uint32_t>(__LINE__)}, "eccl work aborted")));
@@ -145,16 +150,13 @@ ProcessGroupECCL::ProcessGroupECCL(const c10::intrusive_ptr<c10d::Store>& store,
   // TORCH_ECCL_BLOCKING_WAIT (reference: ProcessGroupECCL.hpp:44-149, .cpp:719-756)
   auto bw = c10::utils::get_env("TORCH_ECCL_BLOCKING_WAIT");
   blocking_wait_ = bw.has_value() && (*bw == "1" || *bw == "true" || *bw == "TRUE");
-  watchdog_thread_ = std::thread(&ProcessGroupECCL::watchdog, this);
+  watchdog_ = std::make_unique<WorkWatchdog>([this] { return poll_async_error(); }, [this] { abort(); });
 }
 
 ProcessGroupECCL::~ProcessGroupECCL() { shutdown(); }
 
 void ProcessGroupECCL::shutdown() {
-  if (!stop_.exchange(true)) {
-    work_cv_.notify_all();
-    if (watchdog_thread_.joinable()) watchdog_thread_.join();
-  }
+  if (!stop_.exchange(true) && watchdog_) watchdog_->stop();   // before the communicators go away
   std::lock_guard<std::mutex> g(mutex_);
   for (auto& kv : comms_) {
     Comm& c = kv.second;
@@ -221,44 +223,39 @@ std::string ProcessGroupECCL::get_unique_id_hex() {
   return os.str();
 }
 
+namespace {
+// What the watchdog sees of a WorkECCL.
+struct WatchedWork final : public Watched {
+  explicit WatchedWork(c10::intrusive_ptr<ProcessGroupECCL::WorkECCL> w) : w_(std::move(w)) {}
+  bool poll_completed() override { return w_->isCompleted(); }
+  bool failed() const override { return !w_->isSuccess(); }
+  bool timed_out(std::chrono::steady_clock::time_point now) const override { return w_->timedOut(now); }
+  void fail(std::exception_ptr e) override { w_->setException(e); }
+  void finish() override { w_->markFinished(); }
+  uint64_t sequence() const override { return w_->getSequencenumber(); }
+  std::chrono::milliseconds timeout() const override { return w_->timeout(); }
+  c10::intrusive_ptr<ProcessGroupECCL::WorkECCL> w_;
+};
+}  // namespace
+
 void ProcessGroupECCL::enqueue(const c10::intrusive_ptr<WorkECCL>& work) {
-  {
-    std::lock_guard<std::mutex> g(work_mutex_);
-    works_.push_back(work);
-  }
-  work_cv_.notify_one();
+  watchdog_->watch(std::make_shared<WatchedWork>(work));
 }
 
-// Polls outstanding works: completed ones release their tensors and complete
-// their future; one that exceeds its timeout gets an exception and the
-// communicator is aborted so that no rank stays blocked in the collective.
-void ProcessGroupECCL::watchdog() {
-  while (!stop_.load()) {
-    std::unique_lock<std::mutex> lk(work_mutex_);
-    work_cv_.wait_for(lk, std::chrono::milliseconds(100), [&] { return stop_.load() || !works_.empty(); });
-    if (stop_.load()) break;
-    const auto now = std::chrono::steady_clock::now();
-    bool timed_out = false;
-    for (auto it = works_.begin(); it != works_.end();) {
-      WorkECCL& w = **it;
-      if (w.isCompleted()) {
-        if (w.isSuccess()) w.future_->markCompleted(c10::IValue(w.outputs_));
-        w.stashed_.clear();
-        it = works_.erase(it);
-      } else if (w.timedOut(now)) {
-        w.setException(std::make_exception_ptr(c10::DistBackendError(
-            c10::SourceLocation{__func__, __FILE__, static_cast<uint32_t>(__LINE__)},
-            c10::str("eccl watchdog: collective (seq ", w.seq_, ") did not complete within ", w.timeout_.count(), " ms"))));
-        timed_out = true;
-        it = works_.erase(it);
-      } else {
-        ++it;
-      }
-    }
-    lk.unlock();
-    if (timed_out) abort();
-    else std::this_thread::sleep_for(std::chrono::milliseconds(1));
+// Asked by the watchdog on every sweep (reference: checkForECCLErrors,
+// ProcessGroupECCL.cpp:1682-1700): a communicator that reports anything but success or
+// "in progress" is broken for every outstanding work.
+std::string ProcessGroupECCL::poll_async_error() {
+  std::lock_guard<std::mutex> g(mutex_);
+  for (auto& kv : comms_) {
+    Comm& c = kv.second;
+    if (!c.comm || c.aborted) continue;
+    ncclResult_t state = ncclSuccess;
+    if (ncclCommGetAsyncError(c.comm, &state) != ncclSuccess) continue;
+    if (state != ncclSuccess && state != ncclInProgress)
+      return std::string(ncclGetErrorString(state)) + " (" + ncclGetLastError(c.comm) + ")";
   }
+  return std::string();
 }
 
 template <typename Fn>

@@ -8,8 +8,8 @@
 // with the unique id published through the c10d Store; one dedicated comm stream
 // per device; the compute stream hands over to the comm stream through an event
 // and Work::wait() makes the current stream wait for the end event (no host
-// block unless blocking wait is on); a watchdog thread times works out and aborts
-// the communicator. The allocator is stream-ordered, so instead of recordStream
+// block unless blocking wait is on); a watchdog thread (work_watchdog.h) polls the
+// communicator for asynchronous errors, times works out and aborts the communicator. The allocator is stream-ordered, so instead of recordStream
 // the Work object keeps its tensors alive until it completes.
 #pragma once
 
@@ -25,6 +25,7 @@
 #include <thread>
 #include <unordered_map>
 
+#include "distributed/work_watchdog.h"
 #include "runtime/gcu_runtime.h"
 
 namespace c10d_gcu {
@@ -59,6 +60,8 @@ class ProcessGroupECCL : public c10d::Backend {
     c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
     bool timedOut(std::chrono::steady_clock::time_point now) const;
     void setException(std::exception_ptr e);
+    void markFinished();   // success seen by the watchdog: fulfil the future, release the tensors
+    std::chrono::milliseconds timeout() const { return timeout_; }
 
    private:
     friend class ProcessGroupECCL;
@@ -144,7 +147,7 @@ class ProcessGroupECCL : public c10d::Backend {
   c10::intrusive_ptr<c10d::Work> collective(std::vector<at::Tensor> inputs, std::vector<at::Tensor> outputs, Fn fn,
                                             c10d::OpType op);
   void enqueue(const c10::intrusive_ptr<WorkECCL>& work);
-  void watchdog();
+  std::string poll_async_error();   // "" while every communicator is healthy (ncclCommGetAsyncError)
 
   c10::intrusive_ptr<c10d::Store> store_;
   c10::intrusive_ptr<Options> options_;
@@ -158,10 +161,7 @@ class ProcessGroupECCL : public c10d::Backend {
   bool blocking_wait_ = false;
   c10::Device last_device_ = c10::Device(c10::DeviceType::PrivateUse1, 0);
 
-  std::thread watchdog_thread_;
-  std::mutex work_mutex_;
-  std::condition_variable work_cv_;
-  std::deque<c10::intrusive_ptr<WorkECCL>> works_;
+  std::unique_ptr<WorkWatchdog> watchdog_;
   std::atomic<bool> stop_{false};
 };
 

@@ -18,7 +18,6 @@ namespace torch_gcu {
 void register_runtime();                              // runtime/gcu_guard_hooks.cpp
 const at::Generator& default_generator(c10::DeviceIndex idx);
 void init_distributed_bindings(py::module& m);        // distributed/init.cpp
-py::dict allocator_selftest();                        // python/allocator_selftest.cpp
 }  // namespace torch_gcu
 
 using namespace torch_gcu;
@@ -114,7 +113,6 @@ PYBIND11_MODULE(_C, m) {
     r["num_deferred_frees"] = s.num_deferred_frees;
     return r;
   });
-  m.def("_allocator_selftest", &allocator_selftest);
 
   // ---- autocast accessors for the PrivateUse1 key (reference: InitGcuBindings.cpp:59-127)
   m.def("is_autocast_enabled", [] { return at::autocast::is_autocast_enabled(at::kPrivateUse1); });

@@ -45,7 +45,10 @@ class CudaBackend final : public MemoryBackend {
       (void)cudaGetLastError();
       return false;
     }
-    return true;  // success, or an error we cannot wait out
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    // anything but success keeps the block parked: an event that cannot be queried (recorded on a
+    // capturing stream, a lost context) is no proof that the other stream is done with the memory
+    return e == cudaSuccess;
   }
   void destroy_event(void* event) override { (void)cudaEventDestroy(static_cast<cudaEvent_t>(event)); }
   void synchronize(int device) override {
@@ -122,6 +125,10 @@ size_t StreamOrderedCachingAllocator::round_size(size_t bytes) {
 StreamOrderedCachingAllocator::PerDevice& StreamOrderedCachingAllocator::dev(int device) { return devices_[device]; }
 
 void StreamOrderedCachingAllocator::process_pending_locked() {
+  if (capturing_.empty() && !parked_.empty()) {
+    for (Block* b : parked_) record_deferred_locked(b);
+    parked_.clear();
+  }
   while (!pending_.empty()) {
     auto [event, block] = pending_.front();
     if (!backend_->event_done(event)) break;
@@ -229,11 +236,13 @@ void StreamOrderedCachingAllocator::free(void* ptr) {
     pool.live--;
     b->other_streams.clear();
     if (pool.released) {
+      const uint64_t pool_id = b->pool;        // read before the block (and then the pool) go away
+      const bool last = pool.live == 0;
       backend_->free_plain(b->device, b->ptr);
       d.stats.reserved_bytes -= static_cast<int64_t>(b->size);
       d.stats.num_backend_frees++;
       delete b;
-      if (pool.live == 0) pools_.erase(b->pool);
+      if (last) pools_.erase(pool_id);
     } else {
       pool.cache.emplace(b->size, b);
     }
@@ -244,10 +253,20 @@ void StreamOrderedCachingAllocator::free(void* ptr) {
   } else {
     // other streams may still be using the block: wait for events recorded on them now
     d.stats.num_deferred_frees++;
-    for (cudaStream_t s : b->other_streams) {
-      pending_.emplace_back(backend_->record_event(b->device, s), b);
-      b->pending_events++;
+    if (!capturing_.empty()) {
+      // an event recorded now could land inside a capture and never become queryable: park the
+      // block and record its events when no capture is open any more
+      parked_.push_back(b);
+      return;
     }
+    record_deferred_locked(b);
+  }
+}
+
+void StreamOrderedCachingAllocator::record_deferred_locked(Block* b) {
+  for (cudaStream_t s : b->other_streams) {
+    pending_.emplace_back(backend_->record_event(b->device, s), b);
+    b->pending_events++;
   }
 }
 
@@ -274,6 +293,7 @@ uint64_t StreamOrderedCachingAllocator::begin_capture(int device, cudaStream_t s
 void StreamOrderedCachingAllocator::end_capture(int device, cudaStream_t stream) {
   std::lock_guard<std::mutex> g(mutex_);
   capturing_.erase({device, stream});
+  if (capturing_.empty()) process_pending_locked();   // blocks parked during the capture get their events now
 }
 
 void StreamOrderedCachingAllocator::release_pool(uint64_t id) {

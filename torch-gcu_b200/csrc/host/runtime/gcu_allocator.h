@@ -97,6 +97,7 @@ class StreamOrderedCachingAllocator {
     DeviceStats stats;
   };
   void process_pending_locked();
+  void record_deferred_locked(Block* b);   // one event per other stream that used the block
   void release_cached_locked(int device);
   PerDevice& dev(int device);
 
@@ -105,6 +106,7 @@ class StreamOrderedCachingAllocator {
   std::unordered_map<void*, Block*> live_;
   std::unordered_map<int, PerDevice> devices_;
   std::deque<std::pair<void*, Block*>> pending_;  // (event, block)
+  std::vector<Block*> parked_;   // freed with other streams recorded while a capture was open: events not recorded yet
   std::map<std::pair<int, cudaStream_t>, uint64_t> capturing_;   // (device, stream) -> pool
   std::unordered_map<uint64_t, Pool> pools_;
   uint64_t next_pool_ = 1;

@@ -264,7 +264,7 @@ __device__ __forceinline__ void hist_tile(const uint32_t* __restrict__ keys, int
 #pragma unroll 4
   for (int r = 0; r < kItemsPerThread; ++r) {
     const int64_t i = base + r * kSortThreads + threadIdx.x;
-    if (i < n) atomicAdd(&sh[(keys[i] >> shift) & 255u], 1u);
+    if (i < n) atomicAdd(&sh[((keys[i] & 0x7fffffffu) >> shift) & 255u], 1u);   // bit 31 is a flag, never a digit
   }
   __syncthreads();
   hist[static_cast<int64_t>(threadIdx.x) * nblocks + tile] = sh[threadIdx.x];
@@ -363,7 +363,7 @@ __device__ __forceinline__ void scatter_tile(const uint32_t* __restrict__ keys_i
   for (int r = 0; r < kItemsPerThread; ++r) {
     const int64_t i = wbase + r * 32 + lane;
     const bool live = i < n;
-    const uint32_t d = live ? ((key[r] >> shift) & 255u) : (256u + lane);
+    const uint32_t d = live ? (((key[r] & 0x7fffffffu) >> shift) & 255u) : (256u + lane);
     const uint32_t peers = __match_any_sync(0xffffffffu, d);
     if (live && lane == (__ffs(peers) - 1)) warp_count[warp][d] += __popc(peers);
     __syncwarp();
@@ -385,7 +385,7 @@ __device__ __forceinline__ void scatter_tile(const uint32_t* __restrict__ keys_i
   for (int r = 0; r < kItemsPerThread; ++r) {
     const int64_t i = wbase + r * 32 + lane;
     const bool live = i < n;
-    const uint32_t d = live ? ((key[r] >> shift) & 255u) : (256u + lane);
+    const uint32_t d = live ? (((key[r] & 0x7fffffffu) >> shift) & 255u) : (256u + lane);
     const uint32_t peers = __match_any_sync(0xffffffffu, d);
     uint32_t pos = 0;
     if (live) {
@@ -398,7 +398,8 @@ __device__ __forceinline__ void scatter_tile(const uint32_t* __restrict__ keys_i
     if (live) {
       keys_out[pos] = key[r];
       // bit 31 of a key marks an out-of-range index: it rides along unsorted
-      // (the digits never reach it) and turns the value into an invalid id
+      // (masked out of every digit, the top one of a four-pass sort included) and turns the
+      // value into an invalid id
       vals_out[pos] = (key[r] >> 31) ? 0xffffffffu : (vals_in ? vals_in[i] : static_cast<uint32_t>(i));
     }
   }
@@ -1265,6 +1266,14 @@ static __device__ __align__(256) unsigned char g_static_scratch[B200_STATIC_SCRA
 
 b200Status b200_scatter_add_static(const b200Tensor* out, const b200Tensor* self, int64_t dim,
                                    const b200Tensor* index, const b200Tensor* src, b200Stream stream) {
+  // Argument and size checks come first: a call that is refused costs no device call at all.
+  B200_REQUIRE(out && self && index && src, B200_BAD_PARAM, "b200_scatter_add_static: null tensor");
+  B200_REQUIRE(valid(out) && valid(self) && valid(index) && valid(src), B200_BAD_PARAM,
+               "b200_scatter_add_static: invalid tensor view");
+  const size_t need = b200_scatter_add_workspace_size(self, dim, index, src);
+  B200_REQUIRE(need <= B200_STATIC_SCRATCH_BYTES, B200_NOT_SUPPORTED,
+               "b200_scatter_add_static: this problem needs %zu bytes of scratch, the built-in array holds %u; "
+               "use b200_scatter_add with a caller workspace", need, (unsigned)B200_STATIC_SCRATCH_BYTES);
   // In host code `g_static_scratch` is only a handle for the symbol, not a device
   // address: the address is looked up once per device, with that device current.
   static void* scratch_of_device[64] = {nullptr};
@@ -1288,11 +1297,6 @@ b200Status b200_scatter_add_static(const b200Tensor* out, const b200Tensor* self
     }
     scratch = scratch_of_device[dev];
   }
-  B200_REQUIRE(out && self && index && src, B200_BAD_PARAM, "b200_scatter_add_static: null tensor");
-  const size_t need = b200_scatter_add_workspace_size(self, dim, index, src);
-  B200_REQUIRE(need <= B200_STATIC_SCRATCH_BYTES, B200_NOT_SUPPORTED,
-               "b200_scatter_add_static: this problem needs %zu bytes of scratch, the built-in array holds %u; "
-               "use b200_scatter_add with a caller workspace", need, (unsigned)B200_STATIC_SCRATCH_BYTES);
   // Nothing in the scratch has to start at zero: keys, histograms, sorted pairs and
   // segment starts are all fully rewritten by every call before they are read.
   return b200_scatter_add(out, self, dim, index, src, scratch, B200_STATIC_SCRATCH_BYTES, stream);

@@ -59,6 +59,32 @@ def reference_layer_cpu(x, w, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, 
     return r + (F.silu(gate) * up) @ w["wd"].float().t()
 
 
+def reference_decode_cpu(x, k_cache, v_cache, pos, w, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0):
+    """One decode step of the unsharded layer in plain fp32 torch on the CPU: x (n,1,hidden) new
+    tokens at position `pos`, caches (n, kv_heads, T, D) whose row `pos` the step replaces.
+    Returns (output (n,1,hidden), new key rows (n, kv_heads, D), new value rows)."""
+    n = x.shape[0]
+    cos, sin = rope_tables_cpu(k_cache.shape[2], head_dim, theta)
+    positions = torch.full((n, 1), pos, dtype=torch.int64)
+    h = _rms_cpu(x, w["norm1"], eps)
+    qkv = h.float() @ w["wqkv"].float().t()
+    q, k, v = qkv.split([heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], -1)
+    q = _rope_cpu(q.view(n, 1, heads, head_dim), cos, sin, positions).transpose(1, 2)
+    k = _rope_cpu(k.view(n, 1, kv_heads, head_dim), cos, sin, positions).transpose(1, 2)
+    v = v.view(n, 1, kv_heads, head_dim).transpose(1, 2)
+    kc, vc = k_cache[:, :, :pos + 1].float().clone(), v_cache[:, :, :pos + 1].float().clone()
+    kc[:, :, pos] = k[:, :, 0].to(k_cache.dtype).float()   # the cache holds the rows in its own dtype
+    vc[:, :, pos] = v[:, :, 0].to(v_cache.dtype).float()
+    g = heads // kv_heads
+    att = F.scaled_dot_product_attention(q, kc.repeat_interleave(g, 1), vc.repeat_interleave(g, 1), is_causal=False)
+    o = att.transpose(1, 2).reshape(n, 1, heads * head_dim) @ w["wo"].float().t()
+    r = x.float() + o
+    h2 = _rms_cpu(r, w["norm2"], eps)
+    gu = h2 @ w["wgu"].float().t()
+    gate, up = gu.split(ffn, -1)
+    return r + (F.silu(gate) * up) @ w["wd"].float().t(), k[:, :, 0], v[:, :, 0]
+
+
 class DecoderLayer:
     def __init__(self, weights, tp, backend, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0,
                  device=None):
