@@ -333,6 +333,25 @@ b200Status b200_arange(const b200Tensor* out, double start, double step, b200Str
 b200Status b200_tri(const b200Tensor* out, const b200Tensor* in, int64_t diagonal, int32_t upper,
                     b200Stream stream);
 
+/* ---- sort, top-k, cumulative sum (what a sampling step needs around the logits) ----
+ * reference: generated aotops::sort_out / argsort / topk_out / cumsum_out -> the vendor's
+ * sort, topk and cumsum calls (codegen/gcu_native_functions.yaml rows sort.values_stable,
+ * argsort.stable, topk.values, cumsum.out).
+ * b200_sort_rows: stable sort of every row of a contiguous (rows, n) tensor, ascending or
+ * descending; NaN orders above every number and -0 equals +0, as in CPU ATen; equal elements
+ * keep their input order. values (in's dtype) and / or indices (int64), each contiguous
+ * (rows, k) with k <= n, take the first k sorted entries of every row (k = n: sort / argsort;
+ * k < n with descending: topk largest, ties by lowest index). Either output may be NULL.    */
+size_t b200_sort_rows_workspace_size(const b200Tensor* in);
+b200Status b200_sort_rows(const b200Tensor* values, const b200Tensor* indices, const b200Tensor* in,
+                          int32_t descending, void* workspace, size_t workspace_bytes, b200Stream stream);
+/* out[..., i, ...] = sum of in[..., 0..i, ...] along `dim`; contiguous operands of one dtype.
+ * Accumulates as CPU ATen does: fp32 in fp64, bf16 / f16 in fp32, integers in int64. Along a
+ * non-last dimension the additions run in index order (bit-identical to the CPU); along the
+ * last dimension the row is scanned in parallel (fp results within an ulp of the CPU's,
+ * integers identical).                                                                    */
+b200Status b200_cumsum(const b200Tensor* out, const b200Tensor* in, int64_t dim, b200Stream stream);
+
 /* ---- backward of the layer's pointwise and row operators ---------------------
  * (reference yaml rows silu_backward.grad_input, _softmax_backward_data.out,
  * native_layer_norm_backward; fp32 math, one rounding per output, reductions in a

@@ -336,6 +336,23 @@ def sdpa_flash_bwd(dq, dk, dv, dout, q, k, v, out, lse, is_causal, scale=None, w
                                     _stream(stream)))
 
 
+def sort_rows_workspace_size(inp):
+    return lib().b200_sort_rows_workspace_size(_ref(view(inp)))
+
+
+def sort_rows(values, indices, inp, descending=False, workspace=None, stream=None):
+    """Stable sort of every row of a contiguous (rows, n) tensor; values / indices (rows, k <= n)."""
+    import torch
+    if workspace is None:
+        workspace = torch.empty(max(1, sort_rows_workspace_size(inp)), dtype=torch.uint8, device=inp.device)
+    check(lib().b200_sort_rows(_ref(view(values)), _ref(view(indices)), _ref(view(inp)),
+                               ctypes.c_int32(1 if descending else 0), *ws_args(workspace), _stream(stream)))
+
+
+def cumsum(out, inp, dim, stream=None):
+    check(lib().b200_cumsum(_ref(view(out)), _ref(view(inp)), ctypes.c_int64(dim), _stream(stream)))
+
+
 def launch_count():
     """Kernel launches the library has issued in this process so far."""
     lib().b200_launch_count.restype = ctypes.c_ulonglong
