@@ -151,3 +151,136 @@ def test_greedy_sampling_step(dev):
     same(tok.cpu(), ref)
     probs = torch.softmax(ld, -1)
     same((probs > 1e-3).sum(-1).cpu(), (torch.softmax(logits.masked_fill(banned, float("-inf")), -1) > 1e-3).sum(-1))
+
+
+# ---- sort / argsort / topk / cumsum ------------------------------------------------------------
+SORT_DTYPES = [torch.float32, torch.bfloat16, torch.float16, torch.float64, torch.int64, torch.int32, torch.int16,
+               torch.uint8]
+
+
+@pytest.mark.parametrize("dtype", SORT_DTYPES)
+@pytest.mark.parametrize("descending", [False, True])
+def test_stable_sort_matches_cpu(dev, dtype, descending):
+    """Stable sort along every dimension: values and indices bit for bit with CPU ATen's stable sort
+    (many ties, NaN above every number, infinities, both zeros; rows longer than one 2048-key tile)."""
+    for shape, seed in (((5, 4099), 21), ((3, 7, 33), 22), ((1,), 23), ((2, 0, 3), 24), ((70, 130), 25)):
+        x = _inputs(dtype, shape, seed)
+        if dtype.is_floating_point and x.numel() > 40:
+            x.view(-1)[3::37] = -0.0
+            x.view(-1)[4::41] = 0.0
+        for dim in range(-1, x.dim() - 1 if x.dim() > 1 else 0):
+            v, i = torch.sort(x.to(dev), dim=dim, descending=descending, stable=True)
+            rv, ri = torch.sort(x, dim=dim, descending=descending, stable=True)
+            same(i.cpu(), ri)
+            same(v.cpu(), rv)
+            if dtype.is_floating_point:   # the values are the input's own bits: zero signs survive
+                assert torch.equal(torch.signbit(v.cpu()), torch.signbit(rv))
+            same(torch.argsort(x.to(dev), dim=dim, descending=descending, stable=True).cpu(), ri)
+    s = torch.tensor(3.5).to(dtype)
+    v, i = torch.sort(s.to(dev), stable=True)
+    assert v.cpu() == s and i.item() == 0
+
+
+def test_sort_default_and_noncontiguous_inputs(dev):
+    g = torch.Generator().manual_seed(26)
+    x = torch.randn(40, 50, generator=g)           # distinct values: the unstable request has one answer
+    v, i = torch.sort(x.to(dev).t(), dim=0)
+    rv, ri = torch.sort(x.t(), dim=0)
+    same(v.cpu(), rv)
+    same(i.cpu(), ri)
+    same(torch.argsort(x.to(dev), descending=True).cpu(), torch.argsort(x, descending=True))
+    out_v, out_i = torch.empty(50, 40, device=dev).t(), torch.empty(50, 40, dtype=torch.int64, device=dev).t()
+    torch.sort(x.to(dev), dim=1, stable=True, out=(out_v, out_i))   # non-contiguous outputs
+    rv, ri = torch.sort(x, dim=1, stable=True)
+    same(out_v.cpu(), rv)
+    same(out_i.cpu(), ri)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int64])
+def test_topk_matches_cpu(dev, dtype):
+    g = torch.Generator().manual_seed(27)
+    # distinct values per row (a permutation, scaled): top-k has one answer, indices included
+    n = 300 if dtype == torch.bfloat16 else 5000
+    x = torch.stack([torch.randperm(n, generator=g) for _ in range(6)]).sub(n // 2)
+    x = (x.float() * 0.25).to(dtype) if dtype.is_floating_point else x.to(dtype)
+    for k, largest in ((1, True), (50, True), (17, False), (n, True)):
+        v, i = torch.topk(x.to(dev), k, dim=-1, largest=largest)
+        rv, ri = torch.topk(x, k, dim=-1, largest=largest)
+        same(v.cpu(), rv)
+        same(i.cpu(), ri)
+    v, i = torch.topk(x.to(dev), 5, dim=0)     # a column may hold equal values: the indices are checked through the values
+    rv, ri = torch.topk(x, 5, dim=0)
+    same(v.cpu(), rv)
+    same(torch.gather(x, 0, i.cpu()), rv)
+    # ties and NaN: the values are determined, and every index points at its value; among equal
+    # elements this backend returns the lowest index first (NaN counts as the largest)
+    y = _inputs(torch.float32, (4, 999), 28)
+    v, i = torch.topk(y.to(dev), 40, dim=-1)
+    rv, _ = torch.topk(y, 40, dim=-1)
+    same(v.cpu(), rv)
+    same(torch.gather(y, 1, i.cpu()), rv)
+    sv, si = torch.sort(y, dim=-1, descending=True, stable=True)
+    same(i.cpu(), si[:, :40])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64, torch.bfloat16, torch.float16, torch.int64, torch.int32,
+                                   torch.uint8])
+def test_cumsum_matches_cpu(dev, dtype):
+    g = torch.Generator().manual_seed(29)
+    for shape in ((3, 5000), (17, 9, 11), (1,), (0, 4), (2, 3, 2100)):
+        if dtype.is_floating_point:
+            x = torch.randn(shape, generator=g).to(dtype)
+        else:
+            x = torch.randint(0 if dtype == torch.uint8 else -50, 50, shape, generator=g).to(dtype)
+        for dim in range(x.dim()):
+            got = torch.cumsum(x.to(dev), dim).cpu()
+            ref = torch.cumsum(x, dim)
+            assert got.dtype == ref.dtype and got.shape == ref.shape
+            if not dtype.is_floating_point or dim != x.dim() - 1:
+                same(got, ref)   # integers, and the serial order of a non-last dimension: identical
+            else:
+                # a row is scanned in parallel: fp32 / fp64 within 1e-6 relative, 16-bit types within one ulp
+                rtol = 1e-6 if dtype in (torch.float32, torch.float64) else 2 ** -7
+                scale = x.float().abs().cumsum(dim).clamp_min(1.0)   # error grows with the running magnitude
+                assert ((got.float() - ref.float()).abs() <= rtol * scale).all()
+    # integer inputs promote to int64, and dtype= is honoured
+    xi = torch.randint(-5, 5, (4, 100), generator=g, dtype=torch.int32)
+    same(torch.cumsum(xi.to(dev), 1).cpu(), torch.cumsum(xi, 1))
+    same(torch.cumsum(xi.to(dev), 1, dtype=torch.float32).cpu(), torch.cumsum(xi, 1, dtype=torch.float32))
+
+
+def test_top_k_top_p_sampling_step(dev):
+    """A sampling step the way serving code writes it: top-k cut, softmax, descending sort, cumulative
+    probability, nucleus mask, renormalise -- the kept token set and the renormalised distribution match
+    the CPU."""
+    g = torch.Generator().manual_seed(30)
+    logits = torch.randn(8, 32000, generator=g) * 2.0
+
+    def step(lg):
+        kth = torch.topk(lg, 50, dim=-1).values[:, -1:]
+        lg = lg.masked_fill(lg < kth, float("-inf"))
+        probs = torch.softmax(lg, -1)
+        sp, si = torch.sort(probs, dim=-1, descending=True, stable=True)
+        cum = torch.cumsum(sp, -1)
+        keep = (cum - sp) < 0.9                      # tokens whose preceding mass is below top-p
+        sp = torch.where(keep, sp, torch.zeros_like(sp))
+        sp = sp / sp.sum(-1, keepdim=True)
+        return sp, si, keep
+    sp, si, keep = step(logits.to(dev))
+    rsp, rsi, rkeep = step(logits)
+    same(si.cpu()[:, :50], rsi[:, :50])              # beyond the top-k cut every probability is an equal zero
+    same(keep.cpu(), rkeep)
+    assert torch.allclose(sp.cpu(), rsp, rtol=1e-5, atol=1e-7)
+    # the C ABI itself: sorted probabilities and their cumulative sum
+    import b200ops as ops
+    p = torch.softmax(logits, -1).to("cuda:0")
+    v = torch.empty_like(p)
+    i = torch.empty(p.shape, dtype=torch.int64, device="cuda:0")
+    ops.sort_rows(v, i, p, descending=True)
+    rv, ri = torch.sort(p.cpu(), dim=-1, descending=True, stable=True)
+    same(v.cpu(), rv)
+    same(i.cpu(), ri)
+    c = torch.empty_like(v)
+    ops.cumsum(c, v, 1)
+    assert torch.allclose(c.cpu(), torch.cumsum(rv, -1), rtol=1e-6, atol=1e-7)
+    assert ops.device_error_fetch() == 0

@@ -6,6 +6,7 @@
 #include <ATen/ExpandUtils.h>
 #include <ATen/WrapDimUtilsMulti.h>
 #include <ATen/native/Resize.h>
+#include <ATen/ops/sort.h>
 
 #include "aten/aot_ops.h"
 #include "aten/bridge.h"
@@ -330,6 +331,73 @@ at::Tensor& arange_start_out(const at::Scalar& start, const at::Scalar& end, con
   GCU_KERNEL_CALL(b200_arange, stream, &vo, s, st);
   if (!work.is_same(out)) out.copy_(work);
   return out;
+}
+
+namespace {
+
+// The first k entries of every slice of `self` along `dim`, sorted (stable) ascending or descending,
+// into `values` and `indices` (shaped by ATen's meta: self's shape with k along dim). The kernel
+// sorts the rows of a contiguous (rows, n) view, so the dimension is moved last first; the results
+// are written straight into the outputs when those are the matching contiguous views.
+void sort_rows_impl(const at::Tensor& self, int64_t dim, bool descending, int64_t k, const at::Tensor& values,
+                    const at::Tensor& indices) {
+  if (values.numel() == 0) return;
+  if (self.dim() == 0) {
+    values.copy_(self);
+    indices.zero_();
+    return;
+  }
+  const int64_t d = at::maybe_wrap_dim(dim, self.dim());
+  const int64_t n = self.size(d);
+  const bool last = d == self.dim() - 1;
+  at::Tensor src = (last ? self : self.movedim(d, -1)).contiguous();
+  const int64_t rows = src.numel() / n;
+  const bool direct = last && values.is_contiguous() && indices.is_contiguous();
+  at::Tensor v2 = direct ? values.view({rows, k}) : at::empty({rows, k}, self.options());
+  at::Tensor i2 = direct ? indices.view({rows, k}) : at::empty({rows, k}, self.options().dtype(at::kLong));
+  at::Tensor s2 = src.view({rows, n});
+  b200Tensor vin = to_b200(s2), vv = to_b200(v2), vi = to_b200(i2);
+  const size_t ws_bytes = b200_sort_rows_workspace_size(&vin);
+  at::Tensor ws = alloc_workspace(ws_bytes, self);
+  cudaStream_t stream = current_stream(self);
+  GCU_KERNEL_CALL(b200_sort_rows, stream, &vv, &vi, &vin, descending ? 1 : 0, ws.data_ptr(), ws_bytes);
+  if (!direct) {
+    std::vector<int64_t> moved = src.sizes().vec();
+    moved.back() = k;
+    (last ? values : values.movedim(d, -1)).copy_(v2.view(moved));
+    (last ? indices : indices.movedim(d, -1)).copy_(i2.view(moved));
+  }
+}
+
+}  // namespace
+
+// Always the stable algorithm: a stable sort is a valid answer to a request that does not ask for one.
+void sort_values_stable(const at::Tensor& self, std::optional<bool>, int64_t dim, bool descending, const at::Tensor& values,
+                        const at::Tensor& indices) {
+  sort_rows_impl(self, dim, descending, self.dim() ? self.size(at::maybe_wrap_dim(dim, self.dim())) : 1, values, indices);
+}
+
+at::Tensor argsort_stable(const at::Tensor& self, bool stable, int64_t dim, bool descending) {
+  return std::get<1>(at::sort(self, stable, dim, descending));
+}
+
+// Largest (or smallest) k along dim, always returned sorted (a sorted answer is valid for sorted = false);
+// among equal elements the lowest index comes first.
+void topk_values(const at::Tensor& self, int64_t k, int64_t dim, bool largest, bool, const at::Tensor& values,
+                 const at::Tensor& indices) {
+  sort_rows_impl(self, dim, largest, k, values, indices);
+}
+
+void cumsum_out(const at::Tensor& self, int64_t dim, std::optional<at::ScalarType>, const at::Tensor& out) {
+  if (out.numel() == 0) return;
+  // ATen's meta fixed out's dtype (the dtype argument, or int64 for integer inputs): the sum runs in it
+  at::Tensor src = self.scalar_type() == out.scalar_type() ? self : self.to(out.scalar_type());
+  src = src.contiguous();
+  at::Tensor work = out.is_contiguous() ? out : at::empty(out.sizes(), out.options());
+  b200Tensor vo = to_b200(work), vs = to_b200(src);
+  cudaStream_t stream = current_stream(out);
+  GCU_KERNEL_CALL(b200_cumsum, stream, &vo, &vs, self.dim() ? at::maybe_wrap_dim(dim, self.dim()) : 0);
+  if (!work.is_same(out)) out.copy_(work);
 }
 
 void triu_out(const at::Tensor& self, int64_t diagonal, const at::Tensor& out) { tri_impl(self, diagonal, true, out); }
