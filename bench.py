@@ -351,6 +351,8 @@ def run_gpu(args):
                     "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": x_host.numel() * 2,
                     "copies": "every rank uploads the input from its own pinned buffer; rank 0 reads the result back"},
             "parity": parity,
+            "exchange": ("peer memory: fused reduce-scatter + residual + RMSNorm + all-gather kernels" if stack.uses_peer_exchange()
+                         else ("all-reduce through the eccl process group" if world > 1 else None)),
             "gpu_launches": gpu_launches, "graph_replay": use_graph if graph_error is None else "failed: " + graph_error,
             "prefill": {"tflops_per_gpu": round(flops_rank / prefill_ms / 1e9, 1),
                         "frac_of_bf16_sustained": round(flops_rank / prefill_ms / 1e9 / tf_sust, 3)},
@@ -362,6 +364,14 @@ def run_gpu(args):
         }
     del stack
     torch.gcu.empty_cache()
+    # bit 1 of the device error word: a bounded wait of the exchange (or of a kernel's barrier) ran out
+    device_error = torch.tensor([b200ops.device_error_fetch()], dtype=torch.int32)
+    if world > 1:
+        de = device_error.to(dev)
+        dist.all_reduce(de, op=dist.ReduceOp.MAX)
+        device_error = de.cpu()
+    if rank == 0:
+        result["device_error_word"] = int(device_error.item())
 
     if rank == 0:
         result["roofline"] = gemm_roofline(dev, tf_burst, peak_kind, world)
@@ -376,6 +386,8 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if int(device_error.item()) != 0:
+        raise SystemExit("bench.py: the device error word is %d (bit 1: a bounded wait timed out)" % int(device_error.item()))
     if rank == 0 and parity is not None and not parity["ok"]:
         raise SystemExit("bench.py: the prefill output does not match the CPU reference: %s" % json.dumps(parity))
 
@@ -575,6 +587,64 @@ def run_micro(name):
         ws = torch.empty(ops.scatter_add_workspace_size(base, 0, idx, src), dtype=torch.uint8, device=dev)
         fn = ops.bind("scatter_add", out, base, ctypes.c_int64(0), idx, src, *ops.ws_args(ws), keep=(ws,))
         work = {"bytes": 404750336}
+    elif name in ("add", "silu", "cast", "sum", "softmax", "layer_norm"):
+        # config 1 operand set with 8192 rows (134 MB per fp32 tensor: larger than L2)
+        a = torch.randn(8192, 4096, device=dev)
+        b = torch.randn(8192, 4096, device=dev)
+        o = torch.empty_like(a)
+        if name == "add":
+            fn, work = ops.bind("add", o, a, b, ctypes.c_double(1.0)), {"bytes": 3 * a.numel() * 4}
+        elif name == "silu":
+            fn, work = ops.bind("silu", o, a), {"bytes": 2 * a.numel() * 4}
+        elif name == "cast":
+            h = torch.empty(a.shape, dtype=bf, device=dev)
+            fn, work = ops.bind("copy", h, a), {"bytes": a.numel() * 6}
+        elif name == "sum":
+            s_ = torch.empty(8192, device=dev)
+            fn = ops.bind("sum", s_, a, (ctypes.c_int64 * 1)(1), ctypes.c_int32(1), ctypes.c_int32(0), None, ctypes.c_size_t(0))
+            work = {"bytes": a.numel() * 4 + 8192 * 4}
+        elif name == "softmax":
+            fn, work = ops.bind("softmax", o, a, ctypes.c_int64(1)), {"bytes": 2 * a.numel() * 4}
+        else:
+            w_, b_ = torch.randn(4096, device=dev), torch.randn(4096, device=dev)
+            mean, rstd = torch.empty(8192, device=dev), torch.empty(8192, device=dev)
+            fn = ops.bind("native_layer_norm", o, mean, rstd, a, ctypes.c_int64(8192), ctypes.c_int64(4096), w_, b_,
+                          ctypes.c_double(1e-5))
+            work = {"bytes": 2 * a.numel() * 4}
+    elif name == "index_select":
+        table = (torch.randn(128256, 4096, device=dev) * 0.02).to(bf)
+        idx = torch.randint(0, 128256, (32768,), device=dev)
+        out = torch.empty(32768, 4096, dtype=bf, device=dev)
+        fn, work = ops.bind("index_select", out, table, ctypes.c_int64(0), idx), {"bytes": 2 * out.numel() * 2 + idx.numel() * 8}
+    elif name == "gather":
+        src = torch.randn(16384, 1024, device=dev)
+        idx = torch.randint(0, 1024, (16384, 1024), device=dev)
+        out = torch.empty_like(src)
+        fn, work = ops.bind("gather", out, src, ctypes.c_int64(1), idx), {"bytes": idx.numel() * 8 + 2 * src.numel() * 4}
+    elif name == "rms_norm":
+        x, r = torch.randn(8192, 4096, device=dev).to(bf), torch.randn(8192, 4096, device=dev).to(bf)
+        w_ = torch.ones(4096, device=dev).to(bf)
+        y, h = torch.empty_like(x), torch.empty_like(x)
+        fn, work = ops.bind("rms_norm_residual", y, h, x, r, w_, ctypes.c_double(1e-6)), {"bytes": 4 * x.numel() * 2}
+    elif name == "rope":
+        import workloads
+        q = torch.randn(8, 2048, 32, 128, device=dev).to(bf)
+        cos, sin = (t.to(dev) for t in workloads.rope_tables(2048, 128))
+        out = torch.empty_like(q)
+        fn, work = ops.bind("rope", out, q, cos, sin, None), {"bytes": 2 * q.numel() * 2}
+    elif name == "gemm_splitk":
+        # decode-shaped product: 64 rows against a (28672, 4096) weight (235 MB streamed once)
+        a = torch.randn(64, 4096, device=dev).to(bf)
+        w = (torch.randn(28672, 4096, device=dev) * 0.02).to(bf)
+        out = torch.empty(64, 28672, dtype=bf, device=dev)
+        fn, work = ops.bind("mm", out, a, w.t()), {"bytes": w.numel() * 2}
+    elif name == "sort":
+        p = torch.softmax(torch.randn(64, 128256, device=dev), -1)
+        v = torch.empty_like(p)
+        i = torch.empty(p.shape, dtype=torch.int64, device=dev)
+        ws = torch.empty(ops.sort_rows_workspace_size(p), dtype=torch.uint8, device=dev)
+        fn = ops.bind("sort_rows", v, i, p, ctypes.c_int32(1), *ops.ws_args(ws), keep=(ws,))
+        work = {"bytes": p.numel() * (4 + 4 + 8)}
     else:
         raise SystemExit("unknown micro case " + name)
     for _ in range(2):
@@ -599,7 +669,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the CPU check of the prefill output (profiling aid)")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
-    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | sdpa | sdpa_bwd | decode | swiglu | scatter: a 3-launch case for profiler captures")
+    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
+                         "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures")
     args = ap.parse_args()
     if args.micro:
         run_micro(args.micro)

@@ -400,6 +400,45 @@ b200Status b200_sdpa_flash_bwd(const b200Tensor* dq, const b200Tensor* dk, const
                                int32_t is_causal, double scale, void* workspace, size_t workspace_bytes,
                                b200Stream stream);
 
+/* ---- tensor-parallel exchange over peer memory ---------------------------------------
+ * What stands where the reference's row-parallel projections call the collective library
+ * (reference: torch_gcu/csrc/distributed/ProcessGroupECCL.cpp:2869-2926 allreduce, :3326-3432
+ * reduce_scatter, :3077-3166 allgather): this library's own kernels, over plain peer loads and
+ * stores. Every rank maps the other ranks' buffers once (IPC handles; the host's job) and
+ * passes a table of base addresses as seen from THIS process, its own buffer at [rank].       */
+#define B200_TP_MAX_RANKS 8
+typedef struct b200TpPeers {
+  int32_t world; /* ranks, 1..B200_TP_MAX_RANKS */
+  int32_t rank;  /* this rank                  */
+  void* base[B200_TP_MAX_RANKS];
+} b200TpPeers;
+/* Bytes of one rank's control block (flags and counters of b200_tp_sync); the host allocates one
+ * per rank in peer-visible memory, zeroes it once before first use, and passes the table.       */
+size_t b200_tp_control_bytes(void);
+/* Counting signal / wait between the ranks on `channel` (0..15). do_signal: every peer's copy of
+ * this rank's flag takes this rank's next count, after a system-scope fence, so what this GPU
+ * wrote earlier on the stream is visible to a peer that has seen the flag. do_wait: returns once
+ * every peer has signalled this channel as often as this rank has waited on it. Both in one
+ * call is a barrier. Counts live in the control block, so a captured graph replays correctly.
+ * The wait is bounded: after timeout_ns (> 0) it sets bit 1 (TIMEOUT) of the device error word
+ * (b200_device_error_fetch) and returns; the control blocks must then be zeroed again on every
+ * rank before further use. A channel must not be used from two streams at once.                */
+b200Status b200_tp_sync(const b200TpPeers* control, int32_t channel, int32_t do_signal, int32_t do_wait,
+                        uint64_t timeout_ns, b200Stream stream);
+/* Reduce-scatter + residual add + RMSNorm + all-gather of one row-parallel projection in one
+ * kernel. partial->base[r]: rank r's partial product, (total_rows, N) bf16 / f16 row-major (NULL
+ * table: nothing to reduce). This rank owns rows [row0, row0 + rows), rows = residual's row
+ * count: for each it sums the row of every rank's partial in fp32 in rank order, adds `residual`
+ * (rows, N; may be NULL), rounds once -> residual_out (rows, N; may alias residual; may be NULL),
+ * normalises with `weight` (N) and eps when normalise != 0, and stores the row at
+ * gathered->base[r] + row offset for every rank r (gather_all != 0) or only for this rank.
+ * The caller orders it between b200_tp_sync calls: partials complete on every rank before, the
+ * gathered rows complete on every rank after.                                                  */
+b200Status b200_tp_reduce_norm(const b200TpPeers* partial, const b200TpPeers* gathered,
+                               const b200Tensor* residual, const b200Tensor* residual_out,
+                               const b200Tensor* weight, int64_t row0, int64_t total_rows, double eps,
+                               int32_t normalise, int32_t gather_all, b200Stream stream);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

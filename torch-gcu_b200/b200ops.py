@@ -353,6 +353,38 @@ def cumsum(out, inp, dim, stream=None):
     check(lib().b200_cumsum(_ref(view(out)), _ref(view(inp)), ctypes.c_int64(dim), _stream(stream)))
 
 
+class TpPeers(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("base", ctypes.c_void_p * 8)]
+
+
+def tp_peers(buffers, rank, offset=0):
+    """b200TpPeers over one buffer per rank (tensors, or raw addresses), each at `offset` bytes."""
+    t = TpPeers()
+    t.world, t.rank = len(buffers), rank
+    for r, b in enumerate(buffers):
+        t.base[r] = (b.data_ptr() if hasattr(b, "data_ptr") else int(b)) + offset
+    return t
+
+
+def tp_control_bytes():
+    lib().b200_tp_control_bytes.restype = ctypes.c_size_t
+    return int(lib().b200_tp_control_bytes())
+
+
+def tp_sync(control, channel=0, signal=True, wait=True, timeout_s=2.0, stream=None):
+    check(lib().b200_tp_sync(ctypes.byref(control), ctypes.c_int32(channel), ctypes.c_int32(1 if signal else 0),
+                             ctypes.c_int32(1 if wait else 0), ctypes.c_uint64(int(timeout_s * 1e9)), _stream(stream)))
+
+
+def tp_reduce_norm(partial, gathered, residual, residual_out, weight, row0, total_rows, eps=1e-6, normalise=True,
+                   gather_all=True, stream=None):
+    check(lib().b200_tp_reduce_norm(ctypes.byref(partial) if partial is not None else None, ctypes.byref(gathered),
+                                    _ref(view(residual)), _ref(view(residual_out)), _ref(view(weight)),
+                                    ctypes.c_int64(row0), ctypes.c_int64(total_rows), ctypes.c_double(eps),
+                                    ctypes.c_int32(1 if normalise else 0), ctypes.c_int32(1 if gather_all else 0),
+                                    _stream(stream)))
+
+
 def launch_count():
     """Kernel launches the library has issued in this process so far."""
     lib().b200_launch_count.restype = ctypes.c_ulonglong

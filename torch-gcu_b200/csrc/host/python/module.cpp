@@ -18,6 +18,7 @@ namespace torch_gcu {
 void register_runtime();                              // runtime/gcu_guard_hooks.cpp
 const at::Generator& default_generator(c10::DeviceIndex idx);
 void init_distributed_bindings(py::module& m);        // distributed/init.cpp
+void init_tp_exchange_bindings(py::module& m);        // distributed/tp_exchange.cpp
 }  // namespace torch_gcu
 
 using namespace torch_gcu;
@@ -33,6 +34,7 @@ static c10::List<std::optional<at::Tensor>> to_index_list(const py::list& indice
 
 PYBIND11_MODULE(_C, m) {
   register_runtime();
+  init_tp_exchange_bindings(m);
 
   // ---- devices ---------------------------------------------------------------
   m.def("_gcu_getDeviceCount", [] { return static_cast<int>(device_count()); });

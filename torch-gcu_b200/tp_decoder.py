@@ -142,6 +142,44 @@ class DecoderLayer:
         att, _ = eff.sdpa_flash(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True)
         return torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t())
 
+    # ---- the same two halves, from already normalised activations (the fused exchange path) ----
+    def attn_from_normed(self, h, B, S, out, kv_out=None):
+        """h (B*S, hidden): RMS-normalised input of every row. qkv -> RoPE -> attention -> o_proj; this
+        rank's partial product (all rows) goes into `out` (B*S, hidden)."""
+        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        H = self.hidden
+        cos, sin = self.tables(S)
+        if d == 128:
+            qkv = eff.linear_rope(h.view(B, S, H), w["wqkv"], cos, sin, hq + hk)
+        else:
+            qkv = torch.mm(h, w["wqkv"].t()).view(B, S, hq + 2 * hk, d)
+            eff.rope(qkv[:, :, :hq + hk], cos, sin, None, True)
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+        if kv_out is not None:
+            kv_out[0][:, :, :S].copy_(k.transpose(1, 2))
+            kv_out[1][:, :, :S].copy_(v.transpose(1, 2))
+        att, _ = eff.sdpa_flash(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), True)
+        torch.mm(att.transpose(1, 2).reshape(B * S, hq * d), w["wo"].t(), out=out)
+
+    def mlp_from_normed(self, h2, out):
+        """h2 (rows, hidden) normalised: gate/up + SwiGLU -> down; this rank's partial product into `out`."""
+        act = self.eff.linear_swiglu(h2, self.w["wgu"])
+        torch.mm(act, self.w["wd"].t(), out=out)
+
+    def decode_attn_from_normed(self, h, kv, pos, out):
+        """One new token per sequence, h (B, hidden) normalised: qkv -> RoPE -> cache update -> attention over
+        [0, pos] -> o_proj partial into `out` (B, hidden)."""
+        B, H = h.shape
+        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        cos, sin = self.tables(kv[0].shape[2])
+        qkv = torch.mm(h, w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
+        q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
+        eff.rope(qkv[:, :, :hq + hk], cos, sin, self._positions(B, pos), True)
+        kv[0][:, :, pos:pos + 1].copy_(k.transpose(1, 2))
+        kv[1][:, :, pos:pos + 1].copy_(v.transpose(1, 2))
+        att, _ = eff.sdpa_flash(q.transpose(1, 2), kv[0][:, :, :pos + 1], kv[1][:, :, :pos + 1], False)
+        torch.mm(att.transpose(1, 2).reshape(B, hq * d), w["wo"].t(), out=out)
+
     def mlp_part(self, o, x):
         """o: the reduced attention output. Returns (down, r): this rank's partial MLP output
         (with the residual already added when tp == 1) and the residual stream."""
@@ -214,8 +252,105 @@ class DecoderStack:
         self.layers = [DecoderLayer(workloads.decoder_layer_weights(seed=i, dtype=dtype, tp=tp, rank=rank, **cfg), tp,
                                     backend, device=device, **cfg) for i in range(n_layers)]
         self.cfg, self.tp = cfg, tp
+        self._exchanges, self._side_streams = {}, {}
+
+    # ---- the exchange over peer memory (default for tp > 1 on the device) -----------------------
+    def uses_peer_exchange(self):
+        """tp > 1 on the device: the row-parallel projections are reduced by this backend's own kernels over
+        peer memory (fused with the residual add and the RMSNorm), not by all-reduces of the collective
+        library. TP_DECODER_EXCHANGE=nccl keeps the all-reduce path (the comparison)."""
+        import os
+        return self.tp > 1 and self.layers[0].backend == "gcu" and os.environ.get("TP_DECODER_EXCHANGE", "peer") != "nccl"
+
+    def _exchange(self, key, rows, scatter, group):
+        if key not in self._exchanges:
+            from torch_gcu.distributed.tp_exchange import TensorParallelExchange
+            self._exchanges[key] = TensorParallelExchange(rows, self.cfg["hidden"], self.layers[0].w["wo"].dtype, group,
+                                                          scatter=scatter)
+        return self._exchanges[key]
+
+    def _prefill_exchange_one(self, x, m, group, caches):
+        """One microbatch x (B, S, hidden), sequence-parallel between the projections: this rank keeps the
+        residual stream of its own 1 / tp of the rows; per projection pair one fused kernel reduces the
+        partial products of all ranks for those rows, adds the residual, normalises and scatters the rows
+        to every rank, which the next column-parallel projection then reads locally."""
+        B, S, H = x.shape
+        M = B * S
+        ex = self._exchange(("prefill", m, M), M, True, group)
+        xl = x.reshape(M, H)[ex.row0:ex.row0 + ex.rows].clone()   # this rank's rows of the residual stream
+        ex.sync()                                                  # every rank is done with the previous pass's buffers
+        ex.reduce_norm(None, xl, None, self.layers[0].w["norm1"], self.layers[0].eps)
+        ex.sync()
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            kv = None if caches is None else caches[i]
+            layer.attn_from_normed(ex.gathered, B, S, ex.partial[0], kv)
+            ex.sync()                                              # the partial products are complete on every rank
+            ex.reduce_norm(0, xl, xl, layer.w["norm2"], layer.eps)
+            ex.sync()                                              # every rank's rows have landed here
+            layer.mlp_from_normed(ex.gathered, ex.partial[1])
+            ex.sync()
+            if i + 1 < n:
+                ex.reduce_norm(1, xl, xl, self.layers[i + 1].w["norm1"], self.layers[i + 1].eps)
+            else:
+                ex.reduce_norm(1, xl, xl, None, normalise=False)   # the last residual rows, gathered as they are
+            ex.sync()
+        return ex.gathered.clone().view(B, S, H)
+
+    def prefill_exchange(self, x, group, caches=None):
+        """Prefill with the peer-memory exchange. The batch is cut into microbatches on streams of their own
+        (TP_DECODER_MICROBATCHES, default 2), so the exchange kernels of one run beside the GEMMs and the
+        attention of the other: they are small blocks that share the SMs with a resident GEMM block."""
+        import os
+        n_mb = int(os.environ.get("TP_DECODER_MICROBATCHES", "2"))
+        if n_mb < 1 or x.shape[0] % n_mb != 0:
+            n_mb = 1
+        part = x.shape[0] // n_mb
+        main = torch.gcu.current_stream()
+        fork = main.record_event()
+        outs, joins = [], []
+        for m in range(n_mb):
+            kv = None if caches is None else [tuple(c[m * part:(m + 1) * part] for c in layer_kv) for layer_kv in caches]
+            if m == 0:
+                outs.append(self._prefill_exchange_one(x[:part], 0, group, kv))
+                continue
+            if m not in self._side_streams:
+                self._side_streams[m] = torch.gcu.Stream()
+            s = self._side_streams[m]
+            s.wait_event(fork)
+            with torch.gcu.stream(s):
+                outs.append(self._prefill_exchange_one(x[m * part:(m + 1) * part], m, group, kv))
+                joins.append(s.record_event())
+        for e in joins:
+            main.wait_event(e)
+        return outs[0] if n_mb == 1 else torch.cat(outs, 0)
+
+    def decode_exchange(self, x, caches, pos, group):
+        """One decode step with the peer-memory exchange: few rows, so every rank reduces all of them for
+        itself (one kernel per projection pair that pulls the other ranks' partial rows, adds the residual and
+        normalises); the residual stream stays replicated and nothing is gathered."""
+        B, _, H = x.shape
+        ex = self._exchange(("decode", B), B, False, group)
+        r = x.view(B, H)
+        rbuf = torch.empty_like(r)
+        ex.reduce_norm(None, r, None, self.layers[0].w["norm1"], self.layers[0].eps)
+        n = len(self.layers)
+        for i, (layer, kv) in enumerate(zip(self.layers, caches)):
+            layer.decode_attn_from_normed(ex.gathered, kv, pos, ex.partial[0])
+            ex.sync()
+            ex.reduce_norm(0, r, rbuf, layer.w["norm2"], layer.eps)
+            r = rbuf
+            layer.mlp_from_normed(ex.gathered, ex.partial[1])
+            ex.sync()
+            if i + 1 < n:
+                ex.reduce_norm(1, r, r, self.layers[i + 1].w["norm1"], self.layers[i + 1].eps)
+            else:
+                ex.reduce_norm(1, r, r, None, normalise=False)
+        return ex.gathered.clone().view(B, 1, H)
 
     def prefill(self, x, group=None, caches=None, overlap=None):
+        if overlap is None and self.uses_peer_exchange():
+            return self.prefill_exchange(x, group, caches)
         if overlap is None:
             # measured on B200: tp 8 1.40 M tokens/s against 1.14 M for the plain schedule, tp 4 900 k against
             # 835 k; at tp 2 it only pays when the collective is kept to a few SMs (8 channels, 8 reserved
@@ -276,6 +411,8 @@ class DecoderStack:
         return torch.cat(out, 0)
 
     def decode(self, x, caches, pos, group=None):
+        if self.uses_peer_exchange():
+            return self.decode_exchange(x, caches, pos, group)
         for layer, kv in zip(self.layers, caches):
             x = layer.forward_decode(x, kv, pos, group)
         return x
