@@ -59,7 +59,8 @@ def test_gather_other_dims_and_smaller_index(ops):
 
 
 @pytest.mark.parametrize("n_src,n_dst,inner", [(500, 60, 12), (5000, 300, 256), (4097, 1, 8), (10, 5000, 64),
-                                               (70000, 70000, 4), (1, 1, 1), (9000, 513, 3), (0, 7, 4)])
+                                               (70000, 70000, 4), (1, 1, 1), (9000, 513, 3), (0, 7, 4), (70000, 3, 4),
+                                               (3000, 90, 8)])
 @pytest.mark.parametrize("idt", [torch.int64, torch.int32])
 def test_scatter_add_rows_bit_exact(ops, n_src, n_dst, inner, idt):
     g = torch.Generator().manual_seed(24)
@@ -86,6 +87,26 @@ def test_scatter_add_rows_bit_exact(ops, n_src, n_dst, inner, idt):
         tgt = dev(base).clone()
         ops.index_put(tgt, dev(rows.to(idt)), dev(src), False, ws2)
         exact(tgt, aten_cpu.index_put(base, [rows], src, False))
+
+
+def test_scatter_add_bad_index_is_dropped_and_flagged(ops):
+    """An out-of-range row index never traps: that source row is dropped, bit 0 of the device error word
+    is set, and every other row's sum is unaffected."""
+    g = torch.Generator().manual_seed(28)
+    src = torch.randn(4000, 8, generator=g)
+    rows = torch.randint(0, 50, (4000,), generator=g)
+    bad = rows.clone()
+    bad[123], bad[3999] = 50, -7
+    base = torch.randn(50, 8, generator=g)
+    keep = torch.ones(4000, dtype=torch.bool)
+    keep[123] = keep[3999] = False
+    ref = aten_cpu.scatter_add(base, 0, rows[keep][:, None].expand(-1, 8), src[keep])
+    idx = dev(bad)[:, None].expand(-1, 8)
+    ws = _ws(ops.scatter_add_workspace_size(dev(base), 0, idx, dev(src)))
+    out = torch.empty_like(dev(base))
+    ops.scatter_add(out, dev(base), 0, idx, dev(src), ws)
+    assert ops.device_error_fetch() & 1
+    exact(out, ref)
 
 
 def test_scatter_add_all_sources_one_row(ops):

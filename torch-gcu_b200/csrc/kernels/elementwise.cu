@@ -51,8 +51,11 @@ template <typename M> struct MulConst {
 template <typename M> struct Silu {
   __device__ __forceinline__ M operator()(M x) const { return x / (M(1) + exp(-x)); }
 };
+// fp32: accurate expf (2 ulp) and the approximate division (2 ulp): within 1e-6 relative of the CPU's
+// x / (1 + exp(-x)); the IEEE division it replaces made the kernel issue-bound (57 % SM throughput beside 60 %
+// DRAM throughput in the profiler).
 template <> struct Silu<float> {
-  __device__ __forceinline__ float operator()(float x) const { return x / (1.0f + expf(-x)); }
+  __device__ __forceinline__ float operator()(float x) const { return __fdividef(x, 1.0f + expf(-x)); }
 };
 // 16-bit I/O: fast exp / reciprocal, error far below half an output ulp.
 struct SiluFast {

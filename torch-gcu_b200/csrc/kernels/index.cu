@@ -479,6 +479,235 @@ row_keys_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, in
   }
 }
 
+
+// ---- grouping source rows by destination without a global sort (row form) ----------------
+// The ordered walk needs, for every destination row, its source rows in ascending order. A stable
+// sort of (destination, source) pairs gives that, but for a megabyte of keys its dependent passes
+// are all latency. Instead: count the sources of every destination (one atomic each), scan the
+// counts into segment starts, drop every source id into its segment at an atomically claimed
+// position (the order inside a segment is then arbitrary), and sort each segment by source id:
+// ids are unique, so the result is exactly the stable order. Segments are short for any spread-out
+// index (four ids on average in the benchmark's case): up to 8 ids are sorted in registers, up to
+// 32 by insertion in place, and longer ones are queued for a block-wide radix sort of their own.
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 16;
+constexpr int kScanChunk = kScanThreads * kScanItems;   // counts per scan block
+constexpr uint32_t kBigSegment = 32;                     // longer segments go to the block-wide sort
+
+struct BucketHeader {      // zeroed before every call, together with the scan status words and the counts
+  unsigned int ticket;     // dynamic block order of the scan
+  unsigned int big_n;      // number of queued long segments
+  unsigned int pad[62];
+};
+
+template <typename I>
+__global__ void __launch_bounds__(kThreads)
+bucket_count_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, int64_t n_dst, int wrap_negative,
+                    uint32_t* __restrict__ keys, uint32_t* __restrict__ count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    int64_t d = index[i * index_stride];
+    if (wrap_negative && d < 0) d += n_dst;
+    if (d < 0 || d >= n_dst) {
+      atomicOr(&g_device_error_word, kErrIndexOutOfRange);
+      keys[i] = 0xffffffffu;   // dropped: belongs to no segment
+    } else {
+      keys[i] = static_cast<uint32_t>(d);
+      atomicAdd(&count[d], 1u);
+    }
+  }
+}
+
+// Exclusive scan of count[0, n_dst) in place (it becomes the claim cursor of every segment) and into
+// seg_start[0, n_dst]. Blocks take chunks in ticket order and chain their totals through status words
+// (bits 63-62: 1 = chunk total, 2 = inclusive prefix; low 32 bits: the value); a block only ever waits
+// for blocks that took an earlier ticket, which are running or done. The wait is bounded.
+__global__ void __launch_bounds__(kScanThreads)
+bucket_scan_kernel(uint32_t* __restrict__ count, uint32_t* __restrict__ seg_start, int64_t n_dst, BucketHeader* header,
+                   unsigned long long* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ uint32_t sh[kWarps];
+  __shared__ uint32_t s_chunk, s_before;
+  if (threadIdx.x == 0) s_chunk = atomicAdd(&header->ticket, 1u);
+  __syncthreads();
+  const uint32_t chunk = s_chunk;
+  const int64_t base = static_cast<int64_t>(chunk) * kScanChunk + static_cast<int64_t>(threadIdx.x) * kScanItems;
+  uint32_t v[kScanItems];
+  uint32_t run = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    v[j] = base + j < n_dst ? count[base + j] : 0u;
+    run += v[j];
+  }
+  uint32_t total;
+  const uint32_t ex = block_scan_256(run, sh, &total);
+  if (threadIdx.x == 0) {
+    volatile unsigned long long* st = status;
+    uint32_t before = 0;
+    if (chunk == 0) {
+      st[0] = (2ull << 62) | total;
+    } else {
+      st[chunk] = (1ull << 62) | total;
+      __threadfence();
+      for (int64_t b = static_cast<int64_t>(chunk) - 1; b >= 0; --b) {
+        unsigned long long w = st[b];
+        for (int spin = 0; (w >> 62) == 0 && spin < (1 << 22); ++spin) w = st[b];
+        if ((w >> 62) == 0) {   // gave up: flag it and carry on with what is known
+          atomicOr(&g_device_error_word, 2u);
+          break;
+        }
+        before += static_cast<uint32_t>(w);
+        if ((w >> 62) == 2) break;
+      }
+      __threadfence();
+      st[chunk] = (2ull << 62) | static_cast<unsigned long long>(before + total);
+    }
+    s_before = before;
+  }
+  __syncthreads();
+  uint32_t at = s_before + ex;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    if (base + j < n_dst) {
+      count[base + j] = at;
+      seg_start[base + j] = at;
+    }
+    at += v[j];
+    if (base + j + 1 == n_dst) seg_start[n_dst] = at;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+bucket_scatter_kernel(const uint32_t* __restrict__ keys, int64_t n, uint32_t* __restrict__ cursor, uint32_t* __restrict__ ids) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
+    const uint32_t d = keys[i];
+    if (d != 0xffffffffu) ids[atomicAdd(&cursor[d], 1u)] = static_cast<uint32_t>(i);
+  }
+}
+
+__device__ __forceinline__ void cswap(uint32_t& a, uint32_t& b) {
+  const uint32_t lo = min(a, b), hi = max(a, b);
+  a = lo;
+  b = hi;
+}
+
+// One thread per destination row: its ids into ascending order.
+__global__ void __launch_bounds__(kThreads)
+bucket_sort_segments_kernel(uint32_t* __restrict__ ids, const uint32_t* __restrict__ seg_start, int64_t n_dst, int64_t n_src,
+                            BucketHeader* header, uint32_t* __restrict__ big_list) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
+  for (int64_t d = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; d < n_dst; d += stride) {
+    const uint32_t beg = seg_start[d], end = seg_start[d + 1];
+    if (end <= beg + 1 || end > n_src) continue;
+    const uint32_t k = end - beg;
+    uint32_t* seg = ids + beg;
+    if (k <= 8) {
+      uint32_t a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = static_cast<uint32_t>(j) < k ? seg[j] : 0xffffffffu;
+      // 19-comparator network for 8 keys (padding sorts to the end)
+      cswap(a[0], a[1]); cswap(a[2], a[3]); cswap(a[4], a[5]); cswap(a[6], a[7]);
+      cswap(a[0], a[2]); cswap(a[1], a[3]); cswap(a[4], a[6]); cswap(a[5], a[7]);
+      cswap(a[1], a[2]); cswap(a[5], a[6]); cswap(a[0], a[4]); cswap(a[3], a[7]);
+      cswap(a[1], a[5]); cswap(a[2], a[6]);
+      cswap(a[1], a[4]); cswap(a[3], a[6]);
+      cswap(a[2], a[4]); cswap(a[3], a[5]);
+      cswap(a[3], a[4]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (static_cast<uint32_t>(j) < k) seg[j] = a[j];
+    } else if (k <= kBigSegment) {
+      for (uint32_t i = 1; i < k; ++i) {
+        const uint32_t x = seg[i];
+        uint32_t j = i;
+        while (j > 0 && seg[j - 1] > x) {
+          seg[j] = seg[j - 1];
+          --j;
+        }
+        seg[j] = x;
+      }
+    } else {
+      big_list[atomicAdd(&header->big_n, 1u)] = static_cast<uint32_t>(d);
+    }
+  }
+}
+
+// The queued long segments: one block sorts one segment by source id, 8 bits per pass, between the
+// segment's stretch of `ids` and the same stretch of `tmp`.
+__global__ void __launch_bounds__(kSortThreads)
+bucket_sort_big_kernel(uint32_t* ids, uint32_t* tmp, const uint32_t* __restrict__ seg_start, int64_t n_src, int passes,
+                       const BucketHeader* header, const uint32_t* __restrict__ big_list) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ uint32_t warp_count[kWarps][256];
+  __shared__ uint32_t digit_base[256];
+  __shared__ uint32_t scan_sh[kWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t n_big = header->big_n;
+  for (uint32_t b = blockIdx.x; b < n_big; b += gridDim.x) {
+    const uint32_t d = big_list[b];
+    const uint32_t beg = seg_start[d], end = seg_start[d + 1];
+    if (end <= beg || end > n_src) continue;
+    const uint32_t k = end - beg;
+    uint32_t* in = ids + beg;
+    uint32_t* out = tmp + beg;
+    for (int pass = 0; pass < passes; ++pass) {
+      const int shift = 8 * pass;
+      digit_base[threadIdx.x] = 0;
+      __syncthreads();
+      for (uint32_t i = threadIdx.x; i < k; i += kSortThreads) atomicAdd(&digit_base[(in[i] >> shift) & 255u], 1u);
+      __syncthreads();
+      {
+        uint32_t all;
+        const uint32_t first = block_scan_256(digit_base[threadIdx.x], scan_sh, &all);
+        __syncthreads();
+        digit_base[threadIdx.x] = first;
+      }
+      __syncthreads();
+      for (uint32_t c0 = 0; c0 < k; c0 += kSortThreads) {
+        for (int i = threadIdx.x; i < kWarps * 256; i += kSortThreads) (&warp_count[0][0])[i] = 0;
+        __syncthreads();
+        const uint32_t i = c0 + threadIdx.x;
+        const bool live = i < k;
+        const uint32_t key = live ? in[i] : 0u;
+        const uint32_t dg = live ? ((key >> shift) & 255u) : (256u + lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, dg);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+        if (live && lane == (__ffs(peers) - 1)) warp_count[warp][dg] = __popc(peers);
+        __syncthreads();
+        uint32_t tile_total = 0;
+        {
+          uint32_t run = 0;
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            const uint32_t cnt = warp_count[w][threadIdx.x];
+            warp_count[w][threadIdx.x] = run;
+            run += cnt;
+          }
+          tile_total = run;
+        }
+        __syncthreads();
+        if (live) out[digit_base[dg] + warp_count[warp][dg] + before] = key;
+        __syncthreads();
+        digit_base[threadIdx.x] += tile_total;
+        __syncthreads();
+      }
+      uint32_t* t = in; in = out; out = t;
+    }
+    if (in != ids + beg)   // an odd number of passes ended in tmp
+      for (uint32_t i = threadIdx.x; i < k; i += kSortThreads) ids[beg + i] = in[i];
+    __syncthreads();
+  }
+}
+
 // keys for the element form: linear offset of the destination element.
 template <typename I>
 __global__ void __launch_bounds__(kThreads)
@@ -783,6 +1012,9 @@ struct SortPlan {
   int passes;
   int nblocks;
   size_t keys_bytes, hist_bytes, seg_bytes, total;
+  // row form only (n_dst_rows >= 0): header + scan status + counts (zeroed every call), then the queue of long segments
+  int scan_blocks;
+  size_t zero_bytes, bucket_bytes;
 };
 
 inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
@@ -798,7 +1030,13 @@ SortPlan make_plan(int64_t n, int64_t key_range /* keys in [0, key_range) */, in
   p.keys_bytes = align256(static_cast<size_t>(n) * 4);
   p.hist_bytes = align256((static_cast<size_t>(256) * p.nblocks + 256) * 4);   // tile counts, then digit totals
   p.seg_bytes = n_dst_rows >= 0 ? align256(static_cast<size_t>(n_dst_rows + 2) * 4) : 0;
-  p.total = 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
+  if (n_dst_rows >= 0) {
+    p.scan_blocks = static_cast<int>((n_dst_rows + kScanChunk - 1) / kScanChunk);
+    if (p.scan_blocks < 1) p.scan_blocks = 1;
+    p.zero_bytes = align256(sizeof(BucketHeader) + static_cast<size_t>(p.scan_blocks) * 8 + static_cast<size_t>(n_dst_rows + 1) * 4);
+    p.bucket_bytes = p.zero_bytes + align256((static_cast<size_t>(n) / kBigSegment + 2) * 4);
+  }
+  p.total = 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes + p.bucket_bytes;
   return p;
 }
 
@@ -957,17 +1195,38 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   uint32_t* vals_b = reinterpret_cast<uint32_t*>(w + 3 * p.keys_bytes);
   uint32_t* hist = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes);
   uint32_t* seg = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes + p.hist_bytes);
+  (void)keys_b; (void)vals_b; (void)hist;
+  // grouping by destination: count, scan, claim, sort the (short) segments -- five small dependent launches
+  char* bucket = w + 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
+  BucketHeader* header = reinterpret_cast<BucketHeader*>(bucket);
+  unsigned long long* status = reinterpret_cast<unsigned long long*>(bucket + sizeof(BucketHeader));
+  uint32_t* count = reinterpret_cast<uint32_t*>(bucket + sizeof(BucketHeader) + static_cast<size_t>(p.scan_blocks) * 8);
+  uint32_t* big_list = reinterpret_cast<uint32_t*>(bucket + p.zero_bytes);
+  uint32_t* sv = vals_a;   // the source ids, grouped by destination and ascending inside every group
+  {
+    cudaError_t e = cudaMemsetAsync(bucket, 0, p.zero_bytes, s);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "scatter: %s", cudaGetErrorString(e));
+  }
   const int kgrid = grid_for(n_src, kThreads, 8);
+  cudaError_t le;
   if (index->dtype == B200_I64)
-    row_keys_kernel<int64_t><<<kgrid, kThreads, 0, s>>>((const int64_t*)index->data, index_stride, n_src, n_dst, wrap_negative, keys_a);
+    le = launch_pdl(bucket_count_kernel<int64_t>, kgrid, kThreads, 0, s, (const int64_t*)index->data, index_stride, n_src, n_dst,
+                    wrap_negative, keys_a, count);
   else
-    row_keys_kernel<int32_t><<<kgrid, kThreads, 0, s>>>((const int32_t*)index->data, index_stride, n_src, n_dst, wrap_negative, keys_a);
-  uint32_t *sk, *sv;
-  bool bounds_done = false;   // the one-launch sort also writes the segment bounds
-  b200Status st = run_sort(p, keys_a, keys_b, vals_a, vals_b, hist, s, &sk, &sv, seg, n_dst, &bounds_done);
-  if (st != B200_OK) return st;
-  if (!bounds_done) segment_bounds_kernel<<<grid_for(n_src + 1, kThreads, 8), kThreads, 0, s>>>(sk, n_src, n_dst, seg);
-  note_launches(bounds_done ? 1 : 2);   // key generation (and the bounds); the sort and the segment walk count themselves
+    le = launch_pdl(bucket_count_kernel<int32_t>, kgrid, kThreads, 0, s, (const int32_t*)index->data, index_stride, n_src, n_dst,
+                    wrap_negative, keys_a, count);
+  if (le == cudaSuccess) le = launch_pdl(bucket_scan_kernel, p.scan_blocks, kScanThreads, 0, s, count, seg, n_dst, header, status);
+  if (le == cudaSuccess) le = launch_pdl(bucket_scatter_kernel, kgrid, kThreads, 0, s, (const uint32_t*)keys_a, n_src, count, sv);
+  if (le == cudaSuccess)
+    le = launch_pdl(bucket_sort_segments_kernel, grid_for(n_dst, kThreads, 8), kThreads, 0, s, sv, (const uint32_t*)seg, n_dst, n_src,
+                    header, big_list);
+  int id_bits = 1;
+  while ((int64_t(1) << id_bits) < n_src) ++id_bits;
+  if (le == cudaSuccess)
+    le = launch_pdl(bucket_sort_big_kernel, sm_count_current_device(), kSortThreads, 0, s, sv, keys_b, (const uint32_t*)seg, n_src,
+                    (id_bits + 7) / 8, (const BucketHeader*)header, (const uint32_t*)big_list);
+  B200_REQUIRE(le == cudaSuccess, B200_LAUNCH_FAILED, "scatter: %s", cudaGetErrorString(le));
+  note_launches(6);   // the memset and the five grouping kernels; the segment walk counts itself
   if (mode == 1) return launch_segment_rows<T, 1, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   if (mode == 2 && sizeof(T) == 2) return launch_segment_rows<T, 0, true>(out, self, src, sv, seg, n_dst, n_src, inner, s);
   return launch_segment_rows<T, 0, false>(out, self, src, sv, seg, n_dst, n_src, inner, s);
