@@ -52,6 +52,8 @@ class FakeBackend final : public MemoryBackend {
     ++syncs;
     for (FakeEvent* e : events) e->done = true;
   }
+  std::set<cudaStream_t> capturing_streams;
+  bool stream_is_capturing(cudaStream_t s) override { return capturing_streams.count(s) != 0; }
   int plain_allocs = 0, plain_frees = 0;
   void* alloc_plain(int, size_t bytes) override {
     if (used + bytes > capacity) return nullptr;
@@ -174,6 +176,28 @@ py::dict allocator_selftest() {
     r["parked_block_reused_after_event"] = (again1 == shared || again2 == shared);
     a.free(again1);
     a.free(again2);
+    a.release_pool(pool);
+  }
+
+  // 4d. a side stream that joined the capture: its blocks come from the capture's pool, and a block freed on
+  // one stream of the graph is not handed to the other stream (parallel branches)
+  {
+    const uint64_t pool = a.begin_capture(0, s1);
+    fb->capturing_streams = {s1, s2};
+    const int plain_before = fb->plain_allocs, async_before = fb->allocs;
+    void* on_main = a.malloc(0, 5000, s1);
+    void* on_side = a.malloc(0, 5000, s2);
+    r["side_stream_allocates_from_pool"] = fb->plain_allocs == plain_before + 2 && fb->allocs == async_before;
+    a.free(on_main);
+    void* side2 = a.malloc(0, 5000, s2);
+    r["no_cross_stream_reuse_inside_pool"] = (side2 != on_main);
+    void* main2 = a.malloc(0, 5000, s1);
+    r["same_stream_reuse_inside_pool"] = (main2 == on_main);
+    a.free(on_side);
+    a.free(side2);
+    a.free(main2);
+    fb->capturing_streams.clear();
+    a.end_capture(0, s1);
     a.release_pool(pool);
   }
 

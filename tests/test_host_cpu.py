@@ -79,6 +79,8 @@ def test_caching_allocator_policy(selftest):
     assert r["plain_frees_after_output_died"] == 2   # the last live block of a released pool (pool erased after it)
     assert r["no_event_recorded_during_capture"] and r["event_recorded_after_capture"]
     assert r["parked_block_not_reused_early"] and r["parked_block_reused_after_event"]
+    assert r["side_stream_allocates_from_pool"] and r["no_cross_stream_reuse_inside_pool"]
+    assert r["same_stream_reuse_inside_pool"]
     assert r["allocated_after_all_freed"] == 0 and r["reserved_after_empty_cache"] == 0
     assert r["backend_outstanding"] == 0 and r["cache_hits"] >= 3
 

@@ -74,6 +74,14 @@ class CudaBackend final : public MemoryBackend {
     DeviceSwitch sw(device);
     if (cudaFree(ptr) != cudaSuccess) (void)cudaGetLastError();
   }
+  bool stream_is_capturing(cudaStream_t stream) override {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &st) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    return st == cudaStreamCaptureStatusActive;
+  }
 
  private:
   struct DeviceSwitch {
@@ -162,9 +170,21 @@ void* StreamOrderedCachingAllocator::malloc(int device, size_t bytes, cudaStream
   d.stats.num_allocs++;
   Block* block = nullptr;
   auto cap = capturing_.find({device, stream});
+  if (cap == capturing_.end() && !capturing_.empty() && backend_->stream_is_capturing(stream)) {
+    // a side stream that joined a capture (it waited on an event of the capturing stream): its allocations
+    // belong to that capture's pool too, never to the stream-ordered cache that eager code shares
+    for (auto it = capturing_.begin(); it != capturing_.end(); ++it)
+      if (it->first.first == device) {
+        cap = it;
+        break;
+      }
+  }
   if (cap != capturing_.end()) {
     Pool& pool = pools_[cap->second];
+    // reuse inside the pool only along one stream: two streams of a graph are parallel branches, and nothing
+    // orders a block freed on one of them before its next use on the other
     auto pit = pool.cache.lower_bound(size);
+    while (pit != pool.cache.end() && pit->first <= size + size / 4 && pit->second->stream != stream) ++pit;
     if (pit != pool.cache.end() && pit->first <= size + size / 4) {
       block = pit->second;
       pool.cache.erase(pit);

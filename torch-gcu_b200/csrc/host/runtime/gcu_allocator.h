@@ -55,6 +55,9 @@ class MemoryBackend {
   // Plain (not stream-ordered) allocation, usable while the calling thread captures a graph.
   virtual void* alloc_plain(int device, size_t bytes) = 0;   // nullptr when out of memory
   virtual void free_plain(int device, void* ptr) = 0;
+  // True when work issued to `stream` is being recorded into a graph (the stream started the capture or
+  // joined it by waiting on an event of a capturing stream).
+  virtual bool stream_is_capturing(cudaStream_t stream) = 0;
 };
 std::unique_ptr<MemoryBackend> make_cuda_backend();
 

@@ -503,7 +503,7 @@ struct BucketHeader {      // zeroed before every call, together with the scan s
 template <typename I>
 __global__ void __launch_bounds__(kThreads)
 bucket_count_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, int64_t n_dst, int wrap_negative,
-                    uint32_t* __restrict__ keys, uint32_t* __restrict__ count) {
+                    uint32_t* __restrict__ keys, uint32_t* __restrict__ slot, uint32_t* __restrict__ count) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
@@ -515,17 +515,18 @@ bucket_count_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n
       keys[i] = 0xffffffffu;   // dropped: belongs to no segment
     } else {
       keys[i] = static_cast<uint32_t>(d);
-      atomicAdd(&count[d], 1u);
+      slot[i] = atomicAdd(&count[d], 1u);   // the position this source claims inside its segment (arbitrary order)
     }
   }
 }
 
-// Exclusive scan of count[0, n_dst) in place (it becomes the claim cursor of every segment) and into
-// seg_start[0, n_dst]. Blocks take chunks in ticket order and chain their totals through status words
-// (bits 63-62: 1 = chunk total, 2 = inclusive prefix; low 32 bits: the value); a block only ever waits
-// for blocks that took an earlier ticket, which are running or done. The wait is bounded.
+// Exclusive scan of count[0, n_dst) into seg_start[0, n_dst]. Blocks take chunks in ticket order and chain
+// their totals through status words (bits 63-62: 1 = chunk total, 2 = inclusive prefix; low 32 bits: the
+// value). The look-back reads 32 predecessors at a time, one per lane, so a chain of a few dozen chunks
+// costs one round trip, not one per chunk. A block only ever waits for blocks that took an earlier ticket,
+// which are running or done, and the wait is bounded.
 __global__ void __launch_bounds__(kScanThreads)
-bucket_scan_kernel(uint32_t* __restrict__ count, uint32_t* __restrict__ seg_start, int64_t n_dst, BucketHeader* header,
+bucket_scan_kernel(const uint32_t* __restrict__ count, uint32_t* __restrict__ seg_start, int64_t n_dst, BucketHeader* header,
                    unsigned long long* status) {
   pdl_launch_dependents();
   pdl_wait();
@@ -534,60 +535,78 @@ bucket_scan_kernel(uint32_t* __restrict__ count, uint32_t* __restrict__ seg_star
   if (threadIdx.x == 0) s_chunk = atomicAdd(&header->ticket, 1u);
   __syncthreads();
   const uint32_t chunk = s_chunk;
-  const int64_t base = static_cast<int64_t>(chunk) * kScanChunk + static_cast<int64_t>(threadIdx.x) * kScanItems;
+  const int lane = threadIdx.x & 31;
+  // thread t takes items t, t + 256, ... of the chunk's 16 rows of 256: coalesced loads
+  const int64_t cbase = static_cast<int64_t>(chunk) * kScanChunk;
   uint32_t v[kScanItems];
-  uint32_t run = 0;
 #pragma unroll
   for (int j = 0; j < kScanItems; ++j) {
-    v[j] = base + j < n_dst ? count[base + j] : 0u;
-    run += v[j];
+    const int64_t i = cbase + j * kScanThreads + threadIdx.x;
+    v[j] = i < n_dst ? count[i] : 0u;
   }
-  uint32_t total;
-  const uint32_t ex = block_scan_256(run, sh, &total);
-  if (threadIdx.x == 0) {
+  // row j of the chunk is scanned across the block; rows are chained through `row_before`
+  uint32_t ex[kScanItems];
+  uint32_t row_before = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    uint32_t total;
+    ex[j] = row_before + block_scan_256(v[j], sh, &total);
+    row_before += total;
+  }
+  const uint32_t total = row_before;
+  if (threadIdx.x < 32) {
     volatile unsigned long long* st = status;
     uint32_t before = 0;
-    if (chunk == 0) {
-      st[0] = (2ull << 62) | total;
-    } else {
-      st[chunk] = (1ull << 62) | total;
-      __threadfence();
-      for (int64_t b = static_cast<int64_t>(chunk) - 1; b >= 0; --b) {
-        unsigned long long w = st[b];
-        for (int spin = 0; (w >> 62) == 0 && spin < (1 << 22); ++spin) w = st[b];
-        if ((w >> 62) == 0) {   // gave up: flag it and carry on with what is known
+    if (lane == 0) st[chunk] = ((chunk == 0 ? 2ull : 1ull) << 62) | total;
+    __threadfence();
+    int64_t b = static_cast<int64_t>(chunk) - 1;
+    while (b >= 0) {
+      const int64_t idx = b - lane;
+      unsigned long long w = 2ull << 62;   // lanes past chunk 0 read "inclusive prefix 0"
+      if (idx >= 0) {
+        w = st[idx];
+        for (int spin = 0; (w >> 62) == 0 && spin < (1 << 22); ++spin) w = st[idx];
+        if ((w >> 62) == 0) {   // gave up: flag it and treat the chunk as empty
           atomicOr(&g_device_error_word, 2u);
-          break;
+          w = 2ull << 62;
         }
-        before += static_cast<uint32_t>(w);
-        if ((w >> 62) == 2) break;
       }
-      __threadfence();
-      st[chunk] = (2ull << 62) | static_cast<unsigned long long>(before + total);
+      const unsigned done = __ballot_sync(0xffffffffu, (w >> 62) == 2);
+      const int stop = done ? __ffs(done) - 1 : 32;   // nearest predecessor that already holds an inclusive prefix
+      uint32_t part = lane <= stop ? static_cast<uint32_t>(w) : 0u;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      before += part;
+      if (done) break;
+      b -= 32;
     }
-    s_before = before;
+    if (lane == 0) {
+      if (chunk != 0) {
+        __threadfence();
+        st[chunk] = (2ull << 62) | static_cast<unsigned long long>(before + total);
+      }
+      s_before = before;
+    }
   }
   __syncthreads();
-  uint32_t at = s_before + ex;
+  const uint32_t before = s_before;
 #pragma unroll
   for (int j = 0; j < kScanItems; ++j) {
-    if (base + j < n_dst) {
-      count[base + j] = at;
-      seg_start[base + j] = at;
-    }
-    at += v[j];
-    if (base + j + 1 == n_dst) seg_start[n_dst] = at;
+    const int64_t i = cbase + j * kScanThreads + threadIdx.x;
+    if (i < n_dst) seg_start[i] = before + ex[j];
+    if (i + 1 == n_dst) seg_start[n_dst] = before + ex[j] + v[j];
   }
 }
 
 __global__ void __launch_bounds__(kThreads)
-bucket_scatter_kernel(const uint32_t* __restrict__ keys, int64_t n, uint32_t* __restrict__ cursor, uint32_t* __restrict__ ids) {
+bucket_scatter_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ slot, int64_t n,
+                      const uint32_t* __restrict__ seg_start, uint32_t* __restrict__ ids) {
   pdl_launch_dependents();
   pdl_wait();
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
     const uint32_t d = keys[i];
-    if (d != 0xffffffffu) ids[atomicAdd(&cursor[d], 1u)] = static_cast<uint32_t>(i);
+    if (d != 0xffffffffu) ids[seg_start[d] + slot[i]] = static_cast<uint32_t>(i);
   }
 }
 
@@ -625,15 +644,18 @@ bucket_sort_segments_kernel(uint32_t* __restrict__ ids, const uint32_t* __restri
       for (int j = 0; j < 8; ++j)
         if (static_cast<uint32_t>(j) < k) seg[j] = a[j];
     } else if (k <= kBigSegment) {
+      uint32_t a[kBigSegment];   // thread-local copy: the insertion sort's dependent accesses stay in L1
+      for (uint32_t i = 0; i < k; ++i) a[i] = seg[i];
       for (uint32_t i = 1; i < k; ++i) {
-        const uint32_t x = seg[i];
+        const uint32_t x = a[i];
         uint32_t j = i;
-        while (j > 0 && seg[j - 1] > x) {
-          seg[j] = seg[j - 1];
+        while (j > 0 && a[j - 1] > x) {
+          a[j] = a[j - 1];
           --j;
         }
-        seg[j] = x;
+        a[j] = x;
       }
+      for (uint32_t i = 0; i < k; ++i) seg[i] = a[i];
     } else {
       big_list[atomicAdd(&header->big_n, 1u)] = static_cast<uint32_t>(d);
     }
@@ -1195,7 +1217,7 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   uint32_t* vals_b = reinterpret_cast<uint32_t*>(w + 3 * p.keys_bytes);
   uint32_t* hist = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes);
   uint32_t* seg = reinterpret_cast<uint32_t*>(w + 4 * p.keys_bytes + p.hist_bytes);
-  (void)keys_b; (void)vals_b; (void)hist;
+  (void)hist;
   // grouping by destination: count, scan, claim, sort the (short) segments -- five small dependent launches
   char* bucket = w + 4 * p.keys_bytes + p.hist_bytes + p.seg_bytes;
   BucketHeader* header = reinterpret_cast<BucketHeader*>(bucket);
@@ -1211,12 +1233,15 @@ b200Status scatter_rows(void* out, const void* self, const void* src, const b200
   cudaError_t le;
   if (index->dtype == B200_I64)
     le = launch_pdl(bucket_count_kernel<int64_t>, kgrid, kThreads, 0, s, (const int64_t*)index->data, index_stride, n_src, n_dst,
-                    wrap_negative, keys_a, count);
+                    wrap_negative, keys_a, vals_b, count);
   else
     le = launch_pdl(bucket_count_kernel<int32_t>, kgrid, kThreads, 0, s, (const int32_t*)index->data, index_stride, n_src, n_dst,
-                    wrap_negative, keys_a, count);
-  if (le == cudaSuccess) le = launch_pdl(bucket_scan_kernel, p.scan_blocks, kScanThreads, 0, s, count, seg, n_dst, header, status);
-  if (le == cudaSuccess) le = launch_pdl(bucket_scatter_kernel, kgrid, kThreads, 0, s, (const uint32_t*)keys_a, n_src, count, sv);
+                    wrap_negative, keys_a, vals_b, count);
+  if (le == cudaSuccess)
+    le = launch_pdl(bucket_scan_kernel, p.scan_blocks, kScanThreads, 0, s, (const uint32_t*)count, seg, n_dst, header, status);
+  if (le == cudaSuccess)
+    le = launch_pdl(bucket_scatter_kernel, kgrid, kThreads, 0, s, (const uint32_t*)keys_a, (const uint32_t*)vals_b, n_src,
+                    (const uint32_t*)seg, sv);
   if (le == cudaSuccess)
     le = launch_pdl(bucket_sort_segments_kernel, grid_for(n_dst, kThreads, 8), kThreads, 0, s, sv, (const uint32_t*)seg, n_dst, n_src,
                     header, big_list);
