@@ -30,3 +30,9 @@ def test_eccl_world_size_2():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _run(2, 29712)
+
+
+def test_eccl_world_size_4():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs four GPUs")
+    _run(4, 29713)
