@@ -85,6 +85,38 @@ def reference_decode_cpu(x, k_cache, v_cache, pos, w, hidden, heads, kv_heads, h
     return r + (F.silu(gate) * up) @ w["wd"].float().t(), k[:, :, 0], v[:, :, 0]
 
 
+def unfused_layer_autocast(x, p, heads, kv_heads, head_dim, eps=1e-6, theta=10000.0):
+    """The decoder layer written the way a model author writes it, out of stock ATen operators only
+    (pow / mean / rsqrt / mul, mm, cat, F.scaled_dot_product_attention, silu, add): no fused entry point of
+    this backend is called by name. Meant to run under `torch.autocast("gcu", dtype=torch.bfloat16)` with
+    fp32 parameters: the autocast policy casts the operands of every mm and of the attention to bf16 and
+    keeps pow / mean / rsqrt in fp32 (reference: torch_gcu/csrc/aten/gcu_autocast_ops.cpp:28-72).
+    p: wq, wk, wv, wo, wg, wu, wd, n1, n2."""
+    B, S, H = x.shape
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    cos_h, sin_h = rope_tables_cpu(S, head_dim, theta)
+    cos = torch.cat((cos_h, cos_h), -1)[None, :, None, :].to(x.device)
+    sin = torch.cat((sin_h, sin_h), -1)[None, :, None, :].to(x.device)
+
+    def rope(t):
+        half = head_dim // 2
+        rot = torch.cat((-t[..., half:], t[..., :half]), -1)
+        return t * cos + rot * sin
+
+    h = rms(x, p["n1"]).view(B * S, H)
+    q = rope(torch.mm(h, p["wq"].t()).view(B, S, heads, head_dim)).transpose(1, 2)
+    k = rope(torch.mm(h, p["wk"].t()).view(B, S, kv_heads, head_dim)).transpose(1, 2)
+    v = torch.mm(h, p["wv"].t()).view(B, S, kv_heads, head_dim).transpose(1, 2)
+    att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+    r = x + torch.mm(att.transpose(1, 2).reshape(B * S, heads * head_dim), p["wo"].t()).view(B, S, H)
+    h2 = rms(r, p["n2"]).view(B * S, H)
+    mlp = torch.mm(F.silu(torch.mm(h2, p["wg"].t())) * torch.mm(h2, p["wu"].t()), p["wd"].t())
+    return r + mlp.view(B, S, H)
+
+
 class DecoderLayer:
     def __init__(self, weights, tp, backend, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0,
                  device=None):
