@@ -47,7 +47,6 @@ struct AttnParams {
   int64_t o_sb, o_sh, o_ss;  // element strides of out (B,Hq,Sq,D), D contiguous
   float* lse;                // (B,Hq,Sq) contiguous, may be null
   unsigned int* error_word;
-  int poly_exp;   // prefill kernel: a quarter of the exponentials by polynomial (B200_SDPA_POLY=0 turns it off)
 };
 
 template <int D> struct AttCfg {
@@ -582,30 +581,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       }
       const float mb = (m == -CUDART_INF_F ? 0.f : m) * sl2;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      if (p.poly_exp && !need_mask) {
-        // every fourth exponential on the FMA pipe: the special-function unit (16 results per clock per SM)
-        // is as busy as the tensor core in this loop
 #pragma unroll
-        for (int i = 0; i < BKV; i += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
-          const float p3 = ex2_poly(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
-          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-          s[i / 2] = pack_pair<BF16>(p0, p1);
-          s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < BKV; i += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
-          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-          s[i / 2] = pack_pair<BF16>(p0, p1);
-          s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
-        }
+      for (int i = 0; i < BKV; i += 4) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
+        const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
+        const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        s[i / 2] = pack_pair<BF16>(p0, p1);
+        s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
       }
       l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
       tmem_st_32x32(s_tmem, &s[0]);
@@ -1011,8 +995,6 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
     attention_fwd_kernel<D><<<dim3(1, p.Hkv, p.B), kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
   } else {
     p.pair_heads = (p.Hq / p.Hkv) % 2 == 0 ? 1 : 0;
-    static const int poly = [] { const char* e = getenv("B200_SDPA_POLY"); return (e && e[0] == '1') ? 1 : 0; }();
-    p.poly_exp = poly;
     const dim3 grid = p.pair_heads ? dim3((p.Sq + BQ - 1) / BQ, p.Hq / 2, p.B) : dim3((p.Sq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
     if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
     else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);

@@ -181,21 +181,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-
-// 2^x without the special-function unit: round x to the nearest integer n with the 1.5 * 2^23 trick (the
-// low mantissa bits of x + magic hold n), a cubic for 2^f on f = x - n in [-0.5, 0.5] (relative error 7.5e-5,
-// far below the rounding of a 16-bit probability), and n added into the exponent field. Eight FMA / ALU
-// instructions that run beside the MUFU pipe instead of on it. x is clamped to >= -126.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float magic = 12582912.0f;
-  const float xr = x + magic;
-  const float f = x - (xr - magic);
-  float p = fmaf(0.0551716685f, f, 0.2426111251f);
-  p = fmaf(p, f, 0.6932609677f);
-  p = fmaf(p, f, 0.9999280572f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(xr) << 23));
-}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
