@@ -117,6 +117,46 @@ def unfused_layer_autocast(x, p, heads, kv_heads, head_dim, eps=1e-6, theta=1000
     return r + mlp.view(B, S, H)
 
 
+class HostExchange:
+    """CPU stand-in for torch_gcu.distributed.tp_exchange.TensorParallelExchange over a gloo group: the same
+    buffers, row ownership and call sequence, with the fused kernel's arithmetic written in plain torch
+    (sum of the partial products, residual add, one rounding, RMSNorm, gather). It exists so that the
+    sequence-parallel schedule of the exchange path runs on CPU ranks; it is not a product path."""
+
+    def __init__(self, total_rows, hidden, dtype, group, scatter=True):
+        import torch.distributed as dist
+        self.group, self.scatter = group, scatter
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.total_rows, self.hidden = total_rows, hidden
+        self.rows = total_rows // self.world if scatter else total_rows
+        self.row0 = self.rank * self.rows if scatter else 0
+        self.partial = (torch.zeros(total_rows, hidden, dtype=dtype), torch.zeros(total_rows, hidden, dtype=dtype))
+        self.gathered = torch.zeros(total_rows, hidden, dtype=dtype)
+
+    def sync(self, channel=0, signal=True, wait=True):
+        pass   # the gloo collectives below are synchronous
+
+    def reduce_norm(self, partial, residual, residual_out, weight, eps=1e-6, normalise=True):
+        import torch.distributed as dist
+        acc = torch.zeros(self.rows, self.hidden, dtype=torch.float32)
+        if partial is not None:
+            total = self.partial[partial].float().clone()
+            dist.all_reduce(total, group=self.group)
+            acc = total[self.row0:self.row0 + self.rows]
+        if residual is not None:
+            acc = acc + residual.float()
+        h = acc.to(self.gathered.dtype)
+        if residual_out is not None:
+            residual_out.copy_(h)
+        y = _rms_cpu(h, weight, eps) if normalise else h
+        if self.scatter:
+            parts = [torch.empty_like(y) for _ in range(self.world)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            self.gathered.copy_(torch.cat(parts, 0))
+        else:
+            self.gathered.copy_(y)
+
+
 class DecoderLayer:
     def __init__(self, weights, tp, backend, hidden, heads, kv_heads, head_dim, ffn, eps=1e-6, theta=10000.0,
                  device=None):
@@ -178,9 +218,22 @@ class DecoderLayer:
     def attn_from_normed(self, h, B, S, out, kv_out=None):
         """h (B*S, hidden): RMS-normalised input of every row. qkv -> RoPE -> attention -> o_proj; this
         rank's partial product (all rows) goes into `out` (B*S, hidden)."""
-        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
         H = self.hidden
         cos, sin = self.tables(S)
+        if self.backend != "gcu":   # plain torch (the host-side test of the schedule)
+            qkv = (h.float() @ w["wqkv"].float().t()).view(B, S, hq + 2 * hk, d)
+            q = _rope_cpu(qkv[:, :, :hq], cos, sin).transpose(1, 2)
+            k = _rope_cpu(qkv[:, :, hq:hq + hk], cos, sin).transpose(1, 2)
+            v = qkv[:, :, hq + hk:].transpose(1, 2)
+            if kv_out is not None:
+                kv_out[0][:, :, :S].copy_(k)
+                kv_out[1][:, :, :S].copy_(v)
+            g = hq // hk
+            att = F.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), is_causal=True)
+            out.copy_((att.transpose(1, 2).reshape(B * S, hq * d) @ w["wo"].float().t()).to(out.dtype))
+            return
+        eff = self.eff
         if d == 128:
             qkv = eff.linear_rope(h.view(B, S, H), w["wqkv"], cos, sin, hq + hk)
         else:
@@ -195,6 +248,10 @@ class DecoderLayer:
 
     def mlp_from_normed(self, h2, out):
         """h2 (rows, hidden) normalised: gate/up + SwiGLU -> down; this rank's partial product into `out`."""
+        if self.backend != "gcu":
+            gu = h2.float() @ self.w["wgu"].float().t()
+            out.copy_(((F.silu(gu[..., :self.f]) * gu[..., self.f:]) @ self.w["wd"].float().t()).to(out.dtype))
+            return
         act = self.eff.linear_swiglu(h2, self.w["wgu"])
         torch.mm(act, self.w["wd"].t(), out=out)
 
@@ -202,8 +259,20 @@ class DecoderLayer:
         """One new token per sequence, h (B, hidden) normalised: qkv -> RoPE -> cache update -> attention over
         [0, pos] -> o_proj partial into `out` (B, hidden)."""
         B, H = h.shape
-        hq, hk, d, w, eff = self.hq, self.hk, self.head_dim, self.w, self.eff
+        hq, hk, d, w = self.hq, self.hk, self.head_dim, self.w
         cos, sin = self.tables(kv[0].shape[2])
+        if self.backend != "gcu":
+            qkv = (h.float() @ w["wqkv"].float().t()).view(B, 1, hq + 2 * hk, d)
+            positions = self._positions(B, pos)
+            q = _rope_cpu(qkv[:, :, :hq], cos, sin, positions).transpose(1, 2)
+            kv[0][:, :, pos:pos + 1].copy_(_rope_cpu(qkv[:, :, hq:hq + hk], cos, sin, positions).transpose(1, 2))
+            kv[1][:, :, pos:pos + 1].copy_(qkv[:, :, hq + hk:].transpose(1, 2))
+            g = hq // hk
+            att = F.scaled_dot_product_attention(q, kv[0][:, :, :pos + 1].float().repeat_interleave(g, 1),
+                                                 kv[1][:, :, :pos + 1].float().repeat_interleave(g, 1), is_causal=False)
+            out.copy_((att.transpose(1, 2).reshape(B, hq * d) @ w["wo"].float().t()).to(out.dtype))
+            return
+        eff = self.eff
         qkv = torch.mm(h, w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
         eff.rope(qkv[:, :, :hq + hk], cos, sin, self._positions(B, pos), True)
@@ -296,9 +365,12 @@ class DecoderStack:
 
     def _exchange(self, key, rows, scatter, group):
         if key not in self._exchanges:
-            from torch_gcu.distributed.tp_exchange import TensorParallelExchange
-            self._exchanges[key] = TensorParallelExchange(rows, self.cfg["hidden"], self.layers[0].w["wo"].dtype, group,
-                                                          scatter=scatter)
+            dtype = self.layers[0].w["wo"].dtype
+            if self.layers[0].backend != "gcu":
+                self._exchanges[key] = HostExchange(rows, self.cfg["hidden"], dtype, group, scatter=scatter)
+            else:
+                from torch_gcu.distributed.tp_exchange import TensorParallelExchange
+                self._exchanges[key] = TensorParallelExchange(rows, self.cfg["hidden"], dtype, group, scatter=scatter)
         return self._exchanges[key]
 
     def _prefill_exchange_one(self, x, m, group, caches):
@@ -338,6 +410,12 @@ class DecoderStack:
         if n_mb < 1 or x.shape[0] % n_mb != 0:
             n_mb = 1
         part = x.shape[0] // n_mb
+        if self.layers[0].backend != "gcu":   # host ranks: the same microbatches, one after the other
+            outs = []
+            for m in range(n_mb):
+                kv = None if caches is None else [tuple(c[m * part:(m + 1) * part] for c in layer_kv) for layer_kv in caches]
+                outs.append(self._prefill_exchange_one(x[m * part:(m + 1) * part], m, group, kv))
+            return torch.cat(outs, 0)
         main = torch.gcu.current_stream()
         fork = main.record_event()
         outs, joins = [], []
