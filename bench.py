@@ -698,6 +698,73 @@ def run_micro(name):
                       "rate": round(list(work.values())[0] / ms / 1e9, 1)}))
 
 
+def run_micro_tp(rows):
+    """The tensor-parallel exchange kernels alone, on as many ranks as torchrun started: device time of the
+    signal / wait pair, of the fused kernel pulling only, pushing only, and doing both, with the bytes each rank
+    moves over its links per call."""
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if world < 2:
+        raise SystemExit("bench.py --micro tp_exchange runs under torchrun with 2 to 8 ranks")
+    import torch_gcu  # noqa: F401
+    import b200ops
+    import torch.distributed as dist
+    from torch_gcu import _C
+    from torch_gcu.distributed.tp_exchange import TensorParallelExchange
+    os.environ.setdefault("NCCL_DEBUG", "NONE")
+    torch.gcu.set_device(local)
+    dev = torch.device("gcu", local)
+    dist.init_process_group("eccl", rank=rank, world_size=world)
+    H = CFG["hidden"]
+    ex = TensorParallelExchange(rows, H, torch.bfloat16, None, scatter=True)
+    ex.partial[0].copy_(torch.randn(rows, H).bfloat16().to(dev))
+    xl = torch.randn(ex.rows, H).bfloat16().to(dev)
+    w = torch.ones(H).bfloat16().to(dev)
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.gcu.synchronize()
+        s, e = torch.gcu.Event(enable_timing=True), torch.gcu.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.gcu.synchronize()
+        return s.elapsed_time(e) / n * 1e3
+
+    def pull_only():   # reduce over all ranks' partials, rows stored locally only
+        ex.sync()
+        _C._tp_reduce_norm(ex._buffers, ex.rank, ex._off_partial[0], ex._off_gathered, xl, xl, w, ex.row0, ex.total_rows, 1e-6, True, False)
+        ex.sync()
+
+    def push_only():   # nothing to reduce: the normalised rows pushed to every rank
+        ex.sync()
+        ex.reduce_norm(None, xl, None, w)
+        ex.sync()
+
+    def both():
+        ex.sync()
+        ex.reduce_norm(0, xl, xl, w)
+        ex.sync()
+
+    def sync_pair():
+        ex.sync()
+        ex.sync()
+    block = (world - 1) * ex.rows * H * 2   # bytes of the other ranks' rows
+    out = {"micro": "tp_exchange", "ranks": world, "rows": rows, "hidden": H}
+    for name, fn, nbytes in (("sync_pair", sync_pair, 0), ("pull_only", pull_only, block), ("push_only", push_only, block),
+                             ("pull_and_push", both, 2 * block)):
+        us = timed(fn)
+        out[name] = {"us": round(us, 1), "link_bytes_per_rank_and_direction": nbytes,
+                     "gbs_per_direction": round(nbytes / us / 1e3, 1) if nbytes else None}
+    out["device_error_word"] = b200ops.device_error_fetch()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -708,9 +775,13 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the CPU check of the prefill output (profiling aid)")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
     ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
-                         "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures")
+                         "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
+                         "tp_exchange (under torchrun): the exchange kernels alone")
+    ap.add_argument("--rows", type=int, default=8192, help="--micro tp_exchange: rows of the activation (all ranks together)")
     args = ap.parse_args()
-    if args.micro:
+    if args.micro == "tp_exchange":
+        run_micro_tp(args.rows)
+    elif args.micro:
         run_micro(args.micro)
     elif args.impl == "reference":
         run_reference(args)

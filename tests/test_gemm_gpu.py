@@ -210,7 +210,11 @@ def test_mm_skinny_split_k(ops, M, N, K):
 
 
 @pytest.mark.parametrize("M,F,K,dtype", [(2048, 1024, 256, BF), (1000, 1100, 520, BF), (300, 136, 72, torch.float16),
-                                         (4096, 3584, 512, BF)])
+                                         (4096, 3584, 512, BF),
+                                         # one row-tile against a wide weight: the one-wave kernel (tile width chosen
+                                         # so that the tiles fill the SMs: 104 + 104, 48 + 48, 64 + 64 ... rows)
+                                         (64, 14336, 4096, BF), (1, 7168, 512, BF), (128, 7104, 256, torch.float16),
+                                         (37, 9000, 520, BF), (64, 18944, 1024, BF)])
 def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):
     """Gate/up projection with silu(gate) * up applied in the GEMM epilogue, against
     fp32 CPU arithmetic on the same operands; ragged M, F and K."""

@@ -912,6 +912,176 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
   return check_launch("matmul (tcgen05, split-K)");
 }
 
+// ---------------------------------------------------------------------------
+// One-wave kernel for a single row-tile (M <= 128) against a WIDE weight: the product is bound by
+// streaming the weight once, so what matters is that every SM streams an equal share. A tile
+// count fixed by a 128- or 256-column tile leaves the last wave part empty (28672 weight rows in
+// 256-row tiles: 112 tiles on 148 SMs); here the tile width is a run-time value, a multiple of 16
+// chosen so that the tiles fill one wave (28672 rows: 138 tiles of 208), one tile per CTA, the
+// whole K range per CTA, no split and no merge. With SWIGLU the tile's weight rows are bn/2 "gate"
+// rows and the matching bn/2 "up" rows (two TMA boxes per stage) and the epilogue stores
+// silu(gate) * up: bn/2 output columns per tile.
+constexpr int kWideStage = BM * BK * 2 + 256 * BK * 2;   // 16 KB of A + room for 256 weight rows
+constexpr int kWideStages = 4;
+constexpr int kSmemWide = kWideStages * kWideStage + 1024 + 256;
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmParams p, const int bn) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWideStages * kWideStage);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + kWideStages;
+  uint64_t* acc_full = empty + kWideStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tn = blockIdx.x;
+  const int n_k = (p.K + BK - 1) / BK;
+  const int half = bn / 2;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kWideStages; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      const uint32_t stage_bytes = static_cast<uint32_t>(BM * BK * 2 + bn * BK * 2);
+      for (int k = 0; k < n_k; ++k) {
+        const int stage = k % kWideStages;
+        const uint32_t phase = (k / kWideStages) & 1u;
+        if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) break;
+        uint8_t* sa = smem + stage * kWideStage;
+        uint8_t* sb = sa + BM * BK * 2;
+        mbar_arrive_expect_tx(&full[stage], stage_bytes);
+        tma_load_3d(sa, &tmap_a, &full[stage], k * BK, 0, 0);
+        if (SWIGLU) {
+          tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * half, 0);                              // gate rows
+          tma_load_3d(sb + half * (BK * 2), &tmap_b, &full[stage], k * BK, p.up_offset + tn * half, 0);   // up rows
+        } else {
+          tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * bn, 0);
+        }
+      }
+      pdl_launch_dependents();
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(BM, bn, p.is_bf16 != 0, false, false);
+      bool ok = true;
+      for (int k = 0; k < n_k; ++k) {
+        const int stage = k % kWideStages;
+        const uint32_t phase = (k / kWideStages) & 1u;
+        if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * kWideStage);
+        const uint32_t sb = sa + BM * BK * 2;
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; ++kk)
+          umma_f16(tmem_base, smem_desc_sw128(sa + kk * 32, 16u, 1024u), smem_desc_sw128(sb + kk * 32, 16u, 1024u), idesc,
+                   (k | kk) != 0 ? 1u : 0u);
+        umma_commit(&empty[stage]);
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const bool row_ok = row < p.M;
+    if (mbar_wait(acc_full, 0, abort_flag)) {
+      tc_fence_after();
+      uint16_t* orow = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.o_sm;
+      const uint16_t* crow = p.cin ? static_cast<const uint16_t*>(p.cin) + static_cast<int64_t>(row) * p.c_sm : nullptr;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int cols = SWIGLU ? half : bn;     // output columns of this tile
+#pragma unroll 1
+      for (int c = 0; c < cols; c += 32) {
+        uint32_t r[32], ru[32];
+        tmem_ld_32x32(t_row + static_cast<uint32_t>(c), r);
+        if (SWIGLU) tmem_ld_32x32(t_row + static_cast<uint32_t>(half + c), ru);
+        tmem_wait_ld();
+        const int col0 = tn * cols + c;
+        if (!row_ok) continue;
+        for (int j = 0; j < 32; ++j) {
+          const int col = col0 + j;
+          if (c + j >= cols || col >= p.N) break;
+          float v;
+          if (SWIGLU) {
+            const float g0 = __uint_as_float(r[j]);
+            v = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(ru[j]);
+          } else {
+            v = p.alpha * __uint_as_float(r[j]);
+            if (crow) {
+              const uint16_t cb = crow[static_cast<int64_t>(col) * p.c_sn];
+              v += p.beta * (p.is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+            }
+          }
+          orow[col] = p.is_bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 256);
+  }
+  if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
+}
+
+// Columns per tile for the one-wave kernel: the smallest multiple of `unit` that covers `width` columns in at
+// most `sms` tiles; 0 when the product does not suit the kernel (fewer than `at_least` columns per SM: too narrow
+// to give every SM a worthwhile stream; or more than `at_most`: too wide for one wave).
+int wide_tile_width(int64_t width, int unit, int at_least, int at_most, int sms) {
+  int64_t bn = (width + sms - 1) / sms;
+  bn = (bn + unit - 1) / unit * unit;
+  if (bn < at_least || bn > at_most) return 0;
+  return static_cast<int>(bn);
+}
+
+template <bool SWIGLU>
+b200Status launch_wide(const Operand& oa, Operand ob, GemmParams p, int bn, cudaStream_t s) {
+  ob.box[1] = static_cast<uint32_t>(SWIGLU ? bn / 2 : bn);
+  CUtensorMap ta, tb;
+  const char* err = "";
+  B200_REQUIRE(encode_tmap_16bit(&ta, oa.base, 3, oa.dims, oa.strides, oa.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  B200_REQUIRE(encode_tmap_16bit(&tb, ob.base, 3, ob.dims, ob.strides, ob.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
+  static thread_local int last_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev != last_dev) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wide_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemWide);
+    B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
+    last_dev = dev;
+  }
+  const int cols = SWIGLU ? bn / 2 : bn;
+  const int tiles = (p.N + cols - 1) / cols;
+  cudaError_t le = launch_pdl(gemm_wide_kernel<SWIGLU>, tiles, kGemmThreads, kSmemWide, s, ta, tb, p, bn);
+  B200_REQUIRE(le == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(le));
+  return check_launch("matmul (tcgen05, one wave)");
+}
+
 // B200_GEMM_PAIR=0 keeps every product on the one-CTA kernel (for A/B timing).
 bool pair_kernel_enabled() {
   static const bool on = [] {
@@ -1032,6 +1202,12 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
   p.up_offset = (int)F;
   p.error_word = device_error_word();
   B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+  if (M <= BM) {
+    // one row-tile against a wide weight (a decode step): one wave of equal tiles instead of 256-row pair tiles.
+    // Gate and up halves of a tile are multiples of 8 rows (one 128-byte-swizzle atom), 48 to 128 each.
+    const int half = wide_tile_width(F, 8, 48, 128, gemm_sm_budget());
+    if (half > 0) return launch_wide<true>(oa, ob, p, 2 * half, s);
+  }
   return launch_tc2<1>(oa, ob, p, s);
 }
 
