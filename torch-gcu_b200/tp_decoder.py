@@ -377,7 +377,15 @@ class DecoderStack:
         """One microbatch x (B, S, hidden), sequence-parallel between the projections: this rank keeps the
         residual stream of its own 1 / tp of the rows; per projection pair one fused kernel reduces the
         partial products of all ranks for those rows, adds the residual, normalises and scatters the rows
-        to every rank, which the next column-parallel projection then reads locally."""
+        to every rank, which the next column-parallel projection then reads locally.
+
+        Why single buffers are safe here (every `sync` is signal + wait = a barrier over the ranks):
+        * `partial[k]` is overwritten by this rank's next projection only after the barrier that follows the
+          reduce kernel in which the peers read it (a peer signals that barrier after its reduce kernel);
+        * `gathered` is overwritten by the peers' next reduce kernel only after the barrier that follows this
+          rank's projection that read it (this rank signals that barrier after the projection);
+        * the barrier at the top of a pass keeps a fast rank from pushing rows of the next pass into `gathered`
+          while a slow rank still copies the previous result out of it."""
         B, S, H = x.shape
         M = B * S
         ex = self._exchange(("prefill", m, M), M, True, group)
@@ -438,7 +446,13 @@ class DecoderStack:
     def decode_exchange(self, x, caches, pos, group):
         """One decode step with the peer-memory exchange: few rows, so every rank reduces all of them for
         itself (one kernel per projection pair that pulls the other ranks' partial rows, adds the residual and
-        normalises); the residual stream stays replicated and nothing is gathered."""
+        normalises); the residual stream stays replicated and nothing is gathered.
+
+        Two partial buffers alternate because nothing is gathered here, so no wait orders a peer's read of this
+        rank's o_proj partial before this rank's down projection writes: the down projection writes `partial[1]`
+        instead. `partial[0]` is rewritten by the next layer's o_proj, which runs after this rank has waited for the
+        peers' "down partial ready" signal, and a peer sends that only after its read of `partial[0]`; the same
+        argument, one phase later, covers `partial[1]` (also across the end of a step)."""
         B, _, H = x.shape
         ex = self._exchange(("decode", B), B, False, group)
         r = x.view(B, H)
