@@ -214,7 +214,8 @@ def test_mm_skinny_split_k(ops, M, N, K):
                                          # one row-tile against a wide weight: the one-wave kernel (tile width chosen
                                          # so that the tiles fill the SMs: 104 + 104, 48 + 48, 64 + 64 ... rows)
                                          (64, 14336, 4096, BF), (1, 7168, 512, BF), (128, 7104, 256, torch.float16),
-                                         (37, 9000, 520, BF), (64, 18944, 1024, BF)])
+                                         (37, 9000, 520, BF), (64, 18944, 1024, BF), (64, 1792, 4096, BF), (64, 3584, 1024, BF),
+                                         (16, 2368, 256, torch.float16), (3, 1200, 136, BF), (128, 200, 64, BF)])
 def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):
     """Gate/up projection with silu(gate) * up applied in the GEMM epilogue, against
     fp32 CPU arithmetic on the same operands; ragged M, F and K."""

@@ -921,9 +921,9 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
 // whole K range per CTA, no split and no merge. With SWIGLU the tile's weight rows are bn/2 "gate"
 // rows and the matching bn/2 "up" rows (two TMA boxes per stage) and the epilogue stores
 // silu(gate) * up: bn/2 output columns per tile.
-constexpr int kWideStage = BM * BK * 2 + 256 * BK * 2;   // 16 KB of A + room for 256 weight rows
-constexpr int kWideStages = 4;
-constexpr int kSmemWide = kWideStages * kWideStage + 1024 + 256;
+constexpr int kWideRing = 196608;        // stages of 16 KB of A + bn x 128 B of weight rows: as many as fit (at most 12)
+constexpr int kWideMaxStages = 12;       // narrow tiles need depth: the stream per SM is stages x weight bytes per round trip
+constexpr int kSmemWide = kWideRing + 1024 + 256;
 
 template <bool SWIGLU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -931,10 +931,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmParams p, const int bn) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWideStages * kWideStage);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kWideRing);
   uint64_t* full = bars;
-  uint64_t* empty = bars + kWideStages;
-  uint64_t* acc_full = empty + kWideStages;
+  uint64_t* empty = bars + kWideMaxStages;
+  uint64_t* acc_full = empty + kWideMaxStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -942,9 +942,11 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int tn = blockIdx.x;
   const int n_k = (p.K + BK - 1) / BK;
   const int half = bn / 2;
+  const int stage_stride = BM * BK * 2 + bn * BK * 2;   // a multiple of 2 KB (bn is a multiple of 16)
+  const int n_stages = min(kWideMaxStages, kWideRing / stage_stride);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kWideStages; ++i) {
+    for (int i = 0; i < n_stages; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
@@ -966,12 +968,12 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
-      const uint32_t stage_bytes = static_cast<uint32_t>(BM * BK * 2 + bn * BK * 2);
+      const uint32_t stage_bytes = static_cast<uint32_t>(stage_stride);
       for (int k = 0; k < n_k; ++k) {
-        const int stage = k % kWideStages;
-        const uint32_t phase = (k / kWideStages) & 1u;
+        const int stage = k % n_stages;
+        const uint32_t phase = (k / n_stages) & 1u;
         if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) break;
-        uint8_t* sa = smem + stage * kWideStage;
+        uint8_t* sa = smem + stage * stage_stride;
         uint8_t* sb = sa + BM * BK * 2;
         mbar_arrive_expect_tx(&full[stage], stage_bytes);
         tma_load_3d(sa, &tmap_a, &full[stage], k * BK, 0, 0);
@@ -989,11 +991,11 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t idesc = make_idesc(BM, bn, p.is_bf16 != 0, false, false);
       bool ok = true;
       for (int k = 0; k < n_k; ++k) {
-        const int stage = k % kWideStages;
-        const uint32_t phase = (k / kWideStages) & 1u;
+        const int stage = k % n_stages;
+        const uint32_t phase = (k / n_stages) & 1u;
         if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + stage * kWideStage);
+        const uint32_t sa = smem_u32(smem + stage * stage_stride);
         const uint32_t sb = sa + BM * BK * 2;
 #pragma unroll
         for (int kk = 0; kk < BK / UMMA_K; ++kk)
@@ -1204,7 +1206,9 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
   B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
   if (M <= BM) {
     // one row-tile against a wide weight (a decode step): one wave of equal tiles instead of 256-row pair tiles.
-    // Gate and up halves of a tile are multiples of 8 rows (one 128-byte-swizzle atom), 48 to 128 each.
+    // Gate and up halves of a tile are multiples of 8 rows (one 128-byte-swizzle atom), 48 to 128 each
+    // (measured: with narrower tiles, i.e. F below ~7000, the pair kernel is faster: 25.0 against 29.7 us at
+    // F = 3584, 24.0 against 27.1 us at F = 1792; above, this kernel wins: 51.2 against 56 us at F = 14336).
     const int half = wide_tile_width(F, 8, 48, 128, gemm_sm_budget());
     if (half > 0) return launch_wide<true>(oa, ob, p, 2 * half, s);
   }
