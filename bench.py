@@ -676,6 +676,28 @@ def run_micro(name):
         w = (torch.randn(28672, 4096, device=dev) * 0.02).to(bf)
         out = torch.empty(64, 28672, dtype=bf, device=dev)
         fn, work = ops.bind("mm", out, a, w.t()), {"bytes": w.numel() * 2}
+    elif name == "gemm_wide":
+        # decode-shaped gate/up product with the SwiGLU epilogue: 64 rows against a (2 x 14336, 4096) weight
+        a = torch.randn(64, 4096, device=dev).to(bf)
+        w = (torch.randn(2 * 14336, 4096, device=dev) * 0.02).to(bf)
+        out = torch.empty(64, 14336, dtype=bf, device=dev)
+        fn, work = ops.bind("mm_swiglu", out, a, w), {"bytes": w.numel() * 2}
+    elif name == "tp_reduce_norm":
+        # the fused exchange kernel on ONE GPU: the eight "ranks" are eight local buffers, rank 3 owns 1024 of
+        # 8192 rows (what one rank of eight does per call, with HBM in place of the links)
+        world, rows_all, hid = 8, 8192, 4096
+        parts = [torch.randn(rows_all, hid, device=dev).to(bf) for _ in range(world)]
+        gath = [torch.empty(rows_all, hid, dtype=bf, device=dev) for _ in range(world)]
+        xl = torch.randn(rows_all // world, hid, device=dev).to(bf)
+        w_ = torch.ones(hid, device=dev).to(bf)
+        tp, tg = ops.tp_peers(parts, 3), ops.tp_peers(gath, 3)
+        call = ops.bind("tp_reduce_norm", ctypes.byref(tp), ctypes.byref(tg), xl, xl, w_, ctypes.c_int64(3 * 1024),
+                        ctypes.c_int64(rows_all), ctypes.c_double(1e-6), ctypes.c_int32(1), ctypes.c_int32(1), keep=(tp, tg, parts, gath))
+        fn, work = call, {"bytes": 2 * world * (rows_all // world) * hid * 2}
+    elif name == "cumsum":
+        p_ = torch.softmax(torch.randn(512, 128256, device=dev), -1)
+        o_ = torch.empty_like(p_)
+        fn, work = ops.bind("cumsum", o_, p_, ctypes.c_int64(1)), {"bytes": 2 * p_.numel() * 4}
     elif name == "sort":
         p = torch.softmax(torch.randn(64, 128256, device=dev), -1)
         v = torch.empty_like(p)
@@ -774,7 +796,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the CPU check of the prefill output (profiling aid)")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
-    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
+    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
                          "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
                          "tp_exchange (under torchrun): the exchange kernels alone")
     ap.add_argument("--rows", type=int, default=8192, help="--micro tp_exchange: rows of the activation (all ranks together)")
