@@ -787,6 +787,48 @@ def run_micro_tp(rows):
     dist.destroy_process_group()
 
 
+def run_timeline(args):
+    """Where a tensor-parallel prefill pass spends its time, per microbatch stream: eager passes with a pair
+    of events around every phase (attention part, mlp part, exchange kernel, signal / wait), summed per phase.
+    Phases of the two microbatches overlap, so the sums exceed the pass time; `pass_ms` is the pass itself."""
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    if world < 2:
+        raise SystemExit("bench.py --timeline runs under torchrun with 2 to 8 ranks")
+    import torch_gcu  # noqa: F401
+    import torch.distributed as dist
+    from tp_decoder import DecoderStack
+    os.environ.setdefault("NCCL_DEBUG", "NONE")
+    torch.gcu.set_device(local)
+    dev = torch.device("gcu", local)
+    dist.init_process_group("eccl", rank=rank, world_size=world)
+    stack = DecoderStack(N_LAYERS, world, rank, "gcu", dev, torch.bfloat16, CFG)
+    x = torch.randn(PREFILL_B, PREFILL_S, CFG["hidden"], generator=torch.Generator().manual_seed(1234)).bfloat16().to(dev)
+    for _ in range(3):
+        stack.prefill(x, dist.group.WORLD)
+    reps = 5
+    sums, pass_ms = {}, 0.0
+    for _ in range(reps):
+        dist.barrier()
+        torch.gcu.synchronize()
+        stack.timeline = []
+        s, e = torch.gcu.Event(enable_timing=True), torch.gcu.Event(enable_timing=True)
+        s.record()
+        stack.prefill(x, dist.group.WORLD)
+        e.record()
+        torch.gcu.synchronize()
+        pass_ms += s.elapsed_time(e) / reps
+        for name, m, a, b in stack.timeline:
+            sums[(name, m)] = sums.get((name, m), 0.0) + a.elapsed_time(b) / reps
+        stack.timeline = None
+    if rank == 0:
+        out = {"timeline": "tensor-parallel prefill, eager, exchange over peer memory", "ranks": world,
+               "microbatches": int(os.environ.get("TP_DECODER_MICROBATCHES", "2")), "pass_ms": round(pass_ms, 3),
+               "phase_ms_per_microbatch": {"%s / mb %d" % k: round(v, 3) for k, v in sorted(sums.items())}}
+        print(json.dumps(out), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -799,9 +841,12 @@ def main():
     ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
                          "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
                          "tp_exchange (under torchrun): the exchange kernels alone")
+    ap.add_argument("--timeline", action="store_true", help="under torchrun: per-phase device times of an eager tensor-parallel prefill pass")
     ap.add_argument("--rows", type=int, default=8192, help="--micro tp_exchange: rows of the activation (all ranks together)")
     args = ap.parse_args()
-    if args.micro == "tp_exchange":
+    if args.timeline:
+        run_timeline(args)
+    elif args.micro == "tp_exchange":
         run_micro_tp(args.rows)
     elif args.micro:
         run_micro(args.micro)

@@ -354,6 +354,7 @@ class DecoderStack:
                                     backend, device=device, **cfg) for i in range(n_layers)]
         self.cfg, self.tp = cfg, tp
         self._exchanges, self._side_streams = {}, {}
+        self.timeline = None   # set to a list to collect (phase, microbatch, start, end) events of eager exchange passes
 
     # ---- the exchange over peer memory (default for tp > 1 on the device) -----------------------
     def uses_peer_exchange(self):
@@ -389,24 +390,34 @@ class DecoderStack:
         B, S, H = x.shape
         M = B * S
         ex = self._exchange(("prefill", m, M), M, True, group)
+        tl = self.timeline   # None, or a list that takes (phase, microbatch, start event, end event)
+
+        def phase(name, fn):
+            if tl is None:
+                return fn()
+            s = torch.gcu.current_stream().record_event(torch.gcu.Event(enable_timing=True))
+            r = fn()
+            tl.append((name, m, s, torch.gcu.current_stream().record_event(torch.gcu.Event(enable_timing=True))))
+            return r
         xl = x.reshape(M, H)[ex.row0:ex.row0 + ex.rows].clone()   # this rank's rows of the residual stream
-        ex.sync()                                                  # every rank is done with the previous pass's buffers
-        ex.reduce_norm(None, xl, None, self.layers[0].w["norm1"], self.layers[0].eps)
-        ex.sync()
+        phase("wait", ex.sync)                                     # every rank is done with the previous pass's buffers
+        phase("exchange", lambda: ex.reduce_norm(None, xl, None, self.layers[0].w["norm1"], self.layers[0].eps))
+        phase("wait", ex.sync)
         n = len(self.layers)
         for i, layer in enumerate(self.layers):
             kv = None if caches is None else caches[i]
-            layer.attn_from_normed(ex.gathered, B, S, ex.partial[0], kv)
-            ex.sync()                                              # the partial products are complete on every rank
-            ex.reduce_norm(0, xl, xl, layer.w["norm2"], layer.eps)
-            ex.sync()                                              # every rank's rows have landed here
-            layer.mlp_from_normed(ex.gathered, ex.partial[1])
-            ex.sync()
+            phase("attention part", lambda: layer.attn_from_normed(ex.gathered, B, S, ex.partial[0], kv))
+            phase("wait", ex.sync)                                 # the partial products are complete on every rank
+            phase("exchange", lambda: ex.reduce_norm(0, xl, xl, layer.w["norm2"], layer.eps))
+            phase("wait", ex.sync)                                 # every rank's rows have landed here
+            phase("mlp part", lambda: layer.mlp_from_normed(ex.gathered, ex.partial[1]))
+            phase("wait", ex.sync)
             if i + 1 < n:
-                ex.reduce_norm(1, xl, xl, self.layers[i + 1].w["norm1"], self.layers[i + 1].eps)
+                nxt = self.layers[i + 1]
+                phase("exchange", lambda: ex.reduce_norm(1, xl, xl, nxt.w["norm1"], nxt.eps))
             else:
-                ex.reduce_norm(1, xl, xl, None, normalise=False)   # the last residual rows, gathered as they are
-            ex.sync()
+                phase("exchange", lambda: ex.reduce_norm(1, xl, xl, None, normalise=False))   # the last rows, gathered as they are
+            phase("wait", ex.sync)
         return ex.gathered.clone().view(B, S, H)
 
     def prefill_exchange(self, x, group, caches=None):
