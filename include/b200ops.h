@@ -131,6 +131,9 @@ b200Status b200_sub(const b200Tensor* out, const b200Tensor* a, const b200Tensor
 b200Status b200_div(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b,
                     b200Stream stream);
 b200Status b200_fill(const b200Tensor* out, double value, b200Stream stream);
+/* The same for an int64 tensor and an integer value that a double cannot carry (|value| > 2^53):
+ * ATen keeps integer scalars exact.                                                   */
+b200Status b200_fill_i64(const b200Tensor* out, int64_t value, b200Stream stream);
 
 /* ---- copy / cast (reference: aotops::_copy_from -> copy_device_to_device ->
  *      topsatenCopy, torch_gcu/csrc/aten/aot_ops/gcu_copy.cpp:34-198,402-442)

@@ -153,6 +153,20 @@ def test_config_ops_through_dispatcher(dev):
     run_op_test(torch.neg, dev, src, exact=True)
 
 
+def test_int64_scalars_beyond_2_53_stay_exact(dev):
+    """Integer scalar operands that a double cannot carry: fill, full, add, sub and mul keep them exact, as ATen does."""
+    big = 2 ** 60 + 1
+    assert torch.full((3,), big, dtype=torch.int64, device=dev).cpu().tolist() == [big] * 3
+    x = torch.arange(5, dtype=torch.int64)
+    assert torch.equal((x.to(dev) + big).cpu(), x + big)
+    assert torch.equal((x.to(dev) - big).cpu(), x - big)
+    assert torch.equal((big + x.to(dev)).cpu(), big + x)
+    assert torch.equal((x.to(dev) * (2 ** 55 + 3)).cpu(), x * (2 ** 55 + 3))
+    t = torch.zeros(4, dtype=torch.int64, device=dev)
+    t.fill_(-big)
+    assert t.cpu().tolist() == [-big] * 4
+
+
 def test_int32_index_efficient_op(dev):
     import torch_gcu
     from torch_gcu.gcu.efficient.op import gcu_index

@@ -109,6 +109,33 @@ def test_scatter_add_bad_index_is_dropped_and_flagged(ops):
     exact(out, ref)
 
 
+def test_scatter_add_element_form_four_pass_sort_with_a_bad_index(ops):
+    """Element form (a full index tensor) over more than 2^24 destination elements: the stable sort of
+    (destination offset, source) takes four 8-bit passes, and its top digit reaches bit 24-30 while bit 31
+    carries the out-of-range flag. One bad index must drop that element only (error word bit 0), not
+    disturb the order of the rest."""
+    g = torch.Generator().manual_seed(29)
+    R, C = (1 << 21) + 3, 8                       # 16.8 M destination elements: 25 key bits
+    base = torch.zeros(R, C)
+    n = 3000
+    idx = torch.randint(0, R, (n, C), generator=g)
+    idx[:200] = idx[0]                             # collisions: ordered sums
+    idx[:, 0] = R - 1                              # the top of the key range
+    src = torch.randn(n, C, generator=g)
+    ref = aten_cpu.scatter_add(base, 0, idx, src)
+    bad = idx.clone()
+    bad[1234, 5] = R                               # out of range
+    ref_bad = ref.clone()
+    ref_bad[idx[1234, 5], 5] = aten_cpu.scatter_add(torch.zeros(R, 1), 0, torch.cat([idx[:1234, 5:6], idx[1235:, 5:6]]),
+                                                    torch.cat([src[:1234, 5:6], src[1235:, 5:6]]))[idx[1234, 5], 0]
+    for index, want, flagged in ((idx, ref, False), (bad, ref_bad, True)):
+        ws = _ws(ops.scatter_add_workspace_size(dev(base), 0, dev(index), dev(src)))
+        out = torch.empty_like(dev(base))
+        ops.scatter_add(out, dev(base), 0, dev(index), dev(src), ws)
+        assert bool(ops.device_error_fetch() & 1) == flagged
+        exact(out, want)
+
+
 def test_scatter_add_all_sources_one_row(ops):
     """Worst-case collision: one destination takes every source, in order."""
     g = torch.Generator().manual_seed(25)

@@ -202,6 +202,10 @@ def fill(out, value, stream=None):
     check(lib().b200_fill(_ref(view(out)), ctypes.c_double(value), _stream(stream)))
 
 
+def fill_i64(out, value, stream=None):
+    check(lib().b200_fill_i64(_ref(view(out)), ctypes.c_int64(value), _stream(stream)))
+
+
 def copy(dst, src, stream=None):
     check(lib().b200_copy(_ref(view(dst)), _ref(view(src)), _stream(stream)))
 

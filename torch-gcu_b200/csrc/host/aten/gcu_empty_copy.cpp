@@ -240,6 +240,10 @@ at::Tensor& fill__Scalar(at::Tensor& self, const at::Scalar& value) {
   c10::OptionalDeviceGuard g(self.device());
   b200Tensor v = to_b200(self);
   cudaStream_t stream = current_stream(self);
+  if (self.scalar_type() == at::kLong && value.isIntegral(false)) {
+    GCU_KERNEL_CALL(b200_fill_i64, stream, &v, value.toLong());   // exact beyond 2^53, where a double is not
+    return self;
+  }
   const double x = value.isBoolean() ? static_cast<double>(value.toBool()) : value.toDouble();
   GCU_KERNEL_CALL(b200_fill, stream, &v, x);
   return self;

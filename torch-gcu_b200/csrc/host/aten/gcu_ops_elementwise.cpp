@@ -48,7 +48,16 @@ void binary_impl(at::TensorIteratorBase& iter, Bin kind, const at::Scalar& alpha
   OutStage st(out, common);
   b200Tensor vo = to_b200(st.work);
   cudaStream_t stream = current_stream(out);
-  const bool sa = cpu_scalar(iter, 1), sb = cpu_scalar(iter, 2);
+  bool sa = cpu_scalar(iter, 1), sb = cpu_scalar(iter, 2);
+  // the scalar entry points carry the operand as a double: an int64 operand beyond 2^53 would be rounded, so
+  // such a scalar goes to the device as a 0-d tensor instead (filled exactly) and takes the tensor kernel
+  auto too_big = [&](const at::Tensor& t) {
+    if (common != at::kLong || !c10::isIntegralType(t.scalar_type(), false)) return false;
+    const int64_t v = t.item().toLong();
+    return v > (int64_t(1) << 53) || v < -(int64_t(1) << 53);
+  };
+  if (sa && too_big(ta)) sa = false;
+  if (sb && too_big(tb)) sb = false;
   if (sb && !sa && (kind == Bin::Add || kind == Bin::Sub || kind == Bin::Mul)) {
     // tensor (op) host scalar: scalar kernel, the device never sees the host pointer
     at::Tensor a = prep_input(ta, common, out.sizes());

@@ -426,4 +426,16 @@ b200Status b200_fill(const b200Tensor* out, double value, b200Stream stream) {
   return check_launch("b200_fill");
 }
 
+b200Status b200_fill_i64(const b200Tensor* out, int64_t value, b200Stream stream) {
+  B200_REQUIRE(valid(out), B200_BAD_PARAM, "b200_fill_i64: invalid tensor view");
+  B200_REQUIRE(out->dtype == B200_I64, B200_BAD_PARAM, "b200_fill_i64: an int64 tensor is expected");
+  const int64_t n = numel(out);
+  if (n == 0) return B200_OK;
+  const b200Tensor* ts[1] = {out};
+  auto ix = make_indexer<1>(ts);
+  fill_kernel<int64_t><<<grid_for(n, 256, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>((int64_t*)out->data, n, ix, value,
+                                                                                         is_contiguous(out));
+  return check_launch("b200_fill_i64");
+}
+
 }  // extern "C"
