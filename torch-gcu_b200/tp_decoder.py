@@ -374,11 +374,16 @@ class DecoderStack:
                 self._exchanges[key] = TensorParallelExchange(rows, self.cfg["hidden"], dtype, group, scatter=scatter)
         return self._exchanges[key]
 
-    def _prefill_exchange_one(self, x, m, group, caches):
+    def _prefill_exchange_program(self, x, m, group, caches, result):
         """One microbatch x (B, S, hidden), sequence-parallel between the projections: this rank keeps the
         residual stream of its own 1 / tp of the rows; per projection pair one fused kernel reduces the
         partial products of all ranks for those rows, adds the residual, normalises and scatters the rows
         to every rank, which the next column-parallel projection then reads locally.
+
+        A generator: before every phase it yields the phase's kind, "compute" (projections and attention:
+        they want the SMs) or "exchange" (signal / wait and the fused kernel: they want the links); the
+        caller resumes it on the microbatch's stream and uses the kinds to interleave the microbatches.
+        The output lands in result[m].
 
         Why single buffers are safe here (every `sync` is signal + wait = a barrier over the ranks):
         * `partial[k]` is overwritten by this rank's next projection only after the barrier that follows the
@@ -399,60 +404,87 @@ class DecoderStack:
             r = fn()
             tl.append((name, m, s, torch.gcu.current_stream().record_event(torch.gcu.Event(enable_timing=True))))
             return r
+
+        def exchange(partial, weight, eps, normalise=True):
+            phase("wait", ex.sync)         # the partial products are complete on every rank (or: the buffers are free)
+            phase("exchange", lambda: ex.reduce_norm(partial, xl, None if partial is None else xl, weight, eps, normalise))
+            phase("wait", ex.sync)         # every rank's rows have landed here
+
+        yield "compute"
         xl = x.reshape(M, H)[ex.row0:ex.row0 + ex.rows].clone()   # this rank's rows of the residual stream
-        phase("wait", ex.sync)                                     # every rank is done with the previous pass's buffers
-        phase("exchange", lambda: ex.reduce_norm(None, xl, None, self.layers[0].w["norm1"], self.layers[0].eps))
-        phase("wait", ex.sync)
+        yield "exchange"
+        exchange(None, self.layers[0].w["norm1"], self.layers[0].eps)
         n = len(self.layers)
         for i, layer in enumerate(self.layers):
             kv = None if caches is None else caches[i]
+            yield "compute"
             phase("attention part", lambda: layer.attn_from_normed(ex.gathered, B, S, ex.partial[0], kv))
-            phase("wait", ex.sync)                                 # the partial products are complete on every rank
-            phase("exchange", lambda: ex.reduce_norm(0, xl, xl, layer.w["norm2"], layer.eps))
-            phase("wait", ex.sync)                                 # every rank's rows have landed here
+            yield "exchange"
+            exchange(0, layer.w["norm2"], layer.eps)
+            yield "compute"
             phase("mlp part", lambda: layer.mlp_from_normed(ex.gathered, ex.partial[1]))
-            phase("wait", ex.sync)
+            yield "exchange"
             if i + 1 < n:
-                nxt = self.layers[i + 1]
-                phase("exchange", lambda: ex.reduce_norm(1, xl, xl, nxt.w["norm1"], nxt.eps))
+                exchange(1, self.layers[i + 1].w["norm1"], self.layers[i + 1].eps)
             else:
-                phase("exchange", lambda: ex.reduce_norm(1, xl, xl, None, normalise=False))   # the last rows, gathered as they are
-            phase("wait", ex.sync)
-        return ex.gathered.clone().view(B, S, H)
+                exchange(1, None, 0.0, normalise=False)   # the last residual rows, gathered as they are
+        yield "compute"
+        result[m] = ex.gathered.clone().view(B, S, H)
 
     def prefill_exchange(self, x, group, caches=None):
         """Prefill with the peer-memory exchange. The batch is cut into microbatches on streams of their own
-        (TP_DECODER_MICROBATCHES, default 2), so the exchange kernels of one run beside the GEMMs and the
-        attention of the other: they are small blocks that share the SMs with a resident GEMM block."""
+        (TP_DECODER_MICROBATCHES, default 2). Their compute phases are chained through events in a fixed
+        order (attention part of microbatch 0, of microbatch 1, mlp part of 0, of 1, ...), so each has the SMs
+        to itself, and the exchange phase that follows a compute phase runs under the NEXT compute phase of
+        the other microbatch: the exchange kernels are small blocks that share the SMs with a resident GEMM
+        block. Left to themselves two streams fall into step (both compute, then both exchange) and hide
+        nothing."""
         import os
         n_mb = int(os.environ.get("TP_DECODER_MICROBATCHES", "2"))
         if n_mb < 1 or x.shape[0] % n_mb != 0:
             n_mb = 1
         part = x.shape[0] // n_mb
-        if self.layers[0].backend != "gcu":   # host ranks: the same microbatches, one after the other
-            outs = []
-            for m in range(n_mb):
-                kv = None if caches is None else [tuple(c[m * part:(m + 1) * part] for c in layer_kv) for layer_kv in caches]
-                outs.append(self._prefill_exchange_one(x[m * part:(m + 1) * part], m, group, kv))
-            return torch.cat(outs, 0)
+        result = [None] * n_mb
+
+        def kv_of(m):
+            return None if caches is None else [tuple(c[m * part:(m + 1) * part] for c in layer_kv) for layer_kv in caches]
+        programs = [self._prefill_exchange_program(x[m * part:(m + 1) * part], m, group, kv_of(m), result) for m in range(n_mb)]
+        if self.layers[0].backend != "gcu":   # host ranks: the same microbatches and phases, no streams
+            for prog in programs:
+                for _ in prog:
+                    pass
+            return result[0] if n_mb == 1 else torch.cat(result, 0)
         main = torch.gcu.current_stream()
-        fork = main.record_event()
-        outs, joins = [], []
-        for m in range(n_mb):
-            kv = None if caches is None else [tuple(c[m * part:(m + 1) * part] for c in layer_kv) for layer_kv in caches]
-            if m == 0:
-                outs.append(self._prefill_exchange_one(x[:part], 0, group, kv))
-                continue
+        streams = [main]
+        for m in range(1, n_mb):
             if m not in self._side_streams:
                 self._side_streams[m] = torch.gcu.Stream()
-            s = self._side_streams[m]
+            streams.append(self._side_streams[m])
+        fork = main.record_event()
+        for s in streams[1:]:
             s.wait_event(fork)
-            with torch.gcu.stream(s):
-                outs.append(self._prefill_exchange_one(x[m * part:(m + 1) * part], m, group, kv))
-                joins.append(s.record_event())
-        for e in joins:
-            main.wait_event(e)
-        return outs[0] if n_mb == 1 else torch.cat(outs, 0)
+        kinds = [next(prog) for prog in programs]   # the kind of every microbatch's first phase; nothing has run yet
+        chain = None                                # completion of the compute phase issued last, on whichever stream
+        live = n_mb
+        while live:
+            for m in range(n_mb):
+                if kinds[m] is None:
+                    continue
+                s = streams[m]
+                with torch.gcu.stream(s):
+                    compute = kinds[m] == "compute"
+                    if compute and chain is not None:
+                        s.wait_event(chain)
+                    try:
+                        kinds[m] = next(programs[m])   # runs the phase that was announced, announces the next
+                    except StopIteration:
+                        kinds[m] = None
+                        live -= 1
+                    if compute:
+                        chain = s.record_event()
+        for s in streams[1:]:
+            main.wait_event(s.record_event())
+        return result[0] if n_mb == 1 else torch.cat(result, 0)
 
     def decode_exchange(self, x, caches, pos, group):
         """One decode step with the peer-memory exchange: few rows, so every rank reduces all of them for
