@@ -478,15 +478,23 @@ class DecoderStack:
                 for _ in prog:
                     pass
             return result[0] if n_mb == 1 else torch.cat(result, 0)
+        # Two streams per microbatch: its compute phases on a HIGH-priority stream, its exchange phases on a
+        # normal one, events handing over between them. Priority decides which pending blocks get an SM
+        # first: when a GEMM and an exchange kernel become ready together, the GEMM's one block per SM is
+        # placed first and the exchange blocks fill what is left beside it. The other way round the exchange
+        # blocks (four fit on an empty SM) fill the register files and the GEMM's blocks wait for them to
+        # drain (measured at eight ranks: compute phases took 1.9 x as long).
         main = torch.gcu.current_stream()
-        streams = [main]
-        for m in range(1, n_mb):
-            if m not in self._side_streams:
-                self._side_streams[m] = torch.gcu.Stream()
-            streams.append(self._side_streams[m])
+        use_priority = os.environ.get("TP_DECODER_PRIORITY", "1") != "0"
+
+        def side(key, priority):
+            if key not in self._side_streams:
+                self._side_streams[key] = torch.gcu.Stream(priority=priority)
+            return self._side_streams[key]
+        compute_stream = [side((m, "compute"), -1 if use_priority else 0) for m in range(n_mb)]
+        exchange_stream = [side((m, "exchange"), 0) if use_priority else compute_stream[m] for m in range(n_mb)]
         fork = main.record_event()
-        for s in streams[1:]:
-            s.wait_event(fork)
+        last = [fork] * n_mb                        # completion of each microbatch's latest phase
         kinds = [next(prog) for prog in programs]   # the kind of every microbatch's first phase; nothing has run yet
         chain = None                                # completion of the compute / attention phase issued last, on whichever stream
         live = n_mb
@@ -494,9 +502,10 @@ class DecoderStack:
             for m in range(n_mb):
                 if kinds[m] is None:
                     continue
-                s = streams[m]
                 kind = kinds[m]
+                s = exchange_stream[m] if kind == "exchange" else compute_stream[m]
                 with torch.gcu.stream(s):
+                    s.wait_event(last[m])
                     if kind != "exchange" and chain is not None:
                         s.wait_event(chain)
                     try:
@@ -504,10 +513,11 @@ class DecoderStack:
                     except StopIteration:
                         kinds[m] = None
                         live -= 1
+                    last[m] = s.record_event()
                     if kind != "exchange":
-                        chain = s.record_event()
-        for s in streams[1:]:
-            main.wait_event(s.record_event())
+                        chain = last[m]
+        for m in range(n_mb):
+            main.wait_event(last[m])
         return result[0] if n_mb == 1 else torch.cat(result, 0)
 
     def decode_exchange(self, x, caches, pos, group):
