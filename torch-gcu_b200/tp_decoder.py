@@ -462,7 +462,9 @@ class DecoderStack:
         block. Left to themselves two streams fall into step (both compute, then both exchange) and hide
         nothing. (Measured at four ranks: two free-running streams 14.9 ms per pass, the chain 14.6 ms; also
         keeping the attention kernel, whose blocks fill an SM's register file, apart from the other
-        microbatch's exchange: 15.8 ms -- the extra waits cost more than the interference they remove.)"""
+        microbatch's exchange: 15.8 ms -- the extra waits cost more than the interference they remove. Compute
+        phases on high-priority streams and exchange phases on normal ones, so that a GEMM's blocks are placed
+        before the exchange blocks that became ready with it: 15.6 ms, no better either.)"""
         import os
         n_mb = int(os.environ.get("TP_DECODER_MICROBATCHES", "2"))
         if n_mb < 1 or x.shape[0] % n_mb != 0:
@@ -478,23 +480,15 @@ class DecoderStack:
                 for _ in prog:
                     pass
             return result[0] if n_mb == 1 else torch.cat(result, 0)
-        # Two streams per microbatch: its compute phases on a HIGH-priority stream, its exchange phases on a
-        # normal one, events handing over between them. Priority decides which pending blocks get an SM
-        # first: when a GEMM and an exchange kernel become ready together, the GEMM's one block per SM is
-        # placed first and the exchange blocks fill what is left beside it. The other way round the exchange
-        # blocks (four fit on an empty SM) fill the register files and the GEMM's blocks wait for them to
-        # drain (measured at eight ranks: compute phases took 1.9 x as long).
         main = torch.gcu.current_stream()
-        use_priority = os.environ.get("TP_DECODER_PRIORITY", "1") != "0"
-
-        def side(key, priority):
-            if key not in self._side_streams:
-                self._side_streams[key] = torch.gcu.Stream(priority=priority)
-            return self._side_streams[key]
-        compute_stream = [side((m, "compute"), -1 if use_priority else 0) for m in range(n_mb)]
-        exchange_stream = [side((m, "exchange"), 0) if use_priority else compute_stream[m] for m in range(n_mb)]
+        streams = [main]
+        for m in range(1, n_mb):
+            if m not in self._side_streams:
+                self._side_streams[m] = torch.gcu.Stream()
+            streams.append(self._side_streams[m])
         fork = main.record_event()
-        last = [fork] * n_mb                        # completion of each microbatch's latest phase
+        for s in streams[1:]:
+            s.wait_event(fork)
         kinds = [next(prog) for prog in programs]   # the kind of every microbatch's first phase; nothing has run yet
         chain = None                                # completion of the compute / attention phase issued last, on whichever stream
         live = n_mb
@@ -502,10 +496,9 @@ class DecoderStack:
             for m in range(n_mb):
                 if kinds[m] is None:
                     continue
+                s = streams[m]
                 kind = kinds[m]
-                s = exchange_stream[m] if kind == "exchange" else compute_stream[m]
                 with torch.gcu.stream(s):
-                    s.wait_event(last[m])
                     if kind != "exchange" and chain is not None:
                         s.wait_event(chain)
                     try:
@@ -513,11 +506,10 @@ class DecoderStack:
                     except StopIteration:
                         kinds[m] = None
                         live -= 1
-                    last[m] = s.record_event()
                     if kind != "exchange":
-                        chain = last[m]
-        for m in range(n_mb):
-            main.wait_event(last[m])
+                        chain = s.record_event()
+        for s in streams[1:]:
+            main.wait_event(s.record_event())
         return result[0] if n_mb == 1 else torch.cat(result, 0)
 
     def decode_exchange(self, x, caches, pos, group):
