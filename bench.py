@@ -720,6 +720,67 @@ def run_micro(name):
                       "rate": round(list(work.values())[0] / ms / 1e9, 1)}))
 
 
+def run_micro_interference():
+    """How much a tensor-core GEMM (and the attention kernel) slow down when another stream keeps a second
+    kernel running beside them, on ONE GPU: the fused exchange kernel on local buffers (the eight "ranks" are
+    eight buffers), a device-to-device memcpy loop, and a streaming kernel."""
+    import b200ops as ops
+    import ctypes
+    dev, bf = torch.device("cuda", 0), torch.bfloat16
+    M, F, K = 8192, 3584, 4096
+    a = torch.randn(M, K, device=dev).to(bf)
+    w = (torch.randn(2 * F, K, device=dev) * 0.02).to(bf)
+    out = torch.empty(M, F, dtype=bf, device=dev)
+    gemm = ops.bind("mm_swiglu", out, a, w)
+    B, Hq, Hkv, S, D = 4, 4, 1, 2048, 128
+    q, k, v = (torch.randn(B, h, S, D, device=dev).to(bf) for h in (Hq, Hkv, Hkv))
+    ao = torch.empty(B, S, Hq, D, dtype=bf, device=dev).transpose(1, 2)
+    attn = ops.bind("sdpa_flash_fwd", ao, None, q, k, v, ctypes.c_int32(1), ctypes.c_double(D ** -0.5))
+    world, rows_all, hid = 8, 8192, 4096
+    parts = [torch.randn(rows_all, hid, device=dev).to(bf) for _ in range(world)]
+    gath = [torch.empty(rows_all, hid, dtype=bf, device=dev) for _ in range(world)]
+    xl = torch.randn(rows_all // world, hid, device=dev).to(bf)
+    w_ = torch.ones(hid, device=dev).to(bf)
+    tp, tg = ops.tp_peers(parts, 3), ops.tp_peers(gath, 3)
+    exchange = ops.bind("tp_reduce_norm", ctypes.byref(tp), ctypes.byref(tg), xl, xl, w_, ctypes.c_int64(3 * 1024),
+                        ctypes.c_int64(rows_all), ctypes.c_double(1e-6), ctypes.c_int32(1), ctypes.c_int32(1), keep=(tp, tg, parts, gath))
+    src = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    dst = torch.empty_like(src)
+
+    def memcpy(stream):
+        with torch.cuda.stream(stream):
+            dst.copy_(src, non_blocking=True)
+    x32 = torch.randn(4096, 4096, device=dev)
+    y32 = torch.empty_like(x32)
+    add = ops.bind("add", y32, x32, x32, ctypes.c_double(1.0))
+    rows = []
+    for high in (False, True):
+        s1, s2 = torch.cuda.Stream(priority=-1 if high else 0), torch.cuda.Stream()
+
+        def timed(fn, n, stream, other=None, other_n=0):
+            torch.cuda.synchronize()
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for _ in range(other_n):
+                other(s2)
+            st.record(stream)
+            for _ in range(n):
+                fn(stream)
+            en.record(stream)
+            torch.cuda.synchronize()
+            return st.elapsed_time(en) / n * 1e3
+        for name, fn, n in (("gemm_swiglu 8192x(2x3584)x4096", gemm, 20), ("attention (4, 4q/1kv, 2048, 128)", attn, 40)):
+            for _ in range(3):
+                fn(s1)
+            alone = timed(fn, n, s1)
+            for oname, other in (("exchange kernel on local buffers", exchange), ("memcpy 64 MB device to device", memcpy),
+                                 ("add kernel 3 x 67 MB", add)):
+                o_alone = timed(other, 20, s2)
+                both = timed(fn, n, s1, other, int(alone * n / o_alone * 1.5) + 10)
+                rows.append({"kernel": name, "high_priority_stream": high, "alone_us": round(alone, 1), "beside": oname,
+                             "beside_alone_us": round(o_alone, 1), "with_it_us": round(both, 1), "factor": round(both / alone, 2)})
+    print(json.dumps({"micro": "interference", "rows": rows}))
+
+
 def run_micro_tp(rows):
     """The tensor-parallel exchange kernels alone, on as many ranks as torchrun started: device time of the
     signal / wait pair, of the fused kernel pulling only, pushing only, and doing both, with the bytes each rank
@@ -840,7 +901,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
     ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
                          "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
-                         "tp_exchange (under torchrun): the exchange kernels alone")
+                         "tp_exchange (under torchrun): the exchange kernels alone; interference: a GEMM beside a second kernel on one GPU")
     ap.add_argument("--timeline", action="store_true", help="under torchrun: per-phase device times of an eager tensor-parallel prefill pass")
     ap.add_argument("--rows", type=int, default=8192, help="--micro tp_exchange: rows of the activation (all ranks together)")
     args = ap.parse_args()
@@ -848,6 +909,8 @@ def main():
         run_timeline(args)
     elif args.micro == "tp_exchange":
         run_micro_tp(args.rows)
+    elif args.micro == "interference":
+        run_micro_interference()
     elif args.micro:
         run_micro(args.micro)
     elif args.impl == "reference":
