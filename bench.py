@@ -70,21 +70,47 @@ def layer_flops(tokens_b, seq, tp=1):
     return gemm + attn
 
 
+_CPU_LAYER_WEIGHTS = {}   # layer -> bf16 weights of the unsharded layer, kept between the prefill and the decode check
+
+
+def cpu_layer_weights(i):
+    import workloads
+    if i not in _CPU_LAYER_WEIGHTS:
+        _CPU_LAYER_WEIGHTS[i] = workloads.decoder_layer_weights(seed=i, dtype=torch.bfloat16, **CFG)
+    return _CPU_LAYER_WEIGHTS[i]
+
+
+def decode_parity(y, x_host, kc_local, vc_local, world, pos, seqs=(0, 63)):
+    """The timed decode step's output for two sequences against the unsharded 8-layer stack computed by
+    PyTorch CPU ATen in fp32 on the same bf16 weights, input and caches. Every rank drew its local KV heads from
+    the same seed, so the full cache is the local one repeated over the ranks."""
+    from tp_decoder import reference_decode_cpu
+    t0 = time.perf_counter()
+    seqs = list(seqs)
+    kc = kc_local[seqs].repeat(1, world, 1, 1)
+    vc = vc_local[seqs].repeat(1, world, 1, 1)
+    h = x_host[seqs].float()
+    for i in range(N_LAYERS):
+        h, _, _ = reference_decode_cpu(h, kc, vc, pos, cpu_layer_weights(i), **CFG)
+    got = y[seqs].float()
+    rel = ((got - h).norm() / h.norm()).item()
+    return {"rel": round(rel, 5), "tol": 3e-2, "ok": bool(torch.isfinite(got).all()) and rel < 3e-2,
+            "checked": "sequences %s of the timed decode step (batch 64, 4096-token cache) vs the unsharded fp32 CPU ATen stack" % seqs,
+            "cpu_s": round(time.perf_counter() - t0, 1)}
+
+
 def prefill_parity(y_b0, x_b0):
     """Batch element 0 of the stack's prefill output (any tensor-parallel degree) against the
     unsharded 8-layer stack computed by PyTorch CPU ATen in fp32 on the same bf16 weights and
     input. The device path rounds to bf16 between its launches and, with more than one rank,
     sums the row-parallel partial products in another order, so the bound is a bf16 one:
     relative error of the whole output in the 2-norm below 3e-2."""
-    import workloads
     from tp_decoder import reference_layer_cpu
     torch.set_num_threads(os.cpu_count() or 1)
     t0 = time.perf_counter()
     h = x_b0.float()
     for i in range(N_LAYERS):
-        w = workloads.decoder_layer_weights(seed=i, dtype=torch.bfloat16, **CFG)
-        h = reference_layer_cpu(h, w, **CFG)
-        del w
+        h = reference_layer_cpu(h, cpu_layer_weights(i), **CFG)
     y = y_b0.float()
     rel = ((y - h).norm() / h.norm()).item()
     finite = bool(torch.isfinite(y).all())
@@ -313,7 +339,8 @@ def run_gpu(args):
     caches = []
     for i in range(N_LAYERS):  # one N(0,1) draw, the same values in every layer's cache
         caches.append((kc.to(dev), vc.to(dev)))
-    xd = torch.randn(DECODE_B, 1, CFG["hidden"], generator=g).to(bf).to(dev)
+    xd_host = torch.randn(DECODE_B, 1, CFG["hidden"], generator=g).to(bf)
+    xd = xd_host.to(dev)
     pos = DECODE_T - 1
     for _ in range(warmup):
         stack.decode(xd, caches, pos, group)
@@ -324,11 +351,18 @@ def run_gpu(args):
     if os.environ.get("TP_DECODER_GRAPH", "1") != "0":
         graph = torch.gcu.GCUGraph()
         with torch.gcu.graph(graph):
-            stack.decode(xd, caches, pos, group)
+            yd = stack.decode(xd, caches, pos, group)
         for _ in range(warmup):
             graph.replay()
         decode_ms, decode_graph = timed(graph.replay, max(steps, 5)), True
+        yd_host = yd.cpu()
         graph.reset()
+    else:
+        yd_host = stack.decode(xd, caches, pos, group).cpu()
+    torch.gcu.synchronize()
+    dec_parity = None
+    if rank == 0 and not args.no_parity:   # the other ranks wait at the next collective
+        dec_parity = decode_parity(yd_host, xd_host, kc, vc, world, pos)
     del caches
 
     result = None
@@ -359,6 +393,7 @@ def run_gpu(args):
             "decode": {"tokens_per_s": round(DECODE_B / decode_ms * 1e3, 1), "ms_per_step": round(decode_ms, 4),
                        "graph_replay": decode_graph, "eager_ms_per_step": round(decode_eager_ms, 4),
                        "batch": DECODE_B, "kv_tokens": DECODE_T,
+                       "parity": dec_parity,
                        "hbm_gbs_per_gpu": round((weights_b + kv_b) / decode_ms / 1e6, 1),
                        "frac_of_measured_hbm": round((weights_b + kv_b) / decode_ms / 1e6 / hbm_peak, 3)},
         }
@@ -393,6 +428,8 @@ def run_gpu(args):
         dist.destroy_process_group()
     if int(device_error.item()) != 0:
         raise SystemExit("bench.py: the device error word is %d (bit 1: a bounded wait timed out)" % int(device_error.item()))
+    if rank == 0 and dec_parity is not None and not dec_parity["ok"]:
+        raise SystemExit("bench.py: the decode output does not match the CPU reference: %s" % json.dumps(dec_parity))
     if rank == 0 and parity is not None and not parity["ok"]:
         raise SystemExit("bench.py: the prefill output does not match the CPU reference: %s" % json.dumps(parity))
 
