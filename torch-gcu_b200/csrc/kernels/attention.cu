@@ -41,6 +41,7 @@ struct AttnParams {
   int B, Hq, Hkv, Sq, Sk, D;
   int causal, packed, is_bf16;
   int pair_heads;    // prefill kernel: the CTA's two Q tiles are two heads of one KV group (else two row tiles)
+  int items_x, items_y;   // prefill kernel: blocks of query rows, heads (or head pairs): the work items of its persistent CTAs
   float scale_log2;  // scale * log2(e)
   float scale;
   void* out;
@@ -391,31 +392,57 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   uint64_t* s_full = bars + 7;             // [tile]
   uint64_t* p_full = bars + 9;             // [tile]
   uint64_t* o_done = bars + 11;            // [tile]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* q_empty = bars + 13;           // every S = Q K^T of the item has been computed: the Q buffers may be refilled
+  uint64_t* o_free = bars + 14;            // [tile] the item's O has been read out of tensor memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
-  // The two Q tiles of a CTA: with an even group size, the same 128 query rows of two query heads that share
+  const int n_all = (p.Sk + BKV - 1) / BKV;
+  const int tile_rows = p.pair_heads ? 0 : BQ, tile_heads = p.pair_heads ? 1 : 0;   // step from tile 0 to tile 1
+  // Work items: (block of query rows, head or head pair, batch). The CTAs are persistent: CTA c takes items
+  // c, c + gridDim.x, ... of a list ordered by length, longest causal blocks first, so every CTA gets a mix of
+  // long and short items, and the barriers, the tensor memory and the pipeline are set up once per CTA, not once
+  // per item; the loads of the next item start while the output of the current one is still being written.
+  const int per_x = p.items_y * p.B;
+  const int n_items = p.items_x * per_x;
+  const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
+  // Round k hands item k * gridDim.x + c to CTA c on even rounds and to CTA gridDim.x - 1 - c on odd rounds: the
+  // lengths fall along the list, so the two directions cancel each other's slope. -1: no item in the last round.
+  auto item_of_round = [&](int k) {
+    const int pos = (k & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+    const int idx = k * static_cast<int>(gridDim.x) + pos;
+    return idx < n_items ? idx : -1;
+  };
+
+  // The two Q tiles of an item: with an even group size, the same 128 query rows of two query heads that share
   // the KV head (equal work and equal masks for both tiles, so the ping-pong never runs single-handed);
   // otherwise two consecutive row tiles of one head.
-  const int first = gridDim.x - 1 - blockIdx.x;  // longest (last) causal tiles first
-  const int b = blockIdx.z;
-  const int q0 = p.pair_heads ? first * BQ : first * 2 * BQ;
-  const int hq = p.pair_heads ? blockIdx.y * 2 : blockIdx.y;
-  const int hkv = hq / G;
-  const int tile_rows = p.pair_heads ? 0 : BQ, tile_heads = p.pair_heads ? 1 : 0;   // step from tile 0 to tile 1
-  const int n_all = (p.Sk + BKV - 1) / BKV;
-  int n_t[2];
+  struct Item {
+    int b, q0, hq, hkv, n_t[2], n_max;
+  };
+  auto item_at = [&](int idx) {
+    Item it;
+    const int xr = idx / per_x, rest = idx - xr * per_x;
+    const int first = p.items_x - 1 - xr;   // longest (last) causal blocks first
+    const int y = rest % p.items_y;
+    it.b = rest / p.items_y;
+    it.q0 = p.pair_heads ? first * BQ : first * 2 * BQ;
+    it.hq = p.pair_heads ? y * 2 : y;
+    it.hkv = it.hq / G;
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int q0t = q0 + t * tile_rows;
-    n_t[t] = q0t >= p.Sq ? 0 : (p.causal ? min(n_all, q0t / BKV + 1) : n_all);
-  }
-  const int n_max = max(n_t[0], n_t[1]);
+    for (int t = 0; t < 2; ++t) {
+      const int q0t = it.q0 + t * tile_rows;
+      it.n_t[t] = q0t >= p.Sq ? 0 : (p.causal ? min(n_all, q0t / BKV + 1) : n_all);
+    }
+    it.n_max = max(it.n_t[0], it.n_t[1]);
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
@@ -423,6 +450,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
       mbar_init(&o_done[i], 1);
+      mbar_init(&o_free[i], 4);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -442,23 +470,37 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       prefetch_tmap(&tmap_q);
       prefetch_tmap(&tmap_k);
       prefetch_tmap(&tmap_v);
-      const int n_q = n_t[1] > 0 ? 2 : 1;
-      mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(n_q * Cfg::kQBytes));
-      for (int t = 0; t < n_q; ++t)
+      uint32_t kv_it = 0;   // K / V tiles loaded so far (ring position and phase)
+      uint32_t q_it = 0;    // items started so far
+      bool ok = true;
+      for (int round = 0; round < n_rounds && ok; ++round, ++q_it) {
+        const int idx = item_of_round(round);
+        if (idx < 0) break;
+        const Item it = item_at(idx);
+        for (int j = 0; j < it.n_max && ok; ++j, ++kv_it) {
+          const int st = kv_it & 1;
+          if (!mbar_wait(&kv_empty[st], ((kv_it >> 1) & 1u) ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
+          uint8_t* sV = sK + Cfg::kKVBytes;
+          mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
 #pragma unroll
-        for (int h = 0; h < Cfg::kHalves; ++h)
-          tma_load_4d(sQ + t * Cfg::kQBytes + h * (BQ * 128), &tmap_q, q_full, h * 64, q0 + t * tile_rows, hq + t * tile_heads, b);
-      for (int j = 0; j < n_max; ++j) {
-        const int st = j & 1;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1u) ^ 1u, abort_flag)) break;
-        uint8_t* sK = sKV + st * 2 * Cfg::kKVBytes;
-        uint8_t* sV = sK + Cfg::kKVBytes;
-        mbar_arrive_expect_tx(&k_full[st], Cfg::kKVBytes);
+          for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, j * BKV, it.hkv, it.b);
+          mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
 #pragma unroll
-        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sK + h * (BKV * 128), &tmap_k, &k_full[st], h * 64, j * BKV, hkv, b);
-        mbar_arrive_expect_tx(&v_full[st], Cfg::kKVBytes);
+          for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, j * BKV, it.hkv, it.b);
+          if (j == 0) {
+            // Q after the item's first K / V tile: that tile's buffer frees while the previous item is still
+            // computing, the Q buffers only when its last S has been computed
+            if (q_it > 0 && !mbar_wait(q_empty, (q_it - 1) & 1u, abort_flag)) { ok = false; break; }
+            const int n_q = it.n_t[1] > 0 ? 2 : 1;
+            mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(n_q * Cfg::kQBytes));
+            for (int t = 0; t < n_q; ++t)
 #pragma unroll
-        for (int h = 0; h < Cfg::kHalves; ++h) tma_load_4d(sV + h * (BKV * 128), &tmap_v, &v_full[st], h * 64, j * BKV, hkv, b);
+              for (int h = 0; h < Cfg::kHalves; ++h)
+                tma_load_4d(sQ + t * Cfg::kQBytes + h * (BQ * 128), &tmap_q, q_full, h * 64, it.q0 + t * tile_rows,
+                            it.hq + t * tile_heads, it.b);
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -466,57 +508,74 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(BQ, BKV, BF16, false, false);  // Q, K both K-major
       const uint32_t idesc_o = make_idesc(BQ, D, BF16, false, true);     // P from tensor memory, V MN-major
-      auto issue_s = [&](int t, int j) {
-        const uint32_t q_addr = smem_u32(sQ + t * Cfg::kQBytes);
-        const uint32_t k_addr = smem_u32(sKV + (j & 1) * 2 * Cfg::kKVBytes);
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
+      uint32_t kv_base = 0;            // K / V tiles consumed before this item
+      uint32_t q_it = 0;
+      uint32_t p_cnt[2] = {0, 0};      // softmax results consumed so far, per tile
+      uint32_t o_cnt[2] = {0, 0};      // items with work so far, per tile
+      bool ok = true;
+      for (int round = 0; round < n_rounds && ok; ++round, ++q_it) {
+        const int idx = item_of_round(round);
+        if (idx < 0) break;
+        const Item it = item_at(idx);
+        auto issue_s = [&](int t, int j) {
+          const uint32_t q_addr = smem_u32(sQ + t * Cfg::kQBytes);
+          const uint32_t k_addr = smem_u32(sKV + ((kv_base + j) & 1u) * 2 * Cfg::kKVBytes);
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * (BQ * 128) + (kk % 4) * 32;
-          umma_f16(d_tmem, smem_desc_sw128(q_addr + off, 16u, 1024u), smem_desc_sw128(k_addr + off, 16u, 1024u),
-                   idesc_s, kk != 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[t]);
-      };
-      bool ok = n_max > 0 && mbar_wait(q_full, 0, abort_flag) && mbar_wait(&k_full[0], 0, abort_flag);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0, 0);
-        if (n_t[1] > 0) issue_s(1, 0);
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const int st = j & 1;
-        bool v_ready = false, k_ready = false;
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_t[t]) continue;
-          if (!mbar_wait(&p_full[t], j & 1u, abort_flag)) { ok = false; break; }
-          if (!v_ready) {
-            if (!mbar_wait(&v_full[st], (j >> 1) & 1u, abort_flag)) { ok = false; break; }
-            v_ready = true;
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk / 4) * (BQ * 128) + (kk % 4) * 32;
+            umma_f16(d_tmem, smem_desc_sw128(q_addr + off, 16u, 1024u), smem_desc_sw128(k_addr + off, 16u, 1024u),
+                     idesc_s, kk != 0 ? 1u : 0u);
           }
+          umma_commit(&s_full[t]);
+        };
+        auto k_phase = [&](int j) { return ((kv_base + j) >> 1) & 1u; };
+        ok = mbar_wait(q_full, q_it & 1u, abort_flag) && mbar_wait(&k_full[kv_base & 1u], k_phase(0), abort_flag);
+        if (ok) {
           tc_fence_after();
-          const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
-          const uint32_t o_tmem = tmem_base + static_cast<uint32_t>(Cfg::kOCol + t * BKV);
-          const uint32_t p_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
-#pragma unroll
-          for (int kk = 0; kk < BKV / 16; ++kk) {
-            // A = P_t: 16 keys = 8 packed columns per step. B = V: 64-column slabs BKV*128 bytes
-            // apart (LBO), 8-key groups 1024 bytes apart (SBO), 16 keys = 2048 bytes per step.
-            const uint64_t db = smem_desc_sw128(v_addr + kk * 2048, BKV * 128, 1024u);
-            umma_f16_ts(o_tmem, p_tmem + kk * 8, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
-          }
-          if (j + 1 < n_t[t]) {
-            if (!k_ready) {
-              if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
-              k_ready = true;
-              tc_fence_after();
-            }
-            issue_s(t, j + 1);   // executes after the P.V above, which has then consumed P_t
-          } else {
-            umma_commit(&o_done[t]);
-          }
+          issue_s(0, 0);
+          if (it.n_t[1] > 0) issue_s(1, 0);
         }
-        if (ok) umma_commit(&kv_empty[st]);
+        for (int j = 0; j < it.n_max && ok; ++j) {
+          const int st = (kv_base + j) & 1;
+          bool v_ready = false, k_ready = false;
+          for (int t = 0; t < 2 && ok; ++t) {
+            if (j >= it.n_t[t]) continue;
+            if (!mbar_wait(&p_full[t], p_cnt[t] & 1u, abort_flag)) { ok = false; break; }
+            ++p_cnt[t];
+            if (!v_ready) {
+              if (!mbar_wait(&v_full[st], k_phase(j), abort_flag)) { ok = false; break; }
+              v_ready = true;
+            }
+            // the first P.V of an item overwrites O: the previous item's O must have been read out
+            if (j == 0 && o_cnt[t] > 0 && !mbar_wait(&o_free[t], (o_cnt[t] - 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(sKV + st * 2 * Cfg::kKVBytes + Cfg::kKVBytes);
+            const uint32_t o_tmem = tmem_base + static_cast<uint32_t>(Cfg::kOCol + t * BKV);
+            const uint32_t p_tmem = tmem_base + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
+#pragma unroll
+            for (int kk = 0; kk < BKV / 16; ++kk) {
+              // A = P_t: 16 keys = 8 packed columns per step. B = V: 64-column slabs BKV*128 bytes
+              // apart (LBO), 8-key groups 1024 bytes apart (SBO), 16 keys = 2048 bytes per step.
+              const uint64_t db = smem_desc_sw128(v_addr + kk * 2048, BKV * 128, 1024u);
+              umma_f16_ts(o_tmem, p_tmem + kk * 8, db, idesc_o, (j | kk) != 0 ? 1u : 0u);
+            }
+            if (j + 1 < it.n_t[t]) {
+              if (!k_ready) {
+                if (!mbar_wait(&k_full[(kv_base + j + 1) & 1u], k_phase(j + 1), abort_flag)) { ok = false; break; }
+                k_ready = true;
+                tc_fence_after();
+              }
+              issue_s(t, j + 1);   // executes after the P.V above, which has then consumed P_t
+            } else {
+              umma_commit(&o_done[t]);
+              ++o_cnt[t];
+            }
+          }
+          if (ok) umma_commit(&kv_empty[st]);
+        }
+        if (ok) umma_commit(q_empty);   // arrives when every MMA of the item, its last S included, has completed
+        kv_base += static_cast<uint32_t>(it.n_max);
       }
     }
   } else if (warp >= 4) {
@@ -525,114 +584,131 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     const int quarter = warp & 3;                  // tensor-memory lanes this warp may touch
     const int r = quarter * 32 + lane;             // row of the tile this thread owns
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
-    const int q0t = q0 + t * tile_rows;
-    const int head = hq + t * tile_heads;
-    const int qi = q0t + r;
-    const bool row_valid = qi < p.Sq;
-    const int n_kv = n_t[t];
     const uint32_t s_tmem = tmem_base + lane_sel + static_cast<uint32_t>(Cfg::kSCol + t * BKV);
     const uint32_t o_tmem = tmem_base + lane_sel + static_cast<uint32_t>(Cfg::kOCol + t * BKV);
     const float sl2 = p.scale_log2;
-    float m = -CUDART_INF_F;   // maximum the exponentials are taken against (raw score units)
-    float l = 0.f;
+    uint32_t s_cnt = 0;    // S tiles of this tile consumed so far
+    uint32_t o_cnt = 0;    // items with work for this tile so far
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int k0 = j * BKV;
-      if (!mbar_wait(&s_full[t], j & 1u, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t s[BKV];
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int idx = item_of_round(round);
+      if (idx < 0) break;
+      const Item it = item_at(idx);
+      const int b = it.b;
+      const int q0t = it.q0 + t * tile_rows;
+      const int head = it.hq + t * tile_heads;
+      const int qi = q0t + r;
+      const bool row_valid = qi < p.Sq;
+      const int n_kv = it.n_t[t];
+      float m = -CUDART_INF_F;   // maximum the exponentials are taken against (raw score units)
+      float l = 0.f;
+      for (int j = 0; j < n_kv && ok; ++j, ++s_cnt) {
+        const int k0 = j * BKV;
+        if (!mbar_wait(&s_full[t], s_cnt & 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t s[BKV];
 #pragma unroll
-      for (int c = 0; c < BKV; c += 32) tmem_ld_32x32_at(s_tmem + c, &s[c]);
-      tmem_wait_ld();
-      const bool need_mask = (p.causal && k0 + BKV - 1 > q0t) || (k0 + BKV > p.Sk);
-      if (need_mask) {
-        const int vis = (p.causal ? min(p.Sk, qi + 1) : p.Sk) - k0;  // columns [0, vis) are visible
+        for (int c = 0; c < BKV; c += 32) tmem_ld_32x32_at(s_tmem + c, &s[c]);
+        tmem_wait_ld();
+        const bool need_mask = (p.causal && k0 + BKV - 1 > q0t) || (k0 + BKV > p.Sk);
+        if (need_mask) {
+          const int vis = (p.causal ? min(p.Sk, qi + 1) : p.Sk) - k0;  // columns [0, vis) are visible
 #pragma unroll
-        for (int i = 0; i < BKV; ++i)
-          if (i >= vis) s[i] = 0xff800000u;  // -inf
-      }
-      float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+          for (int i = 0; i < BKV; ++i)
+            if (i >= vis) s[i] = 0xff800000u;  // -inf
+        }
+        float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
 #pragma unroll
-      for (int i = 0; i < BKV; i += 8) {
-        mx0 = fmaxf(mx0, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
-        mx1 = fmaxf(mx1, fmaxf(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])));
-        mx2 = fmaxf(mx2, fmaxf(__uint_as_float(s[i + 4]), __uint_as_float(s[i + 5])));
-        mx3 = fmaxf(mx3, fmaxf(__uint_as_float(s[i + 6]), __uint_as_float(s[i + 7])));
+        for (int i = 0; i < BKV; i += 8) {
+          mx0 = fmaxf(mx0, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+          mx1 = fmaxf(mx1, fmaxf(__uint_as_float(s[i + 2]), __uint_as_float(s[i + 3])));
+          mx2 = fmaxf(mx2, fmaxf(__uint_as_float(s[i + 4]), __uint_as_float(s[i + 5])));
+          mx3 = fmaxf(mx3, fmaxf(__uint_as_float(s[i + 6]), __uint_as_float(s[i + 7])));
+        }
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // advance the maximum only when it grew by more than the threshold
+        const bool grow = (mx - m) * sl2 > kRescaleThreshold;   // true on the first tile (m = -inf)
+        float alpha = 1.f;
+        if (grow) {
+          alpha = ex2_approx((m - mx) * sl2);                    // m = -inf -> 0
+          m = mx;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // the P.V of the previous tile finished before this S was written, so O is stable
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_tmem + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_tmem + c, o);
+          }
+        }
+        const float mb = (m == -CUDART_INF_F ? 0.f : m) * sl2;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < BKV; i += 4) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
+          const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
+          const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
+          sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+          s[i / 2] = pack_pair<BF16>(p0, p1);
+          s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
+        }
+        l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
+        tmem_st_32x32(s_tmem, &s[0]);
+        tmem_st_32x32(s_tmem + 32, &s[32]);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
       }
-      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // advance the maximum only when it grew by more than the threshold
-      const bool grow = (mx - m) * sl2 > kRescaleThreshold;   // true on the first tile (m = -inf)
-      float alpha = 1.f;
-      if (grow) {
-        alpha = ex2_approx((m - mx) * sl2);                    // m = -inf -> 0
-        m = mx;
+      // epilogue: O / l
+      if (ok && n_kv > 0) {
+        ok = mbar_wait(&o_done[t], o_cnt & 1u, abort_flag);
+        ++o_cnt;
       }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // the P.V of the previous tile finished before this S was written, so O is stable
+      if (ok && n_kv > 0) {
+        tc_fence_after();
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(head) * p.o_sh +
+                         static_cast<int64_t>(qi) * p.o_ss;
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
-          uint32_t o[32];
-          tmem_ld_32x32(o_tmem + c, o);
+          uint32_t v[32];
+          tmem_ld_32x32(o_tmem + c, v);
           tmem_wait_ld();
+          if (c + 32 >= D) {
+            // O is in registers: the next item's first P.V may overwrite the accumulator
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&o_free[t]);
+          }
+          if (row_valid) {
+            uint32_t o[16];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32(o_tmem + c, o);
-        }
-      }
-      const float mb = (m == -CUDART_INF_F ? 0.f : m) * sl2;
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            for (int i = 0; i < 16; ++i)
+              o[i] = pack_pair<BF16>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+            if (vec_ok) {
 #pragma unroll
-      for (int i = 0; i < BKV; i += 4) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sl2, -mb));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sl2, -mb));
-        const float p2 = ex2_approx(fmaf(__uint_as_float(s[i + 2]), sl2, -mb));
-        const float p3 = ex2_approx(fmaf(__uint_as_float(s[i + 3]), sl2, -mb));
-        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-        s[i / 2] = pack_pair<BF16>(p0, p1);
-        s[i / 2 + 1] = pack_pair<BF16>(p2, p3);
-      }
-      l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
-      tmem_st_32x32(s_tmem, &s[0]);
-      tmem_st_32x32(s_tmem + 32, &s[32]);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
-    }
-    // epilogue: O / l
-    if (ok && n_kv > 0) ok = mbar_wait(&o_done[t], 0, abort_flag);
-    if (ok && n_kv > 0) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.0f / l : 0.f;
-      uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(head) * p.o_sh +
-                       static_cast<int64_t>(qi) * p.o_ss;
-      const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
-#pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(o_tmem + c, v);
-        tmem_wait_ld();
-        if (row_valid) {
-          uint32_t o[16];
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(orow + c + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
+            } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            o[i] = pack_pair<BF16>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
-          if (vec_ok) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              *reinterpret_cast<uint4*>(orow + c + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              orow[c + 2 * i] = static_cast<uint16_t>(o[i] & 0xffffu);
-              orow[c + 2 * i + 1] = static_cast<uint16_t>(o[i] >> 16);
+              for (int i = 0; i < 16; ++i) {
+                orow[c + 2 * i] = static_cast<uint16_t>(o[i] & 0xffffu);
+                orow[c + 2 * i + 1] = static_cast<uint16_t>(o[i] >> 16);
+              }
             }
           }
         }
-      }
-      if (row_valid && p.lse) {
-        const float lse = l > 0.f ? m * p.scale + logf(l) : -CUDART_INF_F;
-        p.lse[(static_cast<int64_t>(b) * p.Hq + head) * p.Sq + qi] = lse;
+        if (row_valid && p.lse) {
+          const float lse = l > 0.f ? m * p.scale + logf(l) : -CUDART_INF_F;
+          p.lse[(static_cast<int64_t>(b) * p.Hq + head) * p.Sq + qi] = lse;
+        }
       }
     }
   }
@@ -995,7 +1071,12 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
     attention_fwd_kernel<D><<<dim3(1, p.Hkv, p.B), kAttThreads, Cfg::kSmem, s>>>(tq, tk, tv, p);
   } else {
     p.pair_heads = (p.Hq / p.Hkv) % 2 == 0 ? 1 : 0;
-    const dim3 grid = p.pair_heads ? dim3((p.Sq + BQ - 1) / BQ, p.Hq / 2, p.B) : dim3((p.Sq + 2 * BQ - 1) / (2 * BQ), p.Hq, p.B);
+    p.items_x = p.pair_heads ? (p.Sq + BQ - 1) / BQ : (p.Sq + 2 * BQ - 1) / (2 * BQ);
+    p.items_y = p.pair_heads ? p.Hq / 2 : p.Hq;
+    const int64_t items = static_cast<int64_t>(p.items_x) * p.items_y * p.B;
+    B200_REQUIRE(items < (int64_t(1) << 31), B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: too many query tiles");
+    const int sms = sm_count_current_device();
+    const int grid = static_cast<int>(items < sms ? items : sms);   // persistent CTAs, one per SM
     if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
     else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
   }
