@@ -363,7 +363,8 @@ template <int D> struct PrefillCfg {
   static constexpr int kHalves = D / 64;
   static constexpr int kQBytes = BQ * D * 2;     // one Q tile
   static constexpr int kKVBytes = BKV * D * 2;
-  static constexpr int kSmem = 2 * kQBytes + kKVStages * 2 * kKVBytes + 1024 + 256;
+  static constexpr int kOutBytes = 8 * 4096;   // per softmax warp: 32 rows x 64 columns staged for the output store
+  static constexpr int kSmem = 2 * kQBytes + kKVStages * 2 * kKVBytes + kOutBytes + 1024 + 256;
   static constexpr int kSCol = 0;                // S_t at columns t*128 (P_t over its first 64)
   static constexpr int kOCol = 256;              // O_t at columns 256 + t*128
   static constexpr int kTmemCols = 512;
@@ -378,13 +379,15 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack_pair(float lo, flo
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
+                         const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                         const AttnParams p) {
   using Cfg = PrefillCfg<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                    // [tile]
   uint8_t* sKV = sQ + 2 * Cfg::kQBytes;                  // [stage][K | V]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + kKVStages * 2 * Cfg::kKVBytes);
+  uint8_t* sO = sKV + kKVStages * 2 * Cfg::kKVBytes;     // [softmax warp] 32 rows x 128 bytes, 128-byte swizzle
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sO + Cfg::kOutBytes);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;             // [stage]
   uint64_t* v_full = bars + 3;             // [stage]
@@ -673,9 +676,12 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       if (ok && n_kv > 0) {
         tc_fence_after();
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        uint16_t* orow = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(head) * p.o_sh +
-                         static_cast<int64_t>(qi) * p.o_ss;
-        const bool vec_ok = (reinterpret_cast<uintptr_t>(orow) & 15) == 0;
+        // The warp's 32 rows go out through shared memory, 64 columns at a time, as one tensor store each (rows past
+        // the end of the sequence are clipped by the store): a thread holds a whole row, so direct stores would
+        // touch 32 different lines per instruction.
+        const uint32_t stage = smem_u32(sO + (warp - 4) * 4096);
+        const uint32_t stage_row = stage + static_cast<uint32_t>(lane) * 128u;
+        const int row_first = q0t + quarter * 32;
 #pragma unroll 1
         for (int c = 0; c < D; c += 32) {
           uint32_t v[32];
@@ -687,21 +693,26 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&o_free[t]);
           }
-          if (row_valid) {
-            uint32_t o[16];
+          uint32_t o[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              o[i] = pack_pair<BF16>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
-            if (vec_ok) {
+          for (int i = 0; i < 16; ++i)
+            o[i] = pack_pair<BF16>(__uint_as_float(v[2 * i]) * inv, __uint_as_float(v[2 * i + 1]) * inv);
+          if ((c & 63) == 0) {
+            if (lane == 0) bulk_wait_read_all();   // the store that last read this buffer has finished reading it
+            __syncwarp();
+          }
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(orow + c + q * 8) = make_uint4(o[q * 4], o[q * 4 + 1], o[q * 4 + 2], o[q * 4 + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                orow[c + 2 * i] = static_cast<uint16_t>(o[i] & 0xffffu);
-                orow[c + 2 * i + 1] = static_cast<uint16_t>(o[i] >> 16);
-              }
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t chunk = static_cast<uint32_t>((c & 63) / 8 + q);
+            st_shared_v4(stage_row + ((chunk ^ static_cast<uint32_t>(lane & 7)) << 4), o[q * 4], o[q * 4 + 1], o[q * 4 + 2],
+                         o[q * 4 + 3]);
+          }
+          if ((c & 63) == 32) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0 && row_first < p.Sq) {
+              tma_store_4d(&tmap_o, stage, c & ~63, row_first, head, b);
+              bulk_commit();
             }
           }
         }
@@ -711,6 +722,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
         }
       }
     }
+    if (lane == 0) bulk_wait_all();   // the output stores have left shared memory and are complete
   }
 
   tc_fence_before();
@@ -1047,7 +1059,8 @@ bool make_qkv_map(CUtensorMap* m, const b200Tensor* t, uint32_t box_rows, uint32
 }
 
 template <int D>
-b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200Tensor* v, AttnParams p, cudaStream_t s) {
+b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200Tensor* v, const b200Tensor* out, AttnParams p,
+                           cudaStream_t s) {
   using Cfg = AttCfg<D>;
   CUtensorMap tq, tk, tv;
   const char* err = "";
@@ -1077,8 +1090,10 @@ b200Status launch_attention(const b200Tensor* q, const b200Tensor* k, const b200
     B200_REQUIRE(items < (int64_t(1) << 31), B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: too many query tiles");
     const int sms = sm_count_current_device();
     const int grid = static_cast<int>(items < sms ? items : sms);   // persistent CTAs, one per SM
-    if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
-    else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, p);
+    CUtensorMap to;   // output: 64 columns x the 32 rows of one softmax warp per store
+    B200_REQUIRE(make_qkv_map(&to, out, 32, 1, &err), B200_NOT_SUPPORTED, "b200_sdpa_flash_fwd: output: %s", err);
+    if (p.is_bf16) attention_prefill_kernel<D, true><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, to, p);
+    else attention_prefill_kernel<D, false><<<grid, kPrefillThreads, PrefillCfg<D>::kSmem, s>>>(tq, tk, tv, to, p);
   }
   return check_launch("b200_sdpa_flash_fwd");
 }
@@ -1173,6 +1188,6 @@ extern "C" b200Status b200_sdpa_flash_fwd(const b200Tensor* out, const b200Tenso
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (p.packed && p.D == 128 && G * p.Sq <= 16)
     return p.is_bf16 ? launch_decode<true>(q, k, v, p, s) : launch_decode<false>(q, k, v, p, s);
-  if (p.D == 128) return launch_attention<128>(q, k, v, p, s);
-  return launch_attention<64>(q, k, v, p, s);
+  if (p.D == 128) return launch_attention<128>(q, k, v, out, p, s);
+  return launch_attention<64>(q, k, v, out, p, s);
 }
