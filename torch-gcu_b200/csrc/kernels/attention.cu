@@ -1114,11 +1114,15 @@ b200Status launch_decode(const b200Tensor* q, const b200Tensor* k, const b200Ten
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "b200_sdpa_flash_fwd: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
-  // split the keys over a cluster until the grid covers the SMs a few times over
+  // Split the keys of one (batch, KV head) over a cluster only while the split grid still fits the device at once
+  // (two CTAs per SM): a split costs the cluster's co-scheduling and the merge, and more CTAs than places gain
+  // nothing. Measured at batch 64 x 8 KV heads x 4096 keys: 168 us unsplit, 190 us in two, 215 us in four; at
+  // 64 x 1 x 4096: 62 / 40 / 30 / 41 us for 1 / 2 / 4 / 8.
   const int n_tiles = (p.Sk + BKV - 1) / BKV;
   const int ctas = p.B * p.Hkv;
+  const int places = 2 * sm_count_current_device();
   int splits = 1;
-  while (splits < 8 && ctas * splits < 4 * 148 && n_tiles >= splits * 2 * 8) splits *= 2;   // >= 8 tiles per CTA
+  while (splits < 8 && ctas * splits * 2 <= places && n_tiles >= splits * 2 * 8) splits *= 2;   // >= 8 tiles per CTA
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, p.Hkv, p.B);
   cfg.blockDim = dim3(kDecThreads);

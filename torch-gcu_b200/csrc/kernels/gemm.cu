@@ -726,7 +726,7 @@ b200Status launch_tc2(const Operand& oa, const Operand& ob, GemmParams p, cudaSt
 constexpr int BNS = 128;
 constexpr int kStageS = BM * BK * 2 + BNS * BK * 2;   // 32 KB
 constexpr int kStagesS = 3;                           // 96 KB: two CTAs per SM
-constexpr int kPartialStride = BNS + 1;               // padded: conflict-free rows and columns
+constexpr int kPartialStride = BNS + 4;               // padded: 16-byte accesses along rows and along columns without bank conflicts
 constexpr int kSmemS = kStagesS * kStageS + 1024 + 256;
 static_assert(BM * kPartialStride * 4 <= kStagesS * kStageS, "the partial tile reuses the drained stage ring");
 
@@ -823,48 +823,78 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
       if (ok) umma_commit(acc_full);
     }
   } else {
-    // this CTA's partial tile: tensor memory -> shared memory (zeros when the slice of K is empty)
+    // this CTA's partial tile: tensor memory -> shared memory (zeros when the slice of K is empty); rows past the
+    // end of the product are never read
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    const int valid = min(BM, p.M - tm * BM);
     bool ok = true;
     if (n_my > 0) ok = mbar_wait(acc_full, 0, abort_flag);
     tc_fence_after();
+    if (quarter * 32 < valid) {
 #pragma unroll 1
-    for (int c = 0; c < BNS; c += 32) {
-      uint32_t r[32];
-      if (n_my > 0 && ok) {
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c), r);
-        tmem_wait_ld();
-      } else {
+      for (int c = 0; c < BNS; c += 32) {
+        uint32_t r[32];
+        if (n_my > 0 && ok) {
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(c), r);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = 0u;
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<uint4*>(&partial[row * kPartialStride + c + j]) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
       }
-#pragma unroll
-      for (int j = 0; j < 32; ++j) partial[row * kPartialStride + c + j] = __uint_as_float(r[j]);
     }
   }
 
   tc_fence_before();
   cluster.sync();
   if (warp >= 2) {
-    // rows [rank * band, (rank + 1) * band) of the tile, summed over the partials in rank order
+    // The rows of the tile that exist are dealt out in bands, one per CTA of the cluster; a CTA sums its band over
+    // the partials in rank order, four columns per thread and step, every partial's load issued before the first add.
     const int tid = (warp - 2) * 32 + lane;
-    const int band = (BM + splits - 1) / splits;
-    const int band_rows = max(0, min(BM, (rank + 1) * band) - rank * band);
-    for (int e = tid; e < band_rows * BNS; e += 128) {
-      const int lr = rank * band + e / BNS, col = e % BNS;
+    const int valid = min(BM, p.M - tm * BM);
+    const int band = (valid + splits - 1) / splits;
+    const int r0 = min(valid, rank * band), r1 = min(valid, r0 + band);
+    const float* src[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) src[c] = cluster.map_shared_rank(partial, c < splits ? c : 0);
+    const bool is_bf16 = p.is_bf16 != 0;
+    for (int u = tid; u < (r1 - r0) * (BNS / 4); u += 128) {
+      const int lr = r0 + u / (BNS / 4), col = (u % (BNS / 4)) * 4;
       const int grow = tm * BM + lr, gcol = tn * BNS + col;
-      float acc = 0.f;
-      for (int c = 0; c < splits; ++c) acc += cluster.map_shared_rank(partial, c)[lr * kPartialStride + col];
-      if (grow < p.M && gcol < p.N) {
-        float v = p.alpha * acc;
-        if (p.cin) {
-          const uint16_t cb = static_cast<const uint16_t*>(p.cin)[b * p.c_sb + static_cast<int64_t>(grow) * p.c_sm +
-                                                                static_cast<int64_t>(gcol) * p.c_sn];
-          v += p.beta * (p.is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+      float4 v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < splits) v[c] = *reinterpret_cast<const float4*>(src[c] + lr * kPartialStride + col);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        if (c < splits) {
+          acc[0] += v[c].x; acc[1] += v[c].y; acc[2] += v[c].z; acc[3] += v[c].w;
         }
-        static_cast<uint16_t*>(p.out)[b * p.o_sb + static_cast<int64_t>(grow) * p.o_sm + gcol] =
-            p.is_bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+      if (gcol >= p.N) continue;
+      uint16_t bits[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float o = p.alpha * acc[j];
+        if (p.cin && gcol + j < p.N) {
+          const uint16_t cb = static_cast<const uint16_t*>(p.cin)[b * p.c_sb + static_cast<int64_t>(grow) * p.c_sm +
+                                                                static_cast<int64_t>(gcol + j) * p.c_sn];
+          o += p.beta * (is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+        }
+        bits[j] = is_bf16 ? f32_to_bf16_bits(o) : f32_to_f16_bits(o);
+      }
+      uint16_t* dst = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(grow) * p.o_sm + gcol;
+      if (gcol + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (static_cast<uint32_t>(bits[1]) << 16),
+                                                    bits[2] | (static_cast<uint32_t>(bits[3]) << 16));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (gcol + j < p.N) dst[j] = bits[j];
       }
     }
   }
