@@ -757,6 +757,33 @@ def run_micro(name):
                       "rate": round(list(work.values())[0] / ms / 1e9, 1)}))
 
 
+def run_micro_decode_step():
+    """Two layers of the decode step (batch 64, 4096-token cache, one GPU), run eagerly a few times: the case
+    for a per-kernel launch list of the decode path."""
+    import torch_gcu  # noqa: F401
+    from tp_decoder import DecoderStack
+    dev = torch.device("gcu", 0)
+    torch.gcu.set_device(0)
+    bf = torch.bfloat16
+    stack = DecoderStack(2, 1, 0, "gcu", dev, bf, CFG)
+    g = torch.Generator().manual_seed(5)
+    kc = torch.randn(DECODE_B, CFG["kv_heads"], DECODE_T, CFG["head_dim"], generator=g).to(bf)
+    caches = [(kc.to(dev), kc.to(dev)) for _ in range(2)]
+    xd = torch.randn(DECODE_B, 1, CFG["hidden"], generator=g).to(bf).to(dev)
+    reps = 4
+    for _ in range(2):
+        stack.decode(xd, caches, DECODE_T - 1, None)
+    torch.gcu.synchronize()
+    s, e = torch.gcu.Event(enable_timing=True), torch.gcu.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        stack.decode(xd, caches, DECODE_T - 1, None)
+    e.record()
+    torch.gcu.synchronize()
+    print(json.dumps({"micro": "decode_step", "layers": 2, "batch": DECODE_B, "kv_tokens": DECODE_T,
+                      "ms_per_layer": round(s.elapsed_time(e) / reps / 2, 4)}), flush=True)
+
+
 def run_micro_interference():
     """How much a tensor-core GEMM (and the attention kernel) slow down when another stream keeps a second
     kernel running beside them, on ONE GPU: the fused exchange kernel on local buffers (the eight "ranks" are
@@ -938,7 +965,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
     ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
                          "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
-                         "tp_exchange (under torchrun): the exchange kernels alone; interference: a GEMM beside a second kernel on one GPU")
+                         "tp_exchange (under torchrun): the exchange kernels alone; interference: a GEMM beside a second kernel on one GPU; decode_step: two layers of the decode step, eager")
     ap.add_argument("--timeline", action="store_true", help="under torchrun: per-phase device times of an eager tensor-parallel prefill pass")
     ap.add_argument("--rows", type=int, default=8192, help="--micro tp_exchange: rows of the activation (all ranks together)")
     args = ap.parse_args()
@@ -948,6 +975,8 @@ def main():
         run_micro_tp(args.rows)
     elif args.micro == "interference":
         run_micro_interference()
+    elif args.micro == "decode_step":
+        run_micro_decode_step()
     elif args.micro:
         run_micro(args.micro)
     elif args.impl == "reference":

@@ -209,6 +209,14 @@ def test_mm_skinny_split_k(ops, M, N, K):
     tc_close(again, a, w.t(), add, alpha=2.0, beta=0.5)
 
 
+def test_mm_swiglu_one_wave_rule(ops):
+    """The predicate a caller uses to choose between the fused product and mm + swiglu: few rows against a
+    weight that gives every SM 48 to 128 gate columns."""
+    assert ops.mm_swiglu_one_wave(64, 14336) and ops.mm_swiglu_one_wave(1, 7168) and ops.mm_swiglu_one_wave(128, 7104)
+    assert not ops.mm_swiglu_one_wave(64, 3584) and not ops.mm_swiglu_one_wave(129, 14336)
+    assert not ops.mm_swiglu_one_wave(64, 148 * 136) and not ops.mm_swiglu_one_wave(0, 14336)
+
+
 @pytest.mark.parametrize("M,F,K,dtype", [(2048, 1024, 256, BF), (1000, 1100, 520, BF), (300, 136, 72, torch.float16),
                                          (4096, 3584, 512, BF),
                                          # one row-tile against a wide weight: the one-wave kernel (tile width chosen

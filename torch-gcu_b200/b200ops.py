@@ -296,6 +296,13 @@ def mm_swiglu(out, a, w_gate_up, stream=None):
     check(lib().b200_mm_swiglu(_ref(view(out)), _ref(view(a)), _ref(view(w_gate_up)), _stream(stream)))
 
 
+def mm_swiglu_one_wave(rows, f):
+    """True when mm_swiglu runs rows x (2 f) as one equal tile per SM (few rows against a wide weight)."""
+    fn = lib().b200_mm_swiglu_one_wave
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_int64, ctypes.c_int64]
+    return bool(fn(rows, f))
+
+
 def mm_rope(out, a, w, cos_table, sin_table, seq_len, rope_cols, stream=None):
     """out (M,N) = a @ w.T with rotate-half RoPE on the first rope_cols columns (heads of 128), in the GEMM epilogue."""
     check(lib().b200_mm_rope(_ref(view(out)), _ref(view(a)), _ref(view(w)), _ref(view(cos_table)), _ref(view(sin_table)),

@@ -1296,6 +1296,10 @@ b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200
   return mm_swiglu_impl(out, a, w_gate_up, static_cast<cudaStream_t>(stream));
 }
 
+int b200_mm_swiglu_one_wave(int64_t M, int64_t F) {
+  return M > 0 && M <= BM && F > 0 && wide_tile_width(F, 8, 48, 128, gemm_sm_budget()) > 0 ? 1 : 0;
+}
+
 b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
   return matmul_impl(out, a, b, nullptr, 1.0, 0.0, false, static_cast<cudaStream_t>(stream), "b200_mm");
 }
