@@ -187,7 +187,12 @@ def test_bmm_large_enough_for_cta_pairs(ops):
     tc_close(out, a, b)
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (100, 520, 1000), (1, 6144, 4096), (128, 1032, 2048)])
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 14336), (100, 520, 1000), (1, 6144, 4096), (128, 1032, 2048),
+                                   # the rows that exist are dealt out in bands over the cluster: bands of 8, 5
+                                   # (37 = 7 x 5 + 2) and 1 row (three rows over eight CTAs: five own nothing),
+                                   # ragged N and K, two / four / eight slices
+                                   (64, 4096, 4096), (37, 1000, 4104), (3, 2048, 8192), (33, 136, 520), (64, 9000, 1024),
+                                   (65, 4096, 4096)])
 def test_mm_skinny_split_k(ops, M, N, K):
     """Few rows against a large weight matrix (the decode step): K is split over a
     cluster and the partial tiles are summed in a fixed order, so two runs agree
@@ -207,6 +212,13 @@ def test_mm_skinny_split_k(ops, M, N, K):
     add = torch.randn(M, N, generator=g).to(BF)
     ops.addmm(again, dev(add), dev(a), dev(w).t(), beta=0.5, alpha=2.0)
     tc_close(again, a, w.t(), add, alpha=2.0, beta=0.5)
+    if M <= 64:   # through the batched entry point (fewer slices per product: close, not identical)
+        a3, w3 = torch.stack([a, a.flip(0)]), torch.stack([w, w.flip(0)])
+        out3 = torch.empty(2, M, N, dtype=BF, device=DEV)
+        ops.bmm(out3, dev(a3), dev(w3).transpose(1, 2))
+        assert ops.device_error_fetch() == 0
+        tc_close(out3[0], a, w.t())
+        tc_close(out3[1], a3[1], w3[1].t())
 
 
 def test_mm_swiglu_one_wave_rule(ops):
