@@ -272,6 +272,18 @@ b200Status b200_rms_norm_residual(const b200Tensor* y, const b200Tensor* residua
 b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tensor* cos_table,
                      const b200Tensor* sin_table, const b200Tensor* positions,
                      b200Stream stream);
+/* Rotary embedding of a decode step fused with the write into the KV cache: qkv is a fused projection
+ * output (B, S, q_heads + 2 k_heads, D), D contiguous. Query heads are rotated in place; key heads are
+ * rotated (the arithmetic of b200_rope, bit for bit) and written to k_cache[b, head, p, :]; value heads
+ * are copied to v_cache[b, head, p, :], with p = positions[b, s] (int64 (B,S)) both the row of the
+ * cos / sin tables (f32 (P, D/2)) and the slot of the caches ((B, k_heads, T, D) views, D contiguous).
+ * The key and value parts of qkv are left as they were. A position outside [0, min(P, T)) writes
+ * nothing and sets bit 0 of the device error word. Replaces b200_rope followed by two strided copies.
+ * No reference counterpart.                                                                          */
+b200Status b200_rope_kv_append(const b200Tensor* qkv, const b200Tensor* cos_table,
+                               const b200Tensor* sin_table, const b200Tensor* positions,
+                               int64_t q_heads, int64_t k_heads, const b200Tensor* k_cache,
+                               const b200Tensor* v_cache, b200Stream stream);
 /* out = silu(gate) * up, fp32 math, one rounding. 2-D views with contiguous
  * last dim (gate and up may be the two halves of one projection output).      */
 b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200Tensor* up,

@@ -74,6 +74,41 @@ def test_rope_bit_exact(ops, B, S, H, D, dtype):
     exact(dq[:, :, H:].contiguous(), qkv[:, :, H:].contiguous())
 
 
+@pytest.mark.parametrize("B,S,Hq,Hk,D,T", [(4, 1, 8, 2, 128, 40), (2, 3, 3, 1, 64, 16), (64, 1, 32, 8, 128, 64), (1, 1, 1, 1, 32, 8)])
+@pytest.mark.parametrize("dtype", [BF, torch.float32])
+def test_rope_kv_append(ops, B, S, Hq, Hk, D, T, dtype):
+    """The decode step's rotary embedding fused with the cache write, against rope + two copies on the CPU:
+    query heads rotated in place, rotated keys and plain values in the caches' slots, everything else untouched."""
+    g = torch.Generator().manual_seed(34)
+    qkv = torch.randn(B, S, Hq + 2 * Hk, D, generator=g).to(dtype)
+    cos, sin = workloads.rope_tables(T, D)
+    pos = torch.stack([torch.randperm(T, generator=g)[:S] for _ in range(B)])   # distinct slots per sequence
+    # caches as views of a larger allocation (a cache with room to grow), filled with a marker
+    kc_full = torch.full((B, Hk, T + 5, D), 7.0).to(dtype)
+    vc_full = torch.full((B, Hk, T + 5, D), -3.0).to(dtype)
+    dq, dk, dv = dev(qkv), dev(kc_full), dev(vc_full)
+    ops.rope_kv_append(dq, dev(cos), dev(sin), dev(pos), Hq, Hk, dk[:, :, :T], dv[:, :, :T])
+    assert ops.device_error_fetch() == 0
+    rot = aten_cpu.rope(qkv[:, :, :Hq + Hk], cos, sin, pos)
+    want_q = qkv.clone()
+    want_q[:, :, :Hq] = rot[:, :, :Hq]
+    exact(dq, want_q)                       # k and v parts of qkv unchanged
+    want_k, want_v = kc_full.clone(), vc_full.clone()
+    for b in range(B):
+        for s in range(S):
+            want_k[b, :, pos[b, s]] = rot[b, s, Hq:]
+            want_v[b, :, pos[b, s]] = qkv[b, s, Hq + Hk:]
+    exact(dk, want_k)
+    exact(dv, want_v)
+    # a position outside the cache writes nothing and raises the index bit of the error word
+    bad = pos.clone()
+    bad[0, 0] = T
+    before = dk.clone()
+    ops.rope_kv_append(dev(qkv), dev(cos), dev(sin), dev(bad), Hq, Hk, dk[:, :, :T], dv[:, :, :T])
+    assert ops.device_error_fetch() & 1
+    assert torch.equal(dk[0], before[0])
+
+
 def test_rope_golden(ops, golden):
     r = golden("op_small")["rope"]
     out = torch.empty_like(dev(r["q"]))

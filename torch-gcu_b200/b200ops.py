@@ -287,6 +287,14 @@ def rope(out, x, cos_table, sin_table, positions=None, stream=None):
                           _ref(view(positions)), _stream(stream)))
 
 
+def rope_kv_append(qkv, cos_table, sin_table, positions, q_heads, k_heads, k_cache, v_cache, stream=None):
+    """Rotate the query heads of qkv (B,S,Hq+2Hk,D) in place, write the rotated key heads and the value heads
+    into the caches (B,Hk,T,D) at positions (B,S)."""
+    check(lib().b200_rope_kv_append(_ref(view(qkv)), _ref(view(cos_table)), _ref(view(sin_table)), _ref(view(positions)),
+                                    ctypes.c_int64(q_heads), ctypes.c_int64(k_heads), _ref(view(k_cache)), _ref(view(v_cache)),
+                                    _stream(stream)))
+
+
 def swiglu(out, gate, up, stream=None):
     check(lib().b200_swiglu(_ref(view(out)), _ref(view(gate)), _ref(view(up)), _stream(stream)))
 

@@ -18,6 +18,8 @@ at::Tensor swiglu(const at::Tensor& gate, const at::Tensor& up);
 at::Tensor swiglu_packed(const at::Tensor& gate_up);
 at::Tensor linear_swiglu(const at::Tensor& x, const at::Tensor& w_gate_up);
 at::Tensor linear_rope(const at::Tensor& x, const at::Tensor& w, const at::Tensor& cos, const at::Tensor& sin, int64_t rope_heads);
+void rope_kv_append(const at::Tensor& qkv, const at::Tensor& cos, const at::Tensor& sin, const at::Tensor& positions,
+                    int64_t q_heads, const at::Tensor& k_cache, const at::Tensor& v_cache);
 at::Tensor int32_indices_index(const at::Tensor& self, const c10::List<std::optional<at::Tensor>>& indices);
 // (out, logsumexp) of the flash kernel for q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D)
 std::tuple<at::Tensor, at::Tensor> sdpa_flash(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,

@@ -142,6 +142,22 @@ at::Tensor rope(const at::Tensor& x, const at::Tensor& cos, const at::Tensor& si
   return out;
 }
 
+// Decode step: rotate the query heads of qkv (B, S, q_heads + 2 k_heads, D) in place and write the rotated key
+// heads and the value heads into the caches (B, k_heads, T, D) at positions (B, S), in one launch.
+void rope_kv_append(const at::Tensor& qkv, const at::Tensor& cos, const at::Tensor& sin, const at::Tensor& positions,
+                    int64_t q_heads, const at::Tensor& k_cache, const at::Tensor& v_cache) {
+  TORCH_CHECK(qkv.dim() == 4 && k_cache.dim() == 4 && v_cache.dim() == 4, "rope_kv_append: qkv (B,S,H,D) and caches (B,Hk,T,D) expected");
+  TORCH_CHECK(qkv.stride(-1) == 1 && k_cache.stride(-1) == 1 && v_cache.stride(-1) == 1, "rope_kv_append: head dim must be contiguous");
+  TORCH_CHECK(cos.scalar_type() == at::kFloat && sin.scalar_type() == at::kFloat, "rope_kv_append: cos/sin tables must be float32 (P, D/2)");
+  TORCH_CHECK(k_cache.device() == qkv.device() && v_cache.device() == qkv.device(), "rope_kv_append: operands on one device");
+  const c10::OptionalDeviceGuard guard(qkv.device());
+  at::Tensor c = cos.contiguous(), s = sin.contiguous();
+  at::Tensor pos = positions.to(qkv.device(), at::kLong);
+  b200Tensor vq = to_b200(qkv), vc = to_b200(c), vs = to_b200(s), vp = to_b200(pos), vk = to_b200(k_cache), vv = to_b200(v_cache);
+  cudaStream_t stream = current_stream(qkv);
+  GCU_KERNEL_CALL(b200_rope_kv_append, stream, &vq, &vc, &vs, &vp, q_heads, k_cache.size(1), &vk, &vv);
+}
+
 static at::Tensor swiglu_2d(const at::Tensor& gate, const at::Tensor& up, at::IntArrayRef out_shape) {
   at::Tensor out = at::empty(out_shape, gate.options());
   if (out.numel() == 0) return out;

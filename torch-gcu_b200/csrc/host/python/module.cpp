@@ -147,6 +147,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("_swiglu_packed", &aotops::swiglu_packed);
   m.def("_linear_swiglu", &aotops::linear_swiglu);
   m.def("_linear_rope", &aotops::linear_rope);
+  m.def("_rope_kv_append", &aotops::rope_kv_append, py::arg("qkv"), py::arg("cos"), py::arg("sin"), py::arg("positions"),
+        py::arg("q_heads"), py::arg("k_cache"), py::arg("v_cache"));
   m.def("_sdpa_flash", &aotops::sdpa_flash, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("is_causal"),
         py::arg("scale") = py::none());
 

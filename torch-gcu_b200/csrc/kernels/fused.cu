@@ -4,6 +4,8 @@
 #include "common.cuh"
 
 namespace b200 {
+unsigned int* device_error_word();  // index.cu: address of the device error word
+
 namespace {
 
 // ------------------------------------------------------ RMSNorm + residual --
@@ -178,6 +180,84 @@ rope_kernel(RopeArgs a) {
   }
 }
 
+// ------------------------------------------- RoPE + write into the KV cache --
+// One pass over a fused projection output qkv (B, S, q_heads + 2 k_heads, D): query heads are rotated in place, key
+// heads are rotated and written to k_cache[b, head, position, :], value heads are copied to v_cache[b, head,
+// position, :]; position = positions[b, s] is both the row of the tables and the slot of the caches. The key and
+// value parts of qkv stay as they were. A position outside the caches or the tables sets the index-out-of-range
+// bit of the device error word and writes nothing.
+struct RopeAppendArgs {
+  void* qkv;
+  void* kc;
+  void* vc;
+  const float* cos_t;
+  const float* sin_t;
+  const int64_t* positions;
+  int64_t pos_stride_b, pos_stride_s;
+  int64_t B, S, Hq, Hk, D;
+  int64_t xs[3];          // element strides of qkv (b, s, h)
+  int64_t ks[3], vs[3];   // element strides of the caches (b, h, t)
+  int64_t P, T;           // rows of the tables, slots of the caches
+  unsigned int* error_word;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_append_kernel(RopeAppendArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int V = 16 / sizeof(T);
+  const int64_t half = a.D / 2;
+  const int64_t vph = half / V;  // vectors per half row
+  const int64_t H = a.Hq + 2 * a.Hk;
+  const int64_t total = a.B * a.S * H * vph;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 256;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += stride) {
+    int64_t t = i / vph;
+    const int v = static_cast<int>(i - t * vph);
+    const int64_t th = t / H;
+    const int64_t h = t - th * H;
+    const int64_t b = th / a.S;
+    const int64_t s = th - b * a.S;
+    const int64_t p = a.positions[b * a.pos_stride_b + s * a.pos_stride_s];
+    if (p < 0 || p >= a.P || p >= a.T) {
+      if (v == 0 && h == 0) atomicOr(a.error_word, 1u);   // bit 0: index out of range
+      continue;
+    }
+    T* xr = static_cast<T*>(a.qkv) + b * a.xs[0] + s * a.xs[1] + h * a.xs[2];
+    Vec16<T> x1 = load_stream16(xr + v * V);
+    Vec16<T> x2 = load_stream16(xr + half + v * V);
+    T* orow = xr;
+    if (h >= a.Hq + a.Hk) {   // value head: copied as it is
+      orow = static_cast<T*>(a.vc) + b * a.vs[0] + (h - a.Hq - a.Hk) * a.vs[1] + p * a.vs[2];
+      store_stream16(orow + v * V, x1);
+      store_stream16(orow + half + v * V, x2);
+      continue;
+    }
+    if (h >= a.Hq) orow = static_cast<T*>(a.kc) + b * a.ks[0] + (h - a.Hq) * a.ks[1] + p * a.ks[2];
+    const float* c = a.cos_t + p * half + v * V;
+    const float* sn = a.sin_t + p * half + v * V;
+    Vec16<T> o1, o2;
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q) {
+      const float4 cv = *reinterpret_cast<const float4*>(c + q * 4);
+      const float4 sv = *reinterpret_cast<const float4*>(sn + q * 4);
+      const float cc[4] = {cv.x, cv.y, cv.z, cv.w};
+      const float sc[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float a1 = load_as_math(x1.v[q * 4 + e]);
+        const float a2 = load_as_math(x2.v[q * 4 + e]);
+        // the arithmetic of rope_kernel: separate roundings, so both paths give the same bits
+        o1.v[q * 4 + e] = store_from_math<T>(__fadd_rn(__fmul_rn(a1, cc[e]), __fmul_rn(-a2, sc[e])));
+        o2.v[q * 4 + e] = store_from_math<T>(__fadd_rn(__fmul_rn(a2, cc[e]), __fmul_rn(a1, sc[e])));
+      }
+    }
+    store_stream16(orow + v * V, o1);
+    store_stream16(orow + half + v * V, o2);
+  }
+}
+
 // ----------------------------------------------------------------- SwiGLU --
 template <typename T>
 __device__ __forceinline__ Vec16<T> swiglu_vec(const Vec16<T>& g, const Vec16<T>& u) {
@@ -336,6 +416,57 @@ b200Status b200_rope(const b200Tensor* out, const b200Tensor* x, const b200Tenso
     else launch_pdl(rope_kernel<T, int64_t>, wave_grid<rope_kernel<T, int64_t>>(need, 256, 4), 256, 0, s, a);
   });
   return check_launch("b200_rope");
+}
+
+b200Status b200_rope_kv_append(const b200Tensor* qkv, const b200Tensor* cos_table, const b200Tensor* sin_table,
+                               const b200Tensor* positions, int64_t q_heads, int64_t k_heads, const b200Tensor* k_cache,
+                               const b200Tensor* v_cache, b200Stream stream) {
+  const char* name = "b200_rope_kv_append";
+  B200_REQUIRE(valid(qkv) && valid(cos_table) && valid(sin_table) && valid(positions) && valid(k_cache) && valid(v_cache),
+               B200_BAD_PARAM, "%s: invalid tensor view", name);
+  B200_REQUIRE(qkv->ndim == 4 && k_cache->ndim == 4 && v_cache->ndim == 4 && q_heads >= 0 && k_heads >= 0 &&
+               qkv->sizes[2] == q_heads + 2 * k_heads, B200_BAD_PARAM,
+               "%s: qkv must be (B, S, q_heads + 2 k_heads, D), the caches (B, k_heads, T, D)", name);
+  RopeAppendArgs a{};
+  a.B = qkv->sizes[0]; a.S = qkv->sizes[1]; a.Hq = q_heads; a.Hk = k_heads; a.D = qkv->sizes[3];
+  B200_REQUIRE(same_shape(k_cache, v_cache) && k_cache->sizes[0] == a.B && k_cache->sizes[1] == a.Hk &&
+               k_cache->sizes[3] == a.D && k_cache->dtype == qkv->dtype && v_cache->dtype == qkv->dtype, B200_BAD_PARAM,
+               "%s: the caches must be (B, k_heads, T, D) of qkv's dtype", name);
+  if (numel(qkv) == 0) return B200_OK;
+  a.T = k_cache->sizes[2];
+  const int64_t es = static_cast<int64_t>(dtype_size(qkv->dtype));
+  const int64_t V = 16 / es;
+  B200_REQUIRE(a.D % 2 == 0 && qkv->strides[3] == 1 && k_cache->strides[3] == 1 && v_cache->strides[3] == 1, B200_BAD_PARAM,
+               "%s: head dim must be even and contiguous", name);
+  B200_REQUIRE((a.D / 2) % V == 0 && V >= 4, B200_NOT_SUPPORTED, "%s: D/2 must be a multiple of %lld elements", name, (long long)V);
+  B200_REQUIRE(cos_table->dtype == B200_F32 && sin_table->dtype == B200_F32 && cos_table->ndim == 2 &&
+               same_shape(cos_table, sin_table) && cos_table->sizes[1] == a.D / 2 && is_contiguous(cos_table) &&
+               is_contiguous(sin_table), B200_BAD_PARAM, "%s: cos/sin must be contiguous f32 (P, D/2) tables", name);
+  a.P = cos_table->sizes[0];
+  B200_REQUIRE(positions->dtype == B200_I64 && positions->ndim == 2 && positions->sizes[0] == a.B && positions->sizes[1] == a.S,
+               B200_BAD_PARAM, "%s: positions must be int64 (B,S)", name);
+  B200_REQUIRE(aligned16(cos_table->data) && aligned16(sin_table->data) && aligned16(qkv->data) && aligned16(k_cache->data) &&
+               aligned16(v_cache->data), B200_NOT_SUPPORTED, "%s: 16-byte aligned operands needed", name);
+  for (int d = 0; d < 3; ++d) {
+    a.xs[d] = qkv->strides[d]; a.ks[d] = k_cache->strides[d]; a.vs[d] = v_cache->strides[d];
+    B200_REQUIRE((qkv->sizes[d] == 1 || (a.xs[d] * es) % 16 == 0) &&
+                 (k_cache->sizes[d] == 1 || ((a.ks[d] * es) % 16 == 0 && (a.vs[d] * es) % 16 == 0)), B200_NOT_SUPPORTED,
+                 "%s: strides must keep rows 16-byte aligned", name);
+  }
+  a.qkv = qkv->data; a.kc = k_cache->data; a.vc = v_cache->data;
+  a.cos_t = static_cast<const float*>(cos_table->data);
+  a.sin_t = static_cast<const float*>(sin_table->data);
+  a.positions = static_cast<const int64_t*>(positions->data);
+  a.pos_stride_b = positions->strides[0]; a.pos_stride_s = positions->strides[1];
+  a.error_word = device_error_word();
+  B200_REQUIRE(a.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = a.B * a.S * (a.Hq + 2 * a.Hk) * (a.D / 2 / V);
+  const int64_t need = (total + 255) / 256;
+  B200_DISPATCH_HALF_FLOAT(qkv->dtype, T, {
+    launch_pdl(rope_kv_append_kernel<T>, wave_grid<rope_kv_append_kernel<T>>(need, 256, 4), 256, 0, s, a);
+  });
+  return check_launch(name);
 }
 
 b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200Tensor* up, b200Stream stream) {

@@ -66,6 +66,14 @@ def linear_rope(x: Tensor, w: Tensor, cos: Tensor, sin: Tensor, rope_heads: int)
     return _C._linear_rope(x, w, cos, sin, rope_heads)
 
 
+def rope_kv_append(qkv: Tensor, cos: Tensor, sin: Tensor, positions: Tensor, q_heads: int, k_cache: Tensor, v_cache: Tensor):
+    """One decode step's rotary embedding and cache update in one launch: the first `q_heads` heads of qkv
+    (B, S, q_heads + 2 k_heads, D) are rotated in place; the next k_heads heads are rotated and written to
+    k_cache[b, head, positions[b, s]], the last k_heads heads copied to v_cache[b, head, positions[b, s]];
+    caches (B, k_heads, T, D). Same arithmetic as `rope`."""
+    _C._rope_kv_append(qkv, cos, sin, positions, q_heads, k_cache, v_cache)
+
+
 def sdpa_flash(q: Tensor, k: Tensor, v: Tensor, is_causal: bool, scale: Optional[float] = None):
     """Flash attention forward for q (B,Hq,Sq,D), k/v (B,Hkv,Sk,D); returns (out, logsumexp)."""
     return _C._sdpa_flash(q, k, v, is_causal, scale)

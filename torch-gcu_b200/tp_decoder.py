@@ -288,9 +288,8 @@ class DecoderLayer:
         eff = self.eff
         qkv = torch.mm(h, w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
-        eff.rope(qkv[:, :, :hq + hk], cos, sin, self._positions(B, pos), True)
-        kv[0][:, :, pos:pos + 1].copy_(k.transpose(1, 2))
-        kv[1][:, :, pos:pos + 1].copy_(v.transpose(1, 2))
+        # q rotated in place, rotated k and v written into the cache slot: one launch
+        eff.rope_kv_append(qkv, cos, sin, self._positions(B, pos), hq, kv[0], kv[1])
         att, _ = eff.sdpa_flash(q.transpose(1, 2), kv[0][:, :, :pos + 1], kv[1][:, :, :pos + 1], False)
         torch.mm(att.transpose(1, 2).reshape(B, hq * d), w["wo"].t(), out=out)
 
@@ -336,9 +335,7 @@ class DecoderLayer:
         qkv = torch.mm(h.view(B, H), w["wqkv"].t()).view(B, 1, hq + 2 * hk, d)
         q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hk], qkv[:, :, hq + hk:]
         positions = self._positions(B, pos)
-        eff.rope(qkv[:, :, :hq + hk], cos, sin, positions, True)
-        kv[0][:, :, pos:pos + 1].copy_(k.transpose(1, 2))   # strided device copy into the cache slice
-        kv[1][:, :, pos:pos + 1].copy_(v.transpose(1, 2))
+        eff.rope_kv_append(qkv, cos, sin, positions, hq, kv[0], kv[1])   # q in place, rotated k and v into the cache slot
         att, _ = eff.sdpa_flash(q.transpose(1, 2), kv[0][:, :, :pos + 1], kv[1][:, :, :pos + 1], False)
         o = torch.mm(att.transpose(1, 2).reshape(B, hq * d), w["wo"].t())
         self._allreduce(o, group)
