@@ -223,17 +223,19 @@ def test_mm_skinny_split_k(ops, M, N, K):
 
 def test_mm_swiglu_one_wave_rule(ops):
     """The predicate a caller uses to choose between the fused product and mm + swiglu: few rows against a
-    weight that gives every SM 48 to 128 gate columns."""
-    assert ops.mm_swiglu_one_wave(64, 14336) and ops.mm_swiglu_one_wave(1, 7168) and ops.mm_swiglu_one_wave(128, 7104)
-    assert not ops.mm_swiglu_one_wave(64, 3584) and not ops.mm_swiglu_one_wave(129, 14336)
+    weight that gives every SM 64 to 128 gate columns."""
+    assert ops.mm_swiglu_one_wave(64, 14336) and ops.mm_swiglu_one_wave(1, 9472) and ops.mm_swiglu_one_wave(128, 18944)
+    assert not ops.mm_swiglu_one_wave(64, 3584) and not ops.mm_swiglu_one_wave(64, 7168) and not ops.mm_swiglu_one_wave(129, 14336)
     assert not ops.mm_swiglu_one_wave(64, 148 * 136) and not ops.mm_swiglu_one_wave(0, 14336)
 
 
 @pytest.mark.parametrize("M,F,K,dtype", [(2048, 1024, 256, BF), (1000, 1100, 520, BF), (300, 136, 72, torch.float16),
                                          (4096, 3584, 512, BF),
                                          # one row-tile against a wide weight: the one-wave kernel (tile width chosen
-                                         # so that the tiles fill the SMs: 104 + 104, 48 + 48, 64 + 64 ... rows)
-                                         (64, 14336, 4096, BF), (1, 7168, 512, BF), (128, 7104, 256, torch.float16),
+                                         # so that the tiles fill the SMs: 104 + 104, 64 + 64, 128 + 128 rows), and
+                                         # narrower weights, which stay on the pair kernel
+                                         (64, 14336, 4096, BF), (1, 9472, 512, BF), (128, 9400, 256, torch.float16),
+                                         (1, 7168, 512, BF), (128, 7104, 256, torch.float16),
                                          (37, 9000, 520, BF), (64, 18944, 1024, BF), (64, 1792, 4096, BF), (64, 3584, 1024, BF),
                                          (16, 2368, 256, torch.float16), (3, 1200, 136, BF), (128, 200, 64, BF)])
 def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):

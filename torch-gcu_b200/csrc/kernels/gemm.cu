@@ -772,12 +772,18 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) {
+    // under the predecessor's tail: the descriptors, and the first ring's worth of B (a weight, as a rule) asked into
+    // L2, where the loads below find it whatever the predecessor was still doing
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    if (!p.b_mn_major)
+      for (int i = 0; i < min(n_my, kStagesS); ++i) tma_prefetch_l2_3d(&tmap_b, (k_begin + i) * BK, tn * BNS, b);
+  }
   pdl_wait();   // set-up above runs under the predecessor's tail; operands are read from here on
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tmap(&tmap_a);
-      prefetch_tmap(&tmap_b);
       for (int i = 0; i < n_my; ++i) {
         const int stage = i % kStagesS;
         const uint32_t phase = (i / kStagesS) & 1u;
@@ -992,12 +998,23 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) {
+    // under the predecessor's tail: the descriptors, and the first ring's worth of the weight asked into L2
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int k = 0; k < min(n_k, n_stages); ++k) {
+      if (SWIGLU) {
+        tma_prefetch_l2_3d(&tmap_b, k * BK, tn * half, 0);
+        tma_prefetch_l2_3d(&tmap_b, k * BK, p.up_offset + tn * half, 0);
+      } else {
+        tma_prefetch_l2_3d(&tmap_b, k * BK, tn * bn, 0);
+      }
+    }
+  }
   pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
-      prefetch_tmap(&tmap_a);
-      prefetch_tmap(&tmap_b);
       const uint32_t stage_bytes = static_cast<uint32_t>(stage_stride);
       for (int k = 0; k < n_k; ++k) {
         const int stage = k % n_stages;
@@ -1085,6 +1102,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // Columns per tile for the one-wave kernel: the smallest multiple of `unit` that covers `width` columns in at
 // most `sms` tiles; 0 when the product does not suit the kernel (fewer than `at_least` columns per SM: too narrow
 // to give every SM a worthwhile stream; or more than `at_most`: too wide for one wave).
+constexpr int kWideMinHalf = 64;   // gate (and up) rows per tile below which mm_swiglu leaves the one-wave kernel
+
 int wide_tile_width(int64_t width, int unit, int at_least, int at_most, int sms) {
   int64_t bn = (width + sms - 1) / sms;
   bn = (bn + unit - 1) / unit * unit;
@@ -1236,10 +1255,11 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
   B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
   if (M <= BM) {
     // one row-tile against a wide weight (a decode step): one wave of equal tiles instead of 256-row pair tiles.
-    // Gate and up halves of a tile are multiples of 8 rows (one 128-byte-swizzle atom), 48 to 128 each
-    // (measured: with narrower tiles, i.e. F below ~7000, the pair kernel is faster: 25.0 against 29.7 us at
-    // F = 3584, 24.0 against 27.1 us at F = 1792; above, this kernel wins: 51.2 against 56 us at F = 14336).
-    const int half = wide_tile_width(F, 8, 48, 128, gemm_sm_budget());
+    // Gate and up halves of a tile are multiples of 8 rows (one 128-byte-swizzle atom), 64 to 128 each
+    // (measured: with narrower tiles the pair kernel is faster: 25.0 against 29.7 us at F = 3584, 24.0 against
+    // 27.1 us at F = 1792, and at F = 7168, halves of 56 rows, the split-K product followed by the activation
+    // kernel beats both: 27 + 4 us against 34; with wide tiles this kernel wins: 51 against 56 us at F = 14336).
+    const int half = wide_tile_width(F, 8, kWideMinHalf, 128, gemm_sm_budget());
     if (half > 0) return launch_wide<true>(oa, ob, p, 2 * half, s);
   }
   return launch_tc2<1>(oa, ob, p, s);
@@ -1297,7 +1317,7 @@ b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200
 }
 
 int b200_mm_swiglu_one_wave(int64_t M, int64_t F) {
-  return M > 0 && M <= BM && F > 0 && wide_tile_width(F, 8, 48, 128, gemm_sm_budget()) > 0 ? 1 : 0;
+  return M > 0 && M <= BM && F > 0 && wide_tile_width(F, 8, kWideMinHalf, 128, gemm_sm_budget()) > 0 ? 1 : 0;
 }
 
 b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
