@@ -98,6 +98,23 @@ def test_newer_entry_points_reject_malformed_arguments(ops):
     cos16 = _fake(ops, (300, 64), ops.BF16)
     st = L.b200_mm_rope(ref(out_qkv), ref(b16), ref(w16), ref(cos16), ref(cos16), ctypes.c_int64(256), ctypes.c_int64(256), null)
     assert st == ops.BAD_PARAM
+    # rotary embedding + cache write: head counts that do not add up; caches of another dtype; positions not int64
+    qkv = _fake(ops, (4, 1, 12, 128), ops.BF16)
+    kc = _fake(ops, (4, 2, 16, 128), ops.BF16)
+    kc32 = _fake(ops, (4, 2, 16, 128), ops.F32)
+    pos = _fake(ops, (4, 1), ops.I64)
+    posf = _fake(ops, (4, 1), ops.F32)
+    tab = _fake(ops, (16, 64), ops.F32)
+    call = lambda q, p_, hq, hk, k, v: L.b200_rope_kv_append(ref(q), ref(tab), ref(tab), ref(p_), ctypes.c_int64(hq),
+                                                            ctypes.c_int64(hk), ref(k), ref(v), null)
+    assert call(qkv, pos, 9, 2, kc, kc) == ops.BAD_PARAM          # 9 + 2 * 2 != 12
+    assert call(qkv, pos, 8, 2, kc32, kc32) == ops.BAD_PARAM
+    assert call(qkv, posf, 8, 2, kc, kc) == ops.BAD_PARAM
+    # the rule for the one-wave SwiGLU product needs no device (148 SMs assumed without one)
+    L.b200_mm_swiglu_one_wave.restype = ctypes.c_int
+    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(64), ctypes.c_int64(14336)) == 1
+    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(64), ctypes.c_int64(3584)) == 0
+    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(4096), ctypes.c_int64(14336)) == 0
     # comparison: the output must be bool; unknown operator
     bool_out = _fake(ops, (4, 8), ops.BOOL)
     assert L.b200_compare(ref(f32), ref(f32), ref(f32), ctypes.c_int32(0), null) == ops.BAD_PARAM

@@ -455,31 +455,6 @@ radix_sort_fused_kernel(uint32_t* keys_a, uint32_t* keys_b, uint32_t* vals_a, ui
                    static_cast<int64_t>(gridDim.x) * kSortThreads);
 }
 
-__global__ void __launch_bounds__(kThreads)
-segment_bounds_kernel(const uint32_t* __restrict__ sorted_keys, int64_t n, int64_t n_dst,
-                      uint32_t* __restrict__ seg_start) {
-  segment_bounds(sorted_keys, n, n_dst, seg_start, static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x,
-                 static_cast<int64_t>(gridDim.x) * kThreads);
-}
-
-// keys for the row form: the destination row of every source row.
-template <typename I>
-__global__ void __launch_bounds__(kThreads)
-row_keys_kernel(const I* __restrict__ index, int64_t index_stride, int64_t n, int64_t n_dst,
-                int wrap_negative, uint32_t* __restrict__ keys) {
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x; i < n; i += stride) {
-    int64_t d = index[i * index_stride];
-    if (wrap_negative && d < 0) d += n_dst;
-    if (d < 0 || d >= n_dst) {
-      atomicOr(&g_device_error_word, kErrIndexOutOfRange);
-      d = 0x80000000ll;  // flagged: sorts as key 0, consumed as an invalid source
-    }
-    keys[i] = static_cast<uint32_t>(d);
-  }
-}
-
-
 // ---- grouping source rows by destination without a global sort (row form) ----------------
 // The ordered walk needs, for every destination row, its source rows in ascending order. A stable
 // sort of (destination, source) pairs gives that, but for a megabyte of keys its dependent passes
