@@ -713,6 +713,12 @@ def run_micro(name):
         w = (torch.randn(28672, 4096, device=dev) * 0.02).to(bf)
         out = torch.empty(64, 28672, dtype=bf, device=dev)
         fn, work = ops.bind("mm", out, a, w.t()), {"bytes": w.numel() * 2}
+    elif name == "gemm_skinny":
+        # the decode step's down projection: 64 rows against a (4096, 14336) weight, K split over clusters of eight
+        a = torch.randn(64, 14336, device=dev).to(bf)
+        w = (torch.randn(4096, 14336, device=dev) * 0.02).to(bf)
+        out = torch.empty(64, 4096, dtype=bf, device=dev)
+        fn, work = ops.bind("mm", out, a, w.t()), {"bytes": w.numel() * 2}
     elif name == "gemm_wide":
         # decode-shaped gate/up product with the SwiGLU epilogue: 64 rows against a (2 x 14336, 4096) weight
         a = torch.randn(64, 4096, device=dev).to(bf)
@@ -963,7 +969,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-parity", action="store_true", help="skip the CPU check of the prefill output (profiling aid)")
     ap.add_argument("--only", default="", help="comma-separated operator names of the op sweep (profiling aid)")
-    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
+    ap.add_argument("--micro", default="", help="gemm | gemm_swiglu | gemm_splitk | gemm_skinny | gemm_wide | tp_reduce_norm | cumsum | sdpa | sdpa_bwd | decode | swiglu | scatter | add | silu | cast | sum | "
                          "softmax | layer_norm | index_select | gather | rms_norm | rope | sort: a 3-launch case for profiler captures; "
                          "tp_exchange (under torchrun): the exchange kernels alone; interference: a GEMM beside a second kernel on one GPU; decode_step: two layers of the decode step, eager")
     ap.add_argument("--timeline", action="store_true", help="under torchrun: per-phase device times of an eager tensor-parallel prefill pass")
