@@ -410,10 +410,10 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
   // per item; the loads of the next item start while the output of the current one is still being written.
   const int per_x = p.items_y * p.B;
   const int n_items = p.items_x * per_x;
-  const int n_rounds = (n_items + gridDim.x - 1) / gridDim.x;
-  // Round k hands item k * gridDim.x + c to CTA c on even rounds and to CTA gridDim.x - 1 - c on odd rounds: the
-  // lengths fall along the list, so the two directions cancel each other's slope. -1: no item in the last round.
-  auto item_of_round = [&](int k) {
+  const int n_sweeps = (n_items + gridDim.x - 1) / gridDim.x;
+  // Sweep k hands item k * gridDim.x + c to CTA c on even sweeps and to CTA gridDim.x - 1 - c on odd sweeps: the
+  // lengths fall along the list, so the two directions cancel each other's slope. -1: no item in the last sweep.
+  auto item_of_sweep = [&](int k) {
     const int pos = (k & 1) ? static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
     const int idx = k * static_cast<int>(gridDim.x) + pos;
     return idx < n_items ? idx : -1;
@@ -476,8 +476,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       uint32_t kv_it = 0;   // K / V tiles loaded so far (ring position and phase)
       uint32_t q_it = 0;    // items started so far
       bool ok = true;
-      for (int round = 0; round < n_rounds && ok; ++round, ++q_it) {
-        const int idx = item_of_round(round);
+      for (int sweep = 0; sweep < n_sweeps && ok; ++sweep, ++q_it) {
+        const int idx = item_of_sweep(sweep);
         if (idx < 0) break;
         const Item it = item_at(idx);
         for (int j = 0; j < it.n_max && ok; ++j, ++kv_it) {
@@ -516,8 +516,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
       uint32_t p_cnt[2] = {0, 0};      // softmax results consumed so far, per tile
       uint32_t o_cnt[2] = {0, 0};      // items with work so far, per tile
       bool ok = true;
-      for (int round = 0; round < n_rounds && ok; ++round, ++q_it) {
-        const int idx = item_of_round(round);
+      for (int sweep = 0; sweep < n_sweeps && ok; ++sweep, ++q_it) {
+        const int idx = item_of_sweep(sweep);
         if (idx < 0) break;
         const Item it = item_at(idx);
         auto issue_s = [&](int t, int j) {
@@ -593,8 +593,8 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gri
     uint32_t s_cnt = 0;    // S tiles of this tile consumed so far
     uint32_t o_cnt = 0;    // items with work for this tile so far
     bool ok = true;
-    for (int round = 0; round < n_rounds && ok; ++round) {
-      const int idx = item_of_round(round);
+    for (int sweep = 0; sweep < n_sweeps && ok; ++sweep) {
+      const int idx = item_of_sweep(sweep);
       if (idx < 0) break;
       const Item it = item_at(idx);
       const int b = it.b;
