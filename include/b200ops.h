@@ -296,12 +296,13 @@ b200Status b200_swiglu(const b200Tensor* out, const b200Tensor* gate, const b200
  * No reference counterpart: the reference runs mm followed by pointwise ops.     */
 b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200Tensor* w_gate_up,
                           b200Stream stream);
-/* 1 when b200_mm_swiglu runs an (M, 2F) product as one wave of equal tiles, one per SM of the
- * current device, each streaming its rows of the weight once (few rows against a wide weight:
- * a decode step); 0 when it would use the 256-row pair tiles, which for so few rows are slower
- * than b200_mm followed by b200_swiglu. Lets a caller pick between the two without repeating
- * the kernel's tile rule. No reference counterpart.                                           */
-int b200_mm_swiglu_one_wave(int64_t M, int64_t F);
+/* 1 when b200_mm_swiglu has a kernel made for few rows (M <= 128) against this weight: one wave of
+ * equal tiles, one per SM, for a wide weight, or K split over clusters with the activation applied
+ * by the CTA that sums a band, for a narrower one; both stream the weight once. 0 when it would
+ * fall back to the 256-row pair tiles, which for so few rows are slower than b200_mm followed by
+ * b200_swiglu. Lets a caller pick without repeating the kernels' tile rules. No reference
+ * counterpart.                                                                                   */
+int b200_mm_swiglu_few_rows(int64_t M, int64_t F, int64_t K);
 /* Fused qkv projection with the rotary embedding in the GEMM epilogue:
  *   out (M,N) = a @ w^T, then rotate-half RoPE (the convention of b200_rope) on the first
  *   rope_cols columns, taken as heads of 128; row m has position m % seq_len.

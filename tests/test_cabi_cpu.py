@@ -110,11 +110,11 @@ def test_newer_entry_points_reject_malformed_arguments(ops):
     assert call(qkv, pos, 9, 2, kc, kc) == ops.BAD_PARAM          # 9 + 2 * 2 != 12
     assert call(qkv, pos, 8, 2, kc32, kc32) == ops.BAD_PARAM
     assert call(qkv, posf, 8, 2, kc, kc) == ops.BAD_PARAM
-    # the rule for the one-wave SwiGLU product needs no device (148 SMs assumed without one)
-    L.b200_mm_swiglu_one_wave.restype = ctypes.c_int
-    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(64), ctypes.c_int64(14336)) == 1
-    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(64), ctypes.c_int64(3584)) == 0
-    assert L.b200_mm_swiglu_one_wave(ctypes.c_int64(4096), ctypes.c_int64(14336)) == 0
+    # the rule for the few-row SwiGLU product needs no device (148 SMs assumed without one)
+    L.b200_mm_swiglu_few_rows.restype = ctypes.c_int
+    few = lambda m, f, k: L.b200_mm_swiglu_few_rows(ctypes.c_int64(m), ctypes.c_int64(f), ctypes.c_int64(k))
+    assert few(64, 14336, 4096) == 1 and few(64, 3584, 4096) == 1 and few(64, 1792, 4096) == 1
+    assert few(4096, 14336, 4096) == 0 and few(64, 3584, 64) == 0 and few(0, 3584, 4096) == 0
     # comparison: the output must be bool; unknown operator
     bool_out = _fake(ops, (4, 8), ops.BOOL)
     assert L.b200_compare(ref(f32), ref(f32), ref(f32), ctypes.c_int32(0), null) == ops.BAD_PARAM

@@ -221,12 +221,13 @@ def test_mm_skinny_split_k(ops, M, N, K):
         tc_close(out3[1], a3[1], w3[1].t())
 
 
-def test_mm_swiglu_one_wave_rule(ops):
-    """The predicate a caller uses to choose between the fused product and mm + swiglu: few rows against a
-    weight that gives every SM 64 to 128 gate columns."""
-    assert ops.mm_swiglu_one_wave(64, 14336) and ops.mm_swiglu_one_wave(1, 9472) and ops.mm_swiglu_one_wave(128, 18944)
-    assert not ops.mm_swiglu_one_wave(64, 3584) and not ops.mm_swiglu_one_wave(64, 7168) and not ops.mm_swiglu_one_wave(129, 14336)
-    assert not ops.mm_swiglu_one_wave(64, 148 * 136) and not ops.mm_swiglu_one_wave(0, 14336)
+def test_mm_swiglu_few_rows_rule(ops):
+    """The predicate a caller uses to choose between the fused product and mm + swiglu for few rows: a weight
+    wide enough for one tile of 64 to 128 gate columns per SM, or one whose K can be split over clusters."""
+    assert ops.mm_swiglu_few_rows(64, 14336, 4096) and ops.mm_swiglu_few_rows(1, 9472, 512) and ops.mm_swiglu_few_rows(128, 18944, 256)
+    assert ops.mm_swiglu_few_rows(64, 3584, 4096) and ops.mm_swiglu_few_rows(64, 7168, 4096) and ops.mm_swiglu_few_rows(64, 1792, 4096)
+    assert not ops.mm_swiglu_few_rows(129, 14336, 4096) and not ops.mm_swiglu_few_rows(64, 3584, 256)
+    assert not ops.mm_swiglu_few_rows(64, 148 * 136, 256) and not ops.mm_swiglu_few_rows(0, 14336, 4096)
 
 
 @pytest.mark.parametrize("M,F,K,dtype", [(2048, 1024, 256, BF), (1000, 1100, 520, BF), (300, 136, 72, torch.float16),
@@ -236,6 +237,9 @@ def test_mm_swiglu_one_wave_rule(ops):
                                          # narrower weights, which stay on the pair kernel
                                          (64, 14336, 4096, BF), (1, 9472, 512, BF), (128, 9400, 256, torch.float16),
                                          (1, 7168, 512, BF), (128, 7104, 256, torch.float16),
+                                         # few rows against a narrower weight: K split over clusters of 2 / 4 / 8, tiles
+                                         # of 64 gate + 64 up rows, the activation applied by the CTA that sums a band
+                                         (64, 7168, 4096, BF), (37, 1000, 1032, BF), (5, 100, 4096, torch.float16), (128, 1792, 2048, BF),
                                          (37, 9000, 520, BF), (64, 18944, 1024, BF), (64, 1792, 4096, BF), (64, 3584, 1024, BF),
                                          (16, 2368, 256, torch.float16), (3, 1200, 136, BF), (128, 200, 64, BF)])
 def test_mm_swiglu_fused_epilogue(ops, M, F, K, dtype):

@@ -304,11 +304,12 @@ def mm_swiglu(out, a, w_gate_up, stream=None):
     check(lib().b200_mm_swiglu(_ref(view(out)), _ref(view(a)), _ref(view(w_gate_up)), _stream(stream)))
 
 
-def mm_swiglu_one_wave(rows, f):
-    """True when mm_swiglu runs rows x (2 f) as one equal tile per SM (few rows against a wide weight)."""
-    fn = lib().b200_mm_swiglu_one_wave
-    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_int64, ctypes.c_int64]
-    return bool(fn(rows, f))
+def mm_swiglu_few_rows(rows, f, k):
+    """True when mm_swiglu has a few-row kernel (one wave of equal tiles, or split-K with the activation in the
+    reduction) for rows x (2 f) x k."""
+    fn = lib().b200_mm_swiglu_few_rows
+    fn.restype, fn.argtypes = ctypes.c_int, [ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+    return bool(fn(rows, f, k))
 
 
 def mm_rope(out, a, w, cos_table, sin_table, seq_len, rope_cols, stream=None):

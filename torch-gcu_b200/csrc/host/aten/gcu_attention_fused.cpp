@@ -189,9 +189,9 @@ at::Tensor swiglu_packed(const at::Tensor& gate_up) {
 }
 
 // x (..., K) times a fused gate/up weight (2F, K): large row counts run the GEMM whose
-// epilogue applies silu(gate) * up, and so do few rows against a weight wide enough for one
-// equal tile per SM (a decode step); few rows against a narrow weight (a tensor-parallel
-// shard) stream it through the split-K product and apply the activation afterwards.
+// epilogue applies silu(gate) * up, and so do few rows (a decode step) whenever the kernel
+// library has a few-row form for the weight (one equal tile per SM, or K split over clusters);
+// otherwise mm followed by the activation kernel.
 at::Tensor linear_swiglu(const at::Tensor& x, const at::Tensor& w_gate_up) {
   TORCH_CHECK(x.dim() >= 1 && w_gate_up.dim() == 2 && w_gate_up.size(0) % 2 == 0 && w_gate_up.size(1) == x.size(-1),
               "linear_swiglu: x (..., K) and w (2F, K) expected");
@@ -201,7 +201,7 @@ at::Tensor linear_swiglu(const at::Tensor& x, const at::Tensor& w_gate_up) {
   std::vector<int64_t> shape = x.sizes().vec();
   shape.back() = f;
   const c10::OptionalDeviceGuard guard(x.device());
-  const bool fused = (x2.size(0) >= 512 || b200_mm_swiglu_one_wave(x2.size(0), f) != 0) &&
+  const bool fused = (x2.size(0) >= 512 || b200_mm_swiglu_few_rows(x2.size(0), f, k) != 0) &&
                      (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kHalf) && k % 8 == 0;
   if (!fused) return swiglu_packed(at::mm(x2, w_gate_up.t())).view(shape);
   at::Tensor w = w_gate_up.contiguous();

@@ -730,6 +730,10 @@ constexpr int kPartialStride = BNS + 4;               // padded: 16-byte accesse
 constexpr int kSmemS = kStagesS * kStageS + 1024 + 256;
 static_assert(BM * kPartialStride * 4 <= kStagesS * kStageS, "the partial tile reuses the drained stage ring");
 
+// SWIGLU: B is a fused gate/up weight (2F, K), p.N = F output columns. A tile holds 64 gate rows and the 64 up rows
+// that go with them (two boxes of 64 rows), so the summed tile has a gate half and an up half, and the band owner
+// stores silu(gate) * up: 64 output columns per tile.
+template <bool SWIGLU>
 __global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const GemmParams p, const int splits) {
@@ -747,7 +751,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rank = static_cast<int>(cluster.block_rank());
-  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BNS - 1) / BNS;
+  constexpr int kCols = SWIGLU ? BNS / 2 : BNS;   // output columns per tile
+  const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + kCols - 1) / kCols;
   int b, tm, tn;
   tile_coords(static_cast<int>(blockIdx.x) / splits, tiles_m, tiles_n, p.group_m, b, tm, tn);
   const int n_k = (p.K + BK - 1) / BK;
@@ -778,7 +783,10 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
     if (!p.b_mn_major)
-      for (int i = 0; i < min(n_my, kStagesS); ++i) tma_prefetch_l2_3d(&tmap_b, (k_begin + i) * BK, tn * BNS, b);
+      for (int i = 0; i < min(n_my, kStagesS); ++i) {
+        tma_prefetch_l2_3d(&tmap_b, (k_begin + i) * BK, tn * kCols, b);
+        if (SWIGLU) tma_prefetch_l2_3d(&tmap_b, (k_begin + i) * BK, p.up_offset + tn * kCols, b);
+      }
   }
   pdl_wait();   // set-up above runs under the predecessor's tail; operands are read from here on
 
@@ -798,7 +806,10 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, &tmap_a, &full[stage], tm * BM + j * 64, k * BK, b);
         }
-        if (!p.b_mn_major) {
+        if (SWIGLU) {
+          tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * kCols, b);                              // gate rows
+          tma_load_3d(sb + kCols * BK * 2, &tmap_b, &full[stage], k * BK, p.up_offset + tn * kCols, b);   // up rows
+        } else if (!p.b_mn_major) {
           tma_load_3d(sb, &tmap_b, &full[stage], k * BK, tn * BNS, b);
         } else {
 #pragma unroll
@@ -868,39 +879,76 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 #pragma unroll
     for (int c = 0; c < 8; ++c) src[c] = cluster.map_shared_rank(partial, c < splits ? c : 0);
     const bool is_bf16 = p.is_bf16 != 0;
-    for (int u = tid; u < (r1 - r0) * (BNS / 4); u += 128) {
-      const int lr = r0 + u / (BNS / 4), col = (u % (BNS / 4)) * 4;
-      const int grow = tm * BM + lr, gcol = tn * BNS + col;
-      float4 v[8];
+    if constexpr (SWIGLU) {
+      for (int u = tid; u < (r1 - r0) * (kCols / 4); u += 128) {
+        const int lr = r0 + u / (kCols / 4), col = (u % (kCols / 4)) * 4;
+        const int grow = tm * BM + lr, gcol = tn * kCols + col;
+        float4 vg[8], vu[8];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        if (c < splits) v[c] = *reinterpret_cast<const float4*>(src[c] + lr * kPartialStride + col);
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < 8; ++c)
+          if (c < splits) {
+            vg[c] = *reinterpret_cast<const float4*>(src[c] + lr * kPartialStride + col);
+            vu[c] = *reinterpret_cast<const float4*>(src[c] + lr * kPartialStride + kCols + col);
+          }
+        float g[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        if (c < splits) {
-          acc[0] += v[c].x; acc[1] += v[c].y; acc[2] += v[c].z; acc[3] += v[c].w;
+        for (int c = 0; c < 8; ++c)
+          if (c < splits) {
+            g[0] += vg[c].x; g[1] += vg[c].y; g[2] += vg[c].z; g[3] += vg[c].w;
+            up[0] += vu[c].x; up[1] += vu[c].y; up[2] += vu[c].z; up[3] += vu[c].w;
+          }
+        if (gcol >= p.N) continue;
+        uint16_t bits[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float o = __fdividef(g[j], 1.0f + __expf(-g[j])) * up[j];   // the epilogue of the other SwiGLU kernels
+          bits[j] = is_bf16 ? f32_to_bf16_bits(o) : f32_to_f16_bits(o);
         }
-      if (gcol >= p.N) continue;
-      uint16_t bits[4];
+        uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(grow) * p.o_sm + gcol;
+        if (gcol + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (static_cast<uint32_t>(bits[1]) << 16),
+                                                      bits[2] | (static_cast<uint32_t>(bits[3]) << 16));
+        } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float o = p.alpha * acc[j];
-        if (p.cin && gcol + j < p.N) {
-          const uint16_t cb = static_cast<const uint16_t*>(p.cin)[b * p.c_sb + static_cast<int64_t>(grow) * p.c_sm +
-                                                                static_cast<int64_t>(gcol + j) * p.c_sn];
-          o += p.beta * (is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+          for (int j = 0; j < 4; ++j)
+            if (gcol + j < p.N) dst[j] = bits[j];
         }
-        bits[j] = is_bf16 ? f32_to_bf16_bits(o) : f32_to_f16_bits(o);
       }
-      uint16_t* dst = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(grow) * p.o_sm + gcol;
-      if (gcol + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (static_cast<uint32_t>(bits[1]) << 16),
-                                                    bits[2] | (static_cast<uint32_t>(bits[3]) << 16));
-      } else {
+    } else {
+      for (int u = tid; u < (r1 - r0) * (BNS / 4); u += 128) {
+        const int lr = r0 + u / (BNS / 4), col = (u % (BNS / 4)) * 4;
+        const int grow = tm * BM + lr, gcol = tn * BNS + col;
+        float4 v[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (gcol + j < p.N) dst[j] = bits[j];
+        for (int c = 0; c < 8; ++c)
+          if (c < splits) v[c] = *reinterpret_cast<const float4*>(src[c] + lr * kPartialStride + col);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          if (c < splits) {
+            acc[0] += v[c].x; acc[1] += v[c].y; acc[2] += v[c].z; acc[3] += v[c].w;
+          }
+        if (gcol >= p.N) continue;
+        uint16_t bits[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float o = p.alpha * acc[j];
+          if (p.cin && gcol + j < p.N) {
+            const uint16_t cb = static_cast<const uint16_t*>(p.cin)[b * p.c_sb + static_cast<int64_t>(grow) * p.c_sm +
+                                                                  static_cast<int64_t>(gcol + j) * p.c_sn];
+            o += p.beta * (is_bf16 ? bf16_bits_to_f32(cb) : f16_bits_to_f32(cb));
+          }
+          bits[j] = is_bf16 ? f32_to_bf16_bits(o) : f32_to_f16_bits(o);
+        }
+        uint16_t* dst = static_cast<uint16_t*>(p.out) + b * p.o_sb + static_cast<int64_t>(grow) * p.o_sm + gcol;
+        if (gcol + 3 < p.N && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(bits[0] | (static_cast<uint32_t>(bits[1]) << 16),
+                                                      bits[2] | (static_cast<uint32_t>(bits[3]) << 16));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (gcol + j < p.N) dst[j] = bits[j];
+        }
       }
     }
   }
@@ -914,7 +962,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
   if (threadIdx.x == 0 && *abort_flag) atomicOr(p.error_word, 2u);
 }
 
-b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int splits, cudaStream_t s) {
+template <bool SWIGLU>
+b200Status launch_splitk(const Operand& oa, Operand ob, GemmParams p, int splits, cudaStream_t s) {
+  if (SWIGLU) ob.box[1] = BNS / 2;   // gate and up rows of a tile are loaded as two boxes
   CUtensorMap ta, tb;
   const char* err = "";
   B200_REQUIRE(encode_tmap_16bit(&ta, oa.base, 3, oa.dims, oa.strides, oa.box, &err), B200_NOT_SUPPORTED, "matmul: %s", err);
@@ -923,12 +973,13 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev != last_dev) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_splitk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemS);
+    cudaError_t e = cudaFuncSetAttribute(gemm_splitk_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemS);
     B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
     last_dev = dev;
   }
   p.group_m = 8;
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BNS - 1) / BNS) * p.batch;
+  constexpr int kCols = SWIGLU ? BNS / 2 : BNS;
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + kCols - 1) / kCols) * p.batch;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * splits);
   cfg.blockDim = dim3(kGemmThreads);
@@ -943,7 +994,7 @@ b200Status launch_splitk(const Operand& oa, const Operand& ob, GemmParams p, int
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel, ta, tb, p, splits);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<SWIGLU>, ta, tb, p, splits);
   B200_REQUIRE(e == cudaSuccess, B200_LAUNCH_FAILED, "matmul: %s", cudaGetErrorString(e));
   return check_launch("matmul (tcgen05, split-K)");
 }
@@ -1102,6 +1153,16 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // Columns per tile for the one-wave kernel: the smallest multiple of `unit` that covers `width` columns in at
 // most `sms` tiles; 0 when the product does not suit the kernel (fewer than `at_least` columns per SM: too narrow
 // to give every SM a worthwhile stream; or more than `at_most`: too wide for one wave).
+// Slices of K for the few-row SwiGLU product on 64-column tiles: the rule of the plain skinny product (one wave of two
+// CTAs per SM, at least 4 k-steps per slice); 1 = no split.
+int swiglu_splits(int64_t F, int64_t K) {
+  const int64_t tiles = (F + BNS / 2 - 1) / (BNS / 2), n_k = (K + BK - 1) / BK;
+  const int sms = gemm_sm_budget();
+  int splits = 1;
+  while (splits < 8 && tiles * splits * 2 <= 2 * sms && n_k >= splits * 2 * 4) splits *= 2;
+  return splits;
+}
+
 constexpr int kWideMinHalf = 64;   // gate (and up) rows per tile below which mm_swiglu leaves the one-wave kernel
 
 int wide_tile_width(int64_t width, int unit, int at_least, int at_most, int sms) {
@@ -1210,7 +1271,7 @@ b200Status matmul_impl(const b200Tensor* out, const b200Tensor* a, const b200Ten
       p.error_word = device_error_word();
       B200_REQUIRE(p.error_word, B200_LAUNCH_FAILED, "%s: device error word unavailable", name);
       if (pair_kernel) return launch_tc2<0>(oa, ob, p, s);
-      if (skinny) return launch_splitk(oa, ob, p, splits, s);
+      if (skinny) return launch_splitk<false>(oa, ob, p, splits, s);
       if (bn == 256) return launch_tc<256>(oa, ob, p, s);
       if (bn == 128) return launch_tc<128>(oa, ob, p, s);
       return launch_tc<64>(oa, ob, p, s);
@@ -1261,6 +1322,9 @@ b200Status mm_swiglu_impl(const b200Tensor* out, const b200Tensor* a, const b200
     // kernel beats both: 27 + 4 us against 34; with wide tiles this kernel wins: 51 against 56 us at F = 14336).
     const int half = wide_tile_width(F, 8, kWideMinHalf, 128, gemm_sm_budget());
     if (half > 0) return launch_wide<true>(oa, ob, p, 2 * half, s);
+    // a narrower weight: K split over a cluster, 64 gate + 64 up rows per tile, the activation applied by the band owner
+    const int splits = swiglu_splits(F, K);
+    if (splits > 1) return launch_splitk<true>(oa, ob, p, splits, s);
   }
   return launch_tc2<1>(oa, ob, p, s);
 }
@@ -1316,8 +1380,9 @@ b200Status b200_mm_swiglu(const b200Tensor* out, const b200Tensor* a, const b200
   return mm_swiglu_impl(out, a, w_gate_up, static_cast<cudaStream_t>(stream));
 }
 
-int b200_mm_swiglu_one_wave(int64_t M, int64_t F) {
-  return M > 0 && M <= BM && F > 0 && wide_tile_width(F, 8, kWideMinHalf, 128, gemm_sm_budget()) > 0 ? 1 : 0;
+int b200_mm_swiglu_few_rows(int64_t M, int64_t F, int64_t K) {
+  if (M <= 0 || M > BM || F <= 0 || K <= 0 || !pair_kernel_enabled()) return 0;
+  return wide_tile_width(F, 8, kWideMinHalf, 128, gemm_sm_budget()) > 0 || swiglu_splits(F, K) > 1 ? 1 : 0;
 }
 
 b200Status b200_mm(const b200Tensor* out, const b200Tensor* a, const b200Tensor* b, b200Stream stream) {
